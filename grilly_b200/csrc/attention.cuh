@@ -1,0 +1,406 @@
+// Flash-attention forward on tcgen05 for sm_100a: softmax(scale * Q K^T + mask) V
+// without materialising the score matrix.
+//
+// Data layout: Q, K, V and the output are row-major 2-D views [token rows][width];
+// head h of a token occupies columns [h*D, (h+1)*D). That covers the (B,S,H,D)
+// layout of flash_attention2 (width = H*D, three tensors) and a packed QKV
+// projection output (width = 3*H*D, three base pointers into one buffer).
+// Sequences are either padded (batch b owns rows [b*S, (b+1)*S)) or packed
+// back to back with cu_seqlens[b] giving the first row of sequence b.
+//
+// One CTA handles 128 queries of one (sequence, head). Warp 4 (one lane) issues
+// TMA loads and tcgen05.mma; warps 0..3 own one query row per thread:
+//   S = Q K_j^T  (smem x smem -> TMEM, 128 fp32 columns)
+//   row max / exp2 / row sum in registers, P written to swizzled shared memory
+//   O_j = P V_j  (V is the MN-major B operand, read as loaded) -> TMEM
+//   O += O_j with the running-max rescale kept in registers.
+// RoPE (interleaved or rotate-half pairs) is applied to the Q and K tiles in
+// shared memory right after the TMA load, before the first MMA reads them.
+#pragma once
+#include "ptx.cuh"
+#include "gemm.cuh"  // round_to_tf32
+#include <cuda_bf16.h>
+
+namespace gb {
+
+
+
+constexpr int ATTN_THREADS = 160;
+constexpr int ATTN_TILE = 128;       // queries per CTA and keys per step
+constexpr int ATTN_CHUNK_BYTES = ATTN_TILE * 128;  // one 128-row x 128-B swizzled chunk
+
+template <int D, bool kBf16>
+struct AttnCfg {
+  static constexpr int ELT = kBf16 ? 2 : 4;
+  static constexpr int NCH = D * ELT / 128;            // 128-B chunks per Q/K/V row
+  static constexpr int PCH = ATTN_TILE * ELT / 128;    // 128-B chunks per P row
+  static_assert(D * ELT % 128 == 0 && NCH >= 1 && NCH <= 2, "head_dim*elt must be 128 or 256 bytes");
+  static constexpr int Q_BYTES = NCH * ATTN_CHUNK_BYTES;
+  static constexpr int P_BYTES = PCH * ATTN_CHUNK_BYTES;
+  static constexpr int SMEM_BYTES = 3 * Q_BYTES + P_BYTES + 1024 + 128;
+  static constexpr int TMEM_COLS = 256;                // S: 128 columns, O_j: D columns at +128
+};
+
+// Rotate one row of a Q or K tile in place in swizzled shared memory.
+template <int D, bool kBf16>
+__device__ __forceinline__ void rope_row_inplace(uint8_t* tile, int r, int pos, const AttnArgs& a) {
+  constexpr int ELT = kBf16 ? 2 : 4;
+  constexpr int EPP = 16 / ELT;        // elements per 16-B piece
+  constexpr int PIECES = D / EPP;      // pieces per row
+  const float* ct = a.rope_cos + static_cast<long long>(pos) * (D / 2);
+  const float* st = a.rope_sin + static_cast<long long>(pos) * (D / 2);
+  auto piece_ptr = [&](int pc) -> uint4* {
+    const int chunk = pc >> 3, within = pc & 7;
+    return reinterpret_cast<uint4*>(tile + chunk * ATTN_CHUNK_BYTES + r * 128 + ((within ^ (r & 7)) << 4));
+  };
+  auto unpack = [&](const uint4& q, float* f) {
+    if constexpr (kBf16) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    } else {
+      f[0] = __uint_as_float(q.x); f[1] = __uint_as_float(q.y); f[2] = __uint_as_float(q.z); f[3] = __uint_as_float(q.w);
+    }
+  };
+  auto pack = [&](const float* f) -> uint4 {
+    uint4 q;
+    if constexpr (kBf16) {
+      __nv_bfloat162 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      q.x = *reinterpret_cast<uint32_t*>(&h[0]); q.y = *reinterpret_cast<uint32_t*>(&h[1]);
+      q.z = *reinterpret_cast<uint32_t*>(&h[2]); q.w = *reinterpret_cast<uint32_t*>(&h[3]);
+    } else {
+      q.x = __float_as_uint(f[0]); q.y = __float_as_uint(f[1]); q.z = __float_as_uint(f[2]); q.w = __float_as_uint(f[3]);
+    }
+    return q;
+  };
+  if (a.rope_style == ROPE_INTERLEAVED) {
+#pragma unroll
+    for (int pc = 0; pc < PIECES; ++pc) {
+      uint4* p = piece_ptr(pc);
+      float f[EPP];
+      unpack(*p, f);
+#pragma unroll
+      for (int e = 0; e < EPP; e += 2) {
+        const int i = (pc * EPP + e) >> 1;  // pair index
+        const float c = __ldg(ct + i), s = __ldg(st + i);
+        const float x0 = f[e], x1 = f[e + 1];
+        f[e] = x0 * c - x1 * s;
+        f[e + 1] = x0 * s + x1 * c;
+      }
+      *p = pack(f);
+    }
+  } else {
+#pragma unroll
+    for (int pc = 0; pc < PIECES / 2; ++pc) {
+      uint4* p0 = piece_ptr(pc);
+      uint4* p1 = piece_ptr(pc + PIECES / 2);
+      float f0[EPP], f1[EPP];
+      unpack(*p0, f0);
+      unpack(*p1, f1);
+#pragma unroll
+      for (int e = 0; e < EPP; ++e) {
+        const int i = pc * EPP + e;  // pair (i, i + D/2)
+        const float c = __ldg(ct + i), s = __ldg(st + i);
+        const float x0 = f0[e], x1 = f1[e];
+        f0[e] = x0 * c - x1 * s;
+        f1[e] = x1 * c + x0 * s;
+      }
+      *p0 = pack(f0);
+      *p1 = pack(f1);
+    }
+  }
+}
+
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(ATTN_THREADS)
+flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
+  using Cfg = AttnCfg<D, kBf16>;
+  constexpr int ELT = Cfg::ELT;
+  constexpr int NCH = Cfg::NCH;
+  constexpr int PCH = Cfg::PCH;
+  constexpr int CHE = 128 / ELT;            // elements per 128-B chunk
+  constexpr int UMMA_K = 32 / ELT;
+  constexpr uint32_t IDESC_S = make_idesc(kBf16, 128, ATTN_TILE, false, false);  // Q (K-major) x K (K-major)
+  constexpr uint32_t IDESC_O = make_idesc(kBf16, 128, D, false, true);           // P (K-major) x V (MN-major)
+
+  const int qtile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  int row0, L;
+  if (args.cu_seqlens) {
+    row0 = args.cu_seqlens[b];
+    L = args.cu_seqlens[b + 1] - row0;
+  } else {
+    row0 = b * args.S;
+    L = args.S;
+  }
+  const int q0 = qtile * ATTN_TILE;
+  if (q0 >= L) return;  // uniform for the CTA; nothing allocated yet
+  int n_kv = (L + ATTN_TILE - 1) / ATTN_TILE;
+  if (args.causal) n_kv = min(n_kv, qtile + 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::Q_BYTES;
+  uint8_t* sV = sK + Cfg::Q_BYTES;
+  uint8_t* sP = sV + Cfg::Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::P_BYTES);
+  uint64_t* bar_q = bars + 0;     // Q tile landed
+  uint64_t* bar_k = bars + 1;     // K tile landed
+  uint64_t* bar_v = bars + 2;     // V tile landed
+  uint64_t* bar_s = bars + 3;     // S = Q K^T complete in TMEM
+  uint64_t* bar_p = bars + 4;     // P written (and S, O_j of the previous step fully read)
+  uint64_t* bar_o = bars + 5;     // O_j = P V complete in TMEM
+  uint64_t* bar_rq = bars + 6;    // Q rotated (RoPE)
+  uint64_t* bar_rk = bars + 7;    // K rotated (RoPE)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool rope = args.rope_style != ROPE_NONE;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 128); mbar_init(bar_o, 1);
+    mbar_init(bar_rq, 128); mbar_init(bar_rk, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_o = tmem_base + ATTN_TILE;
+
+#define ATTN_FAIL()                                         \
+  do {                                                      \
+    if (!*abort_flag) atomicCAS(args.err, 0, ERR_WAIT_ATTN); \
+    *abort_flag = 1;                                        \
+  } while (0)
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // -------------------------------------------------------- TMA + MMA issuer
+      const int colq = h * D;
+      mbar_expect_tx(bar_q, Cfg::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tma_load_2d(sQ + c * ATTN_CHUNK_BYTES, &tmap_q, bar_q, colq + c * CHE, row0 + q0);
+      mbar_expect_tx(bar_k, Cfg::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tma_load_2d(sK + c * ATTN_CHUNK_BYTES, &tmap_k, bar_k, colq + c * CHE, row0);
+      mbar_expect_tx(bar_v, Cfg::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tma_load_2d(sV + c * ATTN_CHUNK_BYTES, &tmap_v, bar_v, colq + c * CHE, row0);
+
+      bool ok = mbar_wait(rope ? bar_rq : bar_q, 0, abort_flag);
+      if (!ok) ATTN_FAIL();
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(rope ? bar_rk : bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
+        tc_fence_after();
+        // S = Q K_j^T : D/UMMA_K k-steps of 32 B, walking the 128-B chunks
+#pragma unroll
+        for (int ks = 0; ks < D / UMMA_K; ++ks) {
+          const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
+          const uint64_t adesc = make_smem_desc_sw128(smem_u32(sQ) + chunk * ATTN_CHUNK_BYTES + off, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(sK) + chunk * ATTN_CHUNK_BYTES + off, 16, 1024);
+          umma_ss<kBf16>(tmem_s, adesc, bdesc, IDESC_S, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s);
+        if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
+        if (j + 1 < n_kv) {  // K buffer is free again: fetch the next key tile
+          mbar_expect_tx(bar_k, Cfg::Q_BYTES);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+            tma_load_2d(sK + c * ATTN_CHUNK_BYTES, &tmap_k, bar_k, colq + c * CHE, row0 + (j + 1) * ATTN_TILE);
+        }
+        if (!mbar_wait(bar_p, ph, abort_flag)) { ATTN_FAIL(); break; }
+        if (!mbar_wait(bar_v, ph, abort_flag)) { ATTN_FAIL(); break; }
+        tc_fence_after();
+        // O_j = P V_j : 128/UMMA_K k-steps over the keys
+#pragma unroll
+        for (int ks = 0; ks < ATTN_TILE / UMMA_K; ++ks) {
+          const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
+          const uint64_t adesc = make_smem_desc_sw128(smem_u32(sP) + chunk * ATTN_CHUNK_BYTES + off, 16, 1024);
+          // V chunk c holds head-dim columns [c*CHE, (c+1)*CHE) for all 128 keys (rows):
+          // MN-major with LBO = chunk stride (tf32: the 32-byte-atom swizzle, see make_smem_desc_mn).
+          const uint64_t bdesc = make_smem_desc_mn<kBf16>(smem_u32(sV) + ks * (UMMA_K * 128), ATTN_CHUNK_BYTES);
+          umma_ss<kBf16>(tmem_o, adesc, bdesc, IDESC_O, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_o);
+        if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
+        if (j + 1 < n_kv) {  // V buffer is free again
+          mbar_expect_tx(bar_v, Cfg::Q_BYTES);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+            tma_load_2d(sV + c * ATTN_CHUNK_BYTES, &tmap_v, bar_v, colq + c * CHE, row0 + (j + 1) * ATTN_TILE);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------- softmax / output threads
+    const int t = threadIdx.x;            // query row inside the tile, also the TMEM lane
+    const int qi = q0 + t;                // query position in its sequence
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float kLog2e = 1.4426950408889634f;
+    float o_acc[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o_acc[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float* kmask = args.key_mask ? args.key_mask + static_cast<long long>(b) * args.S : nullptr;
+    bool ok = true;
+
+    if (rope) {
+      if (mbar_wait(bar_q, 0, abort_flag)) {
+        rope_row_inplace<D, kBf16>(sQ, t, min(qi, args.S - 1), args);
+        fence_proxy_async_smem();
+        mbar_arrive(bar_rq);
+      } else { ATTN_FAIL(); ok = false; }
+    }
+
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const uint32_t ph = j & 1;
+      const int k0 = j * ATTN_TILE;
+      if (rope) {
+        if (!mbar_wait(bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
+        rope_row_inplace<D, kBf16>(sK, t, min(k0 + t, args.S - 1), args);
+        fence_proxy_async_smem();
+        mbar_arrive(bar_rk);
+      }
+      if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
+      tc_fence_after();
+
+      // ---- pass 1: row maximum of the masked, scaled scores
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < ATTN_TILE / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = k0 + c * 32 + i;
+          float s = __uint_as_float(r[i]) * args.scale;
+          if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
+          if (args.causal && kidx > qi) s = -1e9f;
+          if (kidx >= L) s = -INFINITY;
+          m_tile = fmaxf(m_tile, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float alpha = exp2f((m_run - m_new) * kLog2e);  // 0 on the first step (m_run = -inf)
+      const float m_l2 = m_new * kLog2e;
+
+      // ---- pass 2: p = exp(s - m), row sum, P -> swizzled shared memory (K-major A operand)
+      float l_tile = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < ATTN_TILE / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = k0 + c * 32 + i;
+          float s = __uint_as_float(r[i]) * args.scale;
+          if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
+          if (args.causal && kidx > qi) s = -1e9f;
+          if (kidx >= L) s = -INFINITY;
+          float e = exp2f(s * kLog2e - m_l2);
+          if constexpr (kBf16) e = __bfloat162float(__float2bfloat16(e));
+          else e = round_to_tf32(e);
+          p[i] = e;
+          l_tile += e;
+        }
+        if constexpr (kBf16) {
+          // 32 keys = 64 B = 4 pieces of 8; chunk = (c*32)/64, piece within chunk = ((c*32)%64)/8 + q
+          const int chunk = (c * 32) / CHE;
+          const int piece0 = ((c * 32) % CHE) / 8;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(p[8 * q + 0], p[8 * q + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(p[8 * q + 2], p[8 * q + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(p[8 * q + 4], p[8 * q + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(p[8 * q + 6], p[8 * q + 7]);
+            uint4 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            const int within = piece0 + q;
+            *reinterpret_cast<uint4*>(sP + chunk * ATTN_CHUNK_BYTES + t * 128 + ((within ^ (t & 7)) << 4)) = pk;
+          }
+        } else {
+          // 32 keys = 128 B = one full chunk row: 8 pieces of 4
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 pk;
+            pk.x = __float_as_uint(p[4 * q + 0]); pk.y = __float_as_uint(p[4 * q + 1]);
+            pk.z = __float_as_uint(p[4 * q + 2]); pk.w = __float_as_uint(p[4 * q + 3]);
+            *reinterpret_cast<uint4*>(sP + c * ATTN_CHUNK_BYTES + t * 128 + ((q ^ (t & 7)) << 4)) = pk;
+          }
+        }
+      }
+      fence_proxy_async_smem();   // P visible to the tensor core's reads
+      tc_fence_before();          // and this thread's TMEM reads are complete
+      mbar_arrive(bar_p);
+
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+#pragma unroll
+      for (int d = 0; d < D; ++d) o_acc[d] *= alpha;
+
+      if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+    }
+
+    if (ok && qi < L && !*abort_flag) {
+      const float inv = 1.f / l_run;
+      const long long orow = static_cast<long long>(row0 + qi) * args.ld_out + h * D;
+      if (args.out_bf16) {
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + orow;
+#pragma unroll
+        for (int d = 0; d < D; d += 2)
+          *reinterpret_cast<__nv_bfloat162*>(op + d) = __floats2bfloat162_rn(o_acc[d] * inv, o_acc[d + 1] * inv);
+      } else {
+        float* op = reinterpret_cast<float*>(args.out) + orow;
+        const bool v4 = (args.ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);
+#pragma unroll
+        for (int d = 0; d < D; d += 4) {
+          float4 q = make_float4(o_acc[d] * inv, o_acc[d + 1] * inv, o_acc[d + 2] * inv, o_acc[d + 3] * inv);
+          if (args.round_tf32) {
+            q.x = round_to_tf32(q.x); q.y = round_to_tf32(q.y); q.z = round_to_tf32(q.z); q.w = round_to_tf32(q.w);
+          }
+          if (v4) *reinterpret_cast<float4*>(op + d) = q;
+          else { op[d] = q.x; op[d + 1] = q.y; op[d + 2] = q.z; op[d + 3] = q.w; }
+        }
+      }
+    }
+  }
+#undef ATTN_FAIL
+
+  if (*abort_flag) {
+    for (int i = 0; i < 100; ++i) __nanosleep(10000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 4) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+}  // namespace gb

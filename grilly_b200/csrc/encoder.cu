@@ -1,0 +1,383 @@
+// Device-resident post-LN BERT/MiniLM sentence encoder built from the hot-path
+// kernels. Weights are uploaded once; a forward uploads token ids, runs on
+// packed (padding-free) token rows and downloads one pooled vector per sentence.
+//
+// Per layer (T = packed token rows, F = hidden):
+//   qkv  = x Wqkv^T + bqkv                      tcgen05 GEMM            [T, 3F]
+//   attn = softmax(q k^T / sqrt(d)) v           tcgen05 flash-attention [T, F]
+//   t    = attn Wo^T + bo + x                   GEMM, residual epilogue [T, F]
+//   x2   = LayerNorm(t)                         row kernel
+//   h    = gelu(x2 W1^T + b1)                   GEMM, GELU epilogue     [T, ffn]
+//   t    = h W2^T + b2 + x2                     GEMM, residual epilogue
+//   x    = LayerNorm(t)
+// Sentences are processed in chunks of at most `chunk_tokens` rows through all
+// layers, reusing one set of activation buffers, so a chunk's activations stay
+// in the 126 MB L2 between producer and consumer kernels.
+#include "internal.h"
+#include "args.h"
+#include <algorithm>
+#include <cmath>
+
+using namespace gb;
+
+struct EncLayer {
+  float *wqkv = nullptr, *bqkv = nullptr, *wo = nullptr, *bo = nullptr, *ln1_g = nullptr, *ln1_b = nullptr;
+  float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+};
+
+struct grilly_encoder {
+  grilly_ctx* ctx = nullptr;
+  grilly_encoder_config cfg{};
+  float *word = nullptr, *pos = nullptr, *type = nullptr, *emb_g = nullptr, *emb_b = nullptr;
+  std::vector<EncLayer> layers;
+  // activation workspace for one chunk
+  long long cap_rows = 0;
+  float *x = nullptr, *x2 = nullptr, *t = nullptr, *attn = nullptr, *qkv = nullptr, *h = nullptr;
+  // per-call buffers
+  int cap_B = 0, cap_S = 0;
+  int* ids_dev = nullptr;      // [B][S]
+  int* cu_dev = nullptr;       // chunk-relative row offsets, one [Bc+1] segment per chunk
+  float* out_dev = nullptr;    // [B][F]
+  int* ids_pin = nullptr;      // pinned staging
+  int* cu_pin = nullptr;
+  float* out_pin = nullptr;
+  float* mask_dev = nullptr;   // padded-layout fallback for masks that are not prefixes
+  // optional copy of the final hidden states (packed rows) for parity checks
+  bool keep_hidden = false;
+  float* hidden_all = nullptr;
+  long long hidden_cap = 0, last_rows = 0;
+  std::vector<void*> owned;
+};
+
+static int enc_alloc(grilly_encoder* e, size_t bytes, void** p) {
+  cudaError_t err = cudaMalloc(p, bytes ? bytes : 16);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(e->ctx, err == cudaErrorMemoryAllocation ? GRILLY_ERR_OOM : GRILLY_ERR_CUDA,
+                     std::string("encoder allocation: ") + cudaGetErrorString(err));
+  }
+  e->owned.push_back(*p);
+  return GRILLY_OK;
+}
+static void enc_release(grilly_encoder* e, void* p) {
+  if (!p) return;
+  cudaFree(p);
+  e->owned.erase(std::remove(e->owned.begin(), e->owned.end(), p), e->owned.end());
+}
+
+static int ensure_workspace(grilly_encoder* e, long long rows) {
+  if (rows <= e->cap_rows) return GRILLY_OK;
+  const int F = e->cfg.hidden, ffn = e->cfg.ffn;
+  float** bufs[6] = {&e->x, &e->x2, &e->t, &e->attn, &e->qkv, &e->h};
+  const long long widths[6] = {F, F, F, F, 3LL * F, ffn};
+  for (int i = 0; i < 6; ++i) {
+    enc_release(e, *bufs[i]);
+    *bufs[i] = nullptr;
+    int rc = enc_alloc(e, static_cast<size_t>(rows) * widths[i] * sizeof(float), reinterpret_cast<void**>(bufs[i]));
+    if (rc) { e->cap_rows = 0; return rc; }
+  }
+  e->cap_rows = rows;
+  return GRILLY_OK;
+}
+
+static int ensure_io(grilly_encoder* e, int B, int S) {
+  if (B <= e->cap_B && S <= e->cap_S) return GRILLY_OK;
+  const int nB = std::max(B, e->cap_B), nS = std::max(S, e->cap_S);
+  enc_release(e, e->ids_dev); enc_release(e, e->cu_dev); enc_release(e, e->out_dev); enc_release(e, e->mask_dev);
+  e->ids_dev = nullptr; e->cu_dev = nullptr; e->out_dev = nullptr; e->mask_dev = nullptr;
+  if (e->ids_pin) cudaFreeHost(e->ids_pin);
+  if (e->cu_pin) cudaFreeHost(e->cu_pin);
+  if (e->out_pin) cudaFreeHost(e->out_pin);
+  e->ids_pin = nullptr; e->cu_pin = nullptr; e->out_pin = nullptr;
+  e->cap_B = e->cap_S = 0;
+  int rc;
+  if ((rc = enc_alloc(e, static_cast<size_t>(nB) * nS * sizeof(int), reinterpret_cast<void**>(&e->ids_dev)))) return rc;
+  if ((rc = enc_alloc(e, static_cast<size_t>(2 * nB + 2) * sizeof(int), reinterpret_cast<void**>(&e->cu_dev)))) return rc;
+  if ((rc = enc_alloc(e, static_cast<size_t>(nB) * e->cfg.hidden * sizeof(float), reinterpret_cast<void**>(&e->out_dev)))) return rc;
+  GB_CUDA_CHECK(e->ctx, cudaMallocHost(&e->ids_pin, static_cast<size_t>(nB) * nS * sizeof(int)));
+  GB_CUDA_CHECK(e->ctx, cudaMallocHost(&e->cu_pin, static_cast<size_t>(2 * nB + 2) * sizeof(int)));
+  GB_CUDA_CHECK(e->ctx, cudaMallocHost(&e->out_pin, static_cast<size_t>(nB) * e->cfg.hidden * sizeof(float)));
+  e->cap_B = nB; e->cap_S = nS;
+  return GRILLY_OK;
+}
+
+static int enc_linear(grilly_encoder* e, const float* x, const float* w, const float* bias, const float* residual, float* y,
+                      int M, int N, int K, int act) {
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K;
+  a.bias = bias; a.residual = residual; a.ld_res = N;
+  a.out = y; a.ld_out = N;
+  a.act = act;
+  a.round_tf32 = residual ? 0 : 1;  // outputs that feed an MMA directly are rounded; pre-LayerNorm sums stay fp32
+  return launch_gemm(e->ctx, false, false, x, w, a, 0);
+}
+
+static int enc_norm(grilly_encoder* e, const float* x, const float* g, const float* b, float* y, int rows) {
+  NormArgs n{};
+  n.x = x; n.gamma = g; n.beta = b; n.y = y; n.rows = rows; n.F = e->cfg.hidden; n.eps = e->cfg.layer_ln_eps;
+  n.mode = NORM_LAYER; n.round_tf32 = 1;
+  return launch_norm(e->ctx, n);
+}
+
+// Runs one chunk: sequences [b0, b1) whose packed rows are [0, rows) of the workspace.
+static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_dev, int b0, int b1, int S, int rows,
+                     int max_len, float* out_dev, long long hidden_row0) {
+  grilly_ctx* ctx = e->ctx;
+  const auto& c = e->cfg;
+  const int F = c.hidden, H = c.num_heads, D = F / H, Bc = b1 - b0;
+  int rc;
+  EmbedArgs em{};
+  em.ids = ids_dev + static_cast<long long>(b0) * S; em.cu_seqlens = cu_chunk_dev; em.word = e->word; em.pos = e->pos;
+  em.type0 = c.has_token_type ? e->type : nullptr; em.gamma = e->emb_g; em.beta = e->emb_b; em.out = e->x;
+  em.B = Bc; em.S = S; em.F = F; em.vocab = c.vocab; em.max_pos = c.max_pos; em.eps = c.embed_ln_eps; em.round_tf32 = 1;
+  if ((rc = launch_embed(ctx, em))) return rc;
+  for (int l = 0; l < c.num_layers; ++l) {
+    const EncLayer& L = e->layers[l];
+    if ((rc = enc_linear(e, e->x, L.wqkv, L.bqkv, nullptr, e->qkv, rows, 3 * F, F, ACT_NONE))) return rc;
+    AttnArgs at{};
+    at.B = Bc; at.S = max_len; at.H = H; at.D = D; at.cu_seqlens = cu_chunk_dev; at.scale = 1.0f / sqrtf(static_cast<float>(D));
+    at.out = e->attn; at.ld_out = F; at.round_tf32 = 1;
+    if ((rc = launch_attention(ctx, false, e->qkv, e->qkv + F, e->qkv + 2 * F, 3LL * F, rows, at))) return rc;
+    if ((rc = enc_linear(e, e->attn, L.wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE))) return rc;
+    if ((rc = enc_norm(e, e->t, L.ln1_g, L.ln1_b, e->x2, rows))) return rc;
+    if ((rc = enc_linear(e, e->x2, L.w1, L.b1, nullptr, e->h, rows, c.ffn, F, ACT_GELU_TANH))) return rc;
+    if ((rc = enc_linear(e, e->h, L.w2, L.b2, e->x2, e->t, rows, F, c.ffn, ACT_NONE))) return rc;
+    if ((rc = enc_norm(e, e->t, L.ln2_g, L.ln2_b, e->x, rows))) return rc;
+  }
+  PoolArgs p{};
+  p.x = e->x; p.cu_seqlens = cu_chunk_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
+  if ((rc = launch_pool(ctx, p))) return rc;
+  if (e->keep_hidden && e->hidden_all)
+    GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->hidden_all + hidden_row0 * F, e->x, static_cast<size_t>(rows) * F * sizeof(float),
+                                       cudaMemcpyDeviceToDevice, ctx->stream));
+  return GRILLY_OK;
+}
+
+struct ChunkPlan { int b0, b1, rows, max_len, cu_off; };
+
+// Splits the batch into chunks of consecutive sentences and writes chunk-relative row offsets to cu_host.
+static void plan_chunks(const int* lengths, int B, int chunk_tokens, std::vector<ChunkPlan>& plan, int* cu_host, long long* total) {
+  plan.clear();
+  long long tot = 0;
+  int b = 0, off = 0;
+  while (b < B) {
+    ChunkPlan c{b, b, 0, 0, off};
+    cu_host[off] = 0;
+    while (c.b1 < B) {
+      const int len = lengths[c.b1];
+      if (chunk_tokens > 0 && c.b1 > c.b0 && c.rows + len > chunk_tokens) break;
+      c.rows += len;
+      c.max_len = std::max(c.max_len, len);
+      c.b1++;
+      cu_host[off + (c.b1 - c.b0)] = c.rows;
+    }
+    off += (c.b1 - c.b0) + 1;
+    tot += c.rows;
+    b = c.b1;
+    plan.push_back(c);
+  }
+  *total = tot;
+}
+
+static int forward_device_nolock(grilly_encoder* e, const int* ids_dev, const int* lengths, int B, int S, float* out_dev,
+                                 int* cu_host_staging) {
+  grilly_ctx* ctx = e->ctx;
+  if (S > e->cfg.max_pos) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sequence length exceeds the position table");
+  for (int b = 0; b < B; ++b)
+    if (lengths[b] < 0 || lengths[b] > S) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: a valid length is outside [0, S]");
+  std::vector<ChunkPlan> plan;
+  long long total = 0;
+  plan_chunks(lengths, B, e->cfg.chunk_tokens, plan, cu_host_staging, &total);
+  int max_rows = 1;
+  for (auto& c : plan) max_rows = std::max(max_rows, c.rows);
+  int rc = ensure_workspace(e, max_rows);
+  if (rc) return rc;
+  if (e->keep_hidden && total > e->hidden_cap) {
+    enc_release(e, e->hidden_all);
+    e->hidden_all = nullptr;
+    if ((rc = enc_alloc(e, static_cast<size_t>(total) * e->cfg.hidden * sizeof(float), reinterpret_cast<void**>(&e->hidden_all)))) return rc;
+    e->hidden_cap = total;
+  }
+  const int n_cu = plan.back().cu_off + (plan.back().b1 - plan.back().b0) + 1;
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->cu_dev, cu_host_staging, static_cast<size_t>(n_cu) * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+  long long row0 = 0;
+  for (auto& c : plan) {
+    if (c.rows == 0) {
+      // only empty sentences: their pooled vectors are zero
+      GB_CUDA_CHECK(ctx, cudaMemsetAsync(out_dev + static_cast<long long>(c.b0) * e->cfg.hidden, 0,
+                                         static_cast<size_t>(c.b1 - c.b0) * e->cfg.hidden * sizeof(float), ctx->stream));
+      continue;
+    }
+    if ((rc = run_chunk(e, ids_dev, e->cu_dev + c.cu_off, c.b0, c.b1, S, c.rows, std::max(c.max_len, 1), out_dev, row0))) return rc;
+    row0 += c.rows;
+  }
+  e->last_rows = total;
+  return GRILLY_OK;
+}
+
+extern "C" {
+
+int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, grilly_encoder** out) {
+  if (!ctx || !cfg || !out) return GRILLY_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  *out = nullptr;
+  if (cfg->precision != GRILLY_PREC_TF32) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: only GRILLY_PREC_TF32 is implemented");
+  if (cfg->num_layers <= 0 || cfg->hidden <= 0 || cfg->num_heads <= 0 || cfg->ffn <= 0 || cfg->vocab <= 0 || cfg->max_pos <= 0)
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sizes must be positive");
+  if (cfg->hidden % cfg->num_heads) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: hidden must be divisible by num_heads");
+  const int D = cfg->hidden / cfg->num_heads;
+  if (D != 32 && D != 64) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: head_dim must be 32 or 64");
+  if (cfg->hidden % 4 || cfg->ffn % 4 || cfg->hidden > 1024) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: hidden and ffn must be multiples of 4, hidden at most 1024");
+  cudaSetDevice(ctx->device);
+  grilly_encoder* e = new grilly_encoder();
+  e->ctx = ctx;
+  e->cfg = *cfg;
+  e->layers.resize(cfg->num_layers);
+  const size_t F = cfg->hidden, ffn = cfg->ffn;
+  int rc = 0;
+  auto A = [&](float** p, size_t n) { if (!rc) rc = enc_alloc(e, n * sizeof(float), reinterpret_cast<void**>(p)); };
+  A(&e->word, static_cast<size_t>(cfg->vocab) * F); A(&e->pos, static_cast<size_t>(cfg->max_pos) * F); A(&e->type, 2 * F);
+  A(&e->emb_g, F); A(&e->emb_b, F);
+  for (auto& L : e->layers) {
+    A(&L.wqkv, 3 * F * F); A(&L.bqkv, 3 * F); A(&L.wo, F * F); A(&L.bo, F); A(&L.ln1_g, F); A(&L.ln1_b, F);
+    A(&L.w1, ffn * F); A(&L.b1, ffn); A(&L.w2, F * ffn); A(&L.b2, F); A(&L.ln2_g, F); A(&L.ln2_b, F);
+  }
+  if (rc) {
+    for (void* p : e->owned) cudaFree(p);
+    delete e;
+    return rc;
+  }
+  *out = e;
+  return GRILLY_OK;
+}
+
+int grilly_encoder_set_weight(grilly_encoder* e, const char* name, int layer, const float* data, size_t count) {
+  if (!e || !name || !data) return GRILLY_ERR_INVALID_ARG;
+  grilly_ctx* ctx = e->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  cudaSetDevice(ctx->device);
+  const size_t F = e->cfg.hidden, ffn = e->cfg.ffn;
+  float* dst = nullptr;
+  size_t expect = 0;
+  bool is_gemm_weight = false;
+  const std::string n(name);
+  if (layer < 0) {
+    if (n == "word") { dst = e->word; expect = static_cast<size_t>(e->cfg.vocab) * F; }
+    else if (n == "pos") { dst = e->pos; expect = static_cast<size_t>(e->cfg.max_pos) * F; }
+    else if (n == "type") { dst = e->type; expect = 2 * F; }
+    else if (n == "emb_ln_g") { dst = e->emb_g; expect = F; }
+    else if (n == "emb_ln_b") { dst = e->emb_b; expect = F; }
+  } else if (layer < e->cfg.num_layers) {
+    EncLayer& L = e->layers[layer];
+    if (n == "wqkv") { dst = L.wqkv; expect = 3 * F * F; is_gemm_weight = true; }
+    else if (n == "bqkv") { dst = L.bqkv; expect = 3 * F; }
+    else if (n == "wo") { dst = L.wo; expect = F * F; is_gemm_weight = true; }
+    else if (n == "bo") { dst = L.bo; expect = F; }
+    else if (n == "ln1_g") { dst = L.ln1_g; expect = F; }
+    else if (n == "ln1_b") { dst = L.ln1_b; expect = F; }
+    else if (n == "w1") { dst = L.w1; expect = ffn * F; is_gemm_weight = true; }
+    else if (n == "b1") { dst = L.b1; expect = ffn; }
+    else if (n == "w2") { dst = L.w2; expect = F * ffn; is_gemm_weight = true; }
+    else if (n == "b2") { dst = L.b2; expect = F; }
+    else if (n == "ln2_g") { dst = L.ln2_g; expect = F; }
+    else if (n == "ln2_b") { dst = L.ln2_b; expect = F; }
+  }
+  if (!dst) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_set_weight: unknown weight name '" + n + "' or layer");
+  if (count != expect) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_set_weight: '" + n + "' expects " + std::to_string(expect) + " values");
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, data, count * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  int rc = GRILLY_OK;
+  // GEMM weights are consumed as tf32: round them to nearest once here instead of letting the MMA truncate
+  if (is_gemm_weight) rc = launch_round_tf32(ctx, dst, dst, static_cast<long long>(count));
+  GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));  // the host array may be freed by the caller
+  return rc;
+}
+
+int grilly_encoder_keep_hidden(grilly_encoder* e, int on) {
+  if (!e) return GRILLY_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(e->ctx->mu);
+  e->keep_hidden = on != 0;
+  return GRILLY_OK;
+}
+
+int grilly_encoder_forward_device(grilly_encoder* e, const int* ids_dev, const int* lengths_host, int B, int S, float* out_dev) {
+  if (!e) return GRILLY_ERR_INVALID_ARG;
+  grilly_ctx* ctx = e->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  cudaSetDevice(ctx->device);
+  if (!ids_dev || !lengths_host || !out_dev || B <= 0 || S <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_forward_device: bad arguments");
+  int rc = ensure_io(e, B, S);
+  if (rc) return rc;
+  // the staging array is reused by the next call: wait for the previous upload of it to finish
+  GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+  return forward_device_nolock(e, ids_dev, lengths_host, B, S, out_dev, e->cu_pin);
+}
+
+int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* mask_host, int B, int S, float* out_host) {
+  if (!e) return GRILLY_ERR_INVALID_ARG;
+  grilly_ctx* ctx = e->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  cudaSetDevice(ctx->device);
+  if (!ids_host || !out_host || B <= 0 || S <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_forward: bad arguments");
+  int rc = ensure_io(e, B, S);
+  if (rc) return rc;
+  // valid lengths from the mask; the packed path needs every mask row to be a prefix of ones
+  std::vector<int> lengths(B);
+  for (int b = 0; b < B; ++b) {
+    int len = S;
+    if (mask_host) {
+      const float* m = mask_host + static_cast<size_t>(b) * S;
+      len = 0;
+      while (len < S && m[len] > 0.5f) ++len;
+      for (int s = len; s < S; ++s)
+        if (m[s] > 0.5f) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder_forward: attention_mask rows must be a run of ones followed by zeros");
+    }
+    lengths[b] = len;
+  }
+  const size_t n_ids = static_cast<size_t>(B) * S;
+  std::memcpy(e->ids_pin, ids_host, n_ids * sizeof(int));
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->ids_dev, e->ids_pin, n_ids * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+  if ((rc = forward_device_nolock(e, e->ids_dev, lengths.data(), B, S, e->out_dev, e->cu_pin))) return rc;
+  const size_t out_bytes = static_cast<size_t>(B) * e->cfg.hidden * sizeof(float);
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->out_pin, e->out_dev, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->err_host, ctx->err_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+  if (*ctx->err_host != 0) {
+    const int code = *ctx->err_host;
+    *ctx->err_host = 0;
+    cudaMemsetAsync(ctx->err_dev, 0, sizeof(int), ctx->stream);
+    return set_error(ctx, GRILLY_ERR_TIMEOUT, "a device-side wait gave up (kernel status " + std::to_string(code) + ")");
+  }
+  std::memcpy(out_host, e->out_pin, out_bytes);
+  return GRILLY_OK;
+}
+
+int grilly_encoder_last_hidden(grilly_encoder* e, float* out_host, long long max_rows, long long* rows) {
+  if (!e || !rows) return GRILLY_ERR_INVALID_ARG;
+  grilly_ctx* ctx = e->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  cudaSetDevice(ctx->device);
+  if (!e->keep_hidden || !e->hidden_all) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_last_hidden: enable grilly_encoder_keep_hidden before the forward");
+  *rows = e->last_rows;
+  if (!out_host) return GRILLY_OK;
+  const long long n = std::min(max_rows, e->last_rows);
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(out_host, e->hidden_all, static_cast<size_t>(n) * e->cfg.hidden * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+  return GRILLY_OK;
+}
+
+int grilly_encoder_destroy(grilly_encoder* e) {
+  if (!e) return GRILLY_ERR_INVALID_ARG;
+  {
+    std::lock_guard<std::mutex> lock(e->ctx->mu);
+    cudaSetDevice(e->ctx->device);
+    cudaStreamSynchronize(e->ctx->stream);
+    for (void* p : e->owned) cudaFree(p);
+    if (e->ids_pin) cudaFreeHost(e->ids_pin);
+    if (e->cu_pin) cudaFreeHost(e->cu_pin);
+    if (e->out_pin) cudaFreeHost(e->out_pin);
+  }
+  delete e;
+  return GRILLY_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,105 @@
+// Host-side internals shared by the translation units of libgrilly_b200.so:
+// the context (device, stream, stream-ordered pool, tensor-map cache, status
+// word) and the kernel launchers.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/grilly_b200.h"
+
+struct TmapKey {
+  const void* ptr;
+  uint64_t inner, outer, stride_bytes;
+  uint32_t box_inner, box_outer;
+  int dtype;
+  int swizzle;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && stride_bytes == o.stride_bytes &&
+           box_inner == o.box_inner && box_outer == o.box_outer && dtype == o.dtype && swizzle == o.swizzle;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.ptr);
+    auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.inner); mix(k.outer); mix(k.stride_bytes); mix(k.box_inner); mix(k.box_outer); mix(static_cast<uint64_t>(k.dtype)); mix(static_cast<uint64_t>(k.swizzle));
+    return static_cast<size_t>(h);
+  }
+};
+
+struct grilly_ctx {
+  int device = 0;
+  int num_sms = 148;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaMemPool_t pool = nullptr;
+  int* err_dev = nullptr;       // device status word written by bounded waits
+  int* err_host = nullptr;      // pinned mirror
+  std::mutex mu;
+  std::string last_error;
+  // pool statistics
+  uint64_t n_alloc = 0, n_free = 0, bytes_in_use = 0, peak_bytes = 0;
+  std::unordered_map<void*, size_t> live;
+  // tensor-map cache
+  std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> tmaps;
+  uint64_t tmap_hits = 0, tmap_misses = 0;
+  uint64_t launches = 0;
+  std::unordered_set<const void*> smem_attr_done;  // kernels whose dynamic-smem limit is already raised
+  // RoPE tables, keyed by (S, D, base, scaling)
+  struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };
+  std::vector<RopeTable> rope_tables;
+};
+
+namespace gb {
+
+int set_error(grilly_ctx* ctx, int code, const std::string& msg);
+#define GB_CUDA_CHECK(ctx, expr)                                                                  \
+  do {                                                                                            \
+    cudaError_t e__ = (expr);                                                                     \
+    if (e__ != cudaSuccess)                                                                       \
+      return gb::set_error(ctx, e__ == cudaErrorMemoryAllocation ? GRILLY_ERR_OOM : GRILLY_ERR_CUDA, \
+                           std::string(#expr) + ": " + cudaGetErrorString(e__));                  \
+  } while (0)
+
+enum { TM_F32 = 0, TM_BF16 = 1 };
+enum { TM_SW128 = 0, TM_SW128_ATOM32 = 1 };  // 128-byte swizzle of 16-byte chunks, or of 32-byte chunks (tf32 MN-major)
+// 2-D row-major tensor [outer][inner] with a row pitch, 128-byte swizzle, zero fill out of bounds.
+int get_tmap_2d(grilly_ctx* ctx, int dtype, const void* ptr, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
+                uint32_t box_inner, uint32_t box_outer, CUtensorMap* out, int swizzle = TM_SW128);
+
+struct GemmArgs;
+struct AttnArgs;
+struct NormArgs;
+struct EmbedArgs;
+struct PoolArgs;
+
+// gemm.cu
+int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, const void* b, GemmArgs& args, int force_bn);
+// attention.cu
+int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_qkv,
+                     long long total_rows, AttnArgs& args);
+// rowops.cu
+int launch_norm(grilly_ctx* ctx, const NormArgs& a);
+int launch_softmax(grilly_ctx* ctx, const float* x, float* y, long long rows, int cols);
+int launch_eltwise(grilly_ctx* ctx, int op, const float* a, const float* b, float* y, long long n, int half);
+int launch_round_tf32(grilly_ctx* ctx, const float* x, float* y, long long n);
+int launch_f32_to_bf16(grilly_ctx* ctx, const float* x, void* y, long long n);
+int launch_bf16_to_f32(grilly_ctx* ctx, const void* x, float* y, long long n);
+int launch_gather(grilly_ctx* ctx, const int* ids, const float* table, float* out, long long n, int vocab, int F);
+int launch_embed(grilly_ctx* ctx, const EmbedArgs& a);
+int launch_pool(grilly_ctx* ctx, const PoolArgs& a);
+int launch_fold_ln(grilly_ctx* ctx, const float* w, const float* gamma, const float* beta, const float* bias, void* wf,
+                   float* col_sum, float* bias_f, int N, int K, bool bf16);
+int get_rope_table(grilly_ctx* ctx, int S, int D, float base, float scaling, const float** cos_t, const float** sin_t);
+int launch_rope_apply(grilly_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,
+                      const int* position_ids, int B, int S, int H, int D, int style);
+
+}  // namespace gb

@@ -1,0 +1,188 @@
+/*
+ * grilly_b200 -- C ABI of the CUDA (sm_100a) implementation of grilly's dense
+ * transformer hot path.  Plain pointers and sizes only; every function returns
+ * a status code (0 = GRILLY_OK, negative = error) and grilly_last_error() gives
+ * the message.  Pointers named *_dev are device addresses on the context's GPU;
+ * pointers named *_host are host addresses.  All work is issued on the
+ * context's stream; calls taking host output buffers return after the data has
+ * arrived, the others are asynchronous until grilly_sync().
+ *
+ * File:line citations name the reference (grilly 0.1.0) interface each entry
+ * point replaces; paths are relative to the reference's project root.
+ */
+#ifndef GRILLY_B200_H
+#define GRILLY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct grilly_ctx grilly_ctx;
+typedef struct grilly_encoder grilly_encoder;
+
+enum {
+  GRILLY_OK = 0,
+  GRILLY_ERR_INVALID_ARG = -1,
+  GRILLY_ERR_OOM = -2,
+  GRILLY_ERR_CUDA = -3,
+  GRILLY_ERR_NCCL = -4,
+  GRILLY_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up */
+  GRILLY_ERR_UNSUPPORTED = -6
+};
+
+enum { GRILLY_PREC_TF32 = 0, GRILLY_PREC_BF16 = 1 };
+enum { GRILLY_ACT_NONE = 0, GRILLY_ACT_GELU = 1, GRILLY_ACT_SILU = 2, GRILLY_ACT_RELU = 3 };
+enum { GRILLY_NORM_LAYER = 0, GRILLY_NORM_RMS = 1 };
+enum { GRILLY_ELT_GELU = 1, GRILLY_ELT_SILU = 2, GRILLY_ELT_RELU = 3, GRILLY_ELT_ADD = 4, GRILLY_ELT_SWIGLU = 5 };
+enum { GRILLY_ROPE_NONE = 0, GRILLY_ROPE_INTERLEAVED = 1, GRILLY_ROPE_ROTATE_HALF = 2 };
+
+/* flags for the GEMM family, attention and the norms */
+enum {
+  GRILLY_FLAG_OUT_BF16 = 1,     /* store the result as bf16 instead of fp32 */
+  GRILLY_FLAG_ROUND_TF32 = 2,   /* round fp32 results to the nearest tf32 value (they feed a tf32 GEMM next) */
+  GRILLY_FLAG_SWIGLU_PAIRS = 4  /* weight rows interleaved (gate_j, up_j): y[:, j] = gate_j * silu(up_j), N/2 columns out */
+};
+
+/* ---- context, replaces VulkanCore (backend/core.py:14-439) ------------------------------- */
+int grilly_device_count(int* count);
+/* backend/core.py:17-33,57-166: instance + device + queue creation -> one context per (process, GPU) */
+int grilly_init(int device, grilly_ctx** ctx);
+/* backend/core.py:423-439 cleanup(), backend/compute.py:56-68 */
+int grilly_shutdown(grilly_ctx* ctx);
+const char* grilly_last_error(grilly_ctx* ctx);
+/* run on a caller-owned CUDA stream (e.g. torch's current stream); NULL restores the context's own stream */
+int grilly_set_stream(grilly_ctx* ctx, void* cuda_stream);
+/* backend/core.py:417-418 vkQueueWaitIdle; also reports a device-side wait that gave up as GRILLY_ERR_TIMEOUT */
+int grilly_sync(grilly_ctx* ctx);
+/* number of kernels this context has launched (monotonic) */
+int grilly_launch_count(grilly_ctx* ctx, uint64_t* count);
+
+/* ---- device pool, replaces BufferPool / VMABufferPool (backend/buffer_pool.py:466-651, 120-462;
+ *      backend/vma_wrapper.py:268-437) with a stream-ordered cudaMallocAsync pool ------------- */
+/* backend/buffer_pool.py:534-562 acquire() */
+int grilly_alloc(grilly_ctx* ctx, size_t bytes, void** dptr);
+/* backend/buffer_pool.py:564-579 release() */
+int grilly_free(grilly_ctx* ctx, void* dptr);
+/* backend/core.py:345-350 _upload_buffer */
+int grilly_upload(grilly_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+/* backend/core.py:352-360 _download_buffer (returns after the copy has completed) */
+int grilly_download(grilly_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+/* pinned host staging memory for the two calls above */
+int grilly_host_alloc(grilly_ctx* ctx, size_t bytes, void** hptr);
+int grilly_host_free(grilly_ctx* ctx, void* hptr);
+/* backend/buffer_pool.py:627-640 get_stats(): out[0]=allocs out[1]=frees out[2]=bytes_in_use
+ * out[3]=peak_bytes out[4]=pool_reserved_bytes out[5]=tensor_map_cache_hits out[6]=tensor_map_cache_misses out[7]=0 */
+int grilly_pool_stats(grilly_ctx* ctx, uint64_t out[8]);
+
+/* ---- conversions used when operands enter from NumPy ------------------------------------ */
+int grilly_round_tf32(grilly_ctx* ctx, const float* x_dev, float* y_dev, long long n);
+int grilly_cast_f32_to_bf16(grilly_ctx* ctx, const float* x_dev, void* y_dev, long long n);
+int grilly_cast_bf16_to_f32(grilly_ctx* ctx, const void* x_dev, float* y_dev, long long n);
+
+/* ---- GEMM family ------------------------------------------------------------------------- */
+/* y[M,N] = act(x[M,K] * W[N,K]^T + bias) (+ residual).  W is (out, in) row-major.
+ * VulkanFNN.linear backend/fnn.py:1394-1496 (shader fnn-linear.glsl:33-58);
+ * fused_linear_gelu/relu/silu backend/fnn.py:2022-2303 (fused-linear-{gelu,relu,silu}.glsl);
+ * GRILLY_FLAG_SWIGLU_PAIRS: fused-swiglu.glsl:48-79, backend/_glu_append.py:47-60.
+ * x and W are fp32 (precision TF32) or bf16 (precision BF16); bias and residual are fp32. */
+int grilly_linear(grilly_ctx* ctx, const void* x_dev, const void* w_dev, const float* bias_dev,
+                  const float* residual_dev, void* y_dev, int M, int N, int K, int act, int precision, int flags);
+/* QKV = x * [Wq;Wk;Wv]^T + [bq;bk;bv], output (rows, 3*H*D) with column blocks Q,K,V.
+ * fused-qkv-projection.glsl:48-74 (no Python wrapper in the reference). */
+int grilly_fused_qkv_projection(grilly_ctx* ctx, const void* x_dev, const void* w_qkv_dev, const float* b_qkv_dev,
+                                void* qkv_dev, int rows, int hidden, int num_heads, int head_dim, int precision,
+                                int flags);
+/* One-time fold for the call below: Wf = W * diag(gamma), col_sum[c] = sum_k Wf[c,k] (of the tf32/bf16-rounded
+ * values the GEMM will consume), bias_f = bias + W * beta.  Outputs: wf_dev (N*K, fp32 or bf16), col_sum_dev (N),
+ * bias_f_dev (N). */
+int grilly_fold_layernorm_weights(grilly_ctx* ctx, const float* w_dev, const float* gamma_dev, const float* beta_dev,
+                                  const float* bias_dev, void* wf_dev, float* col_sum_dev, float* bias_f_dev, int N,
+                                  int K, int precision);
+/* y = Linear(Norm(x)): row statistics kernel + GEMM with the normalisation finished in the epilogue.
+ * fused-layernorm-linear.glsl:67-128 (mode GRILLY_NORM_LAYER); snn-rmsnorm.glsl:34-75 then fnn-linear (GRILLY_NORM_RMS).
+ * x fp32 [M,K]; stats_dev is scratch for 2*M floats (mean, rstd). */
+int grilly_layernorm_linear(grilly_ctx* ctx, const float* x_dev, const void* wf_dev, const float* col_sum_dev,
+                            const float* bias_f_dev, void* y_dev, float* stats_dev, int M, int N, int K, float eps,
+                            int norm_mode, int act, int precision, int flags);
+/* C[M,N] = A[M,K] * B[K,N], all row-major.  VulkanFNN.gemm backend/fnn.py:104-166 (gemm_mnk.glsl:35-88). */
+int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int M, int K, int N,
+                    int precision, int flags);
+
+/* ---- attention --------------------------------------------------------------------------- */
+/* out = softmax(scale * Q K^T + mask) V per (sequence, head); Q/K/V/out are 2-D row-major views
+ * [rows][ld] with head h in columns [h*D, (h+1)*D)  (the (B,S,H,D) layout of
+ * VulkanAttention.flash_attention2 backend/attention.py:361-597, flash-attention2.glsl:81-219;
+ * RoPE variant flash-attention2-rope.glsl:74-149,165-247; rotate-half pairing rope.glsl:52-126).
+ * cu_seqlens_dev == NULL: padded layout, sequence b = rows [b*S,(b+1)*S), optional key_mask_dev [B][S] (1 = keep).
+ * cu_seqlens_dev != NULL: packed layout, int32 [B+1] row offsets, S = longest sequence, total_rows = cu_seqlens[B].
+ * Causal rule: key position > query position is masked (attention-mask.glsl:42-46). */
+int grilly_flash_attention(grilly_ctx* ctx, const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
+                           int B, int S, int H, int D, long long ld_qkv, long long ld_out, const int* cu_seqlens_dev,
+                           long long total_rows, const float* key_mask_dev, float scale, int causal, int rope_style,
+                           float rope_base, float rope_scaling, int precision, int flags);
+/* stand-alone RoPE on (B,S,H,D) fp32, VulkanAttention.apply_rope backend/attention.py:599-676 (rope.glsl:52-126);
+ * position_ids_dev int32 [B][S] or NULL for 0..S-1; max_pos = number of table rows to build. */
+int grilly_apply_rope(grilly_ctx* ctx, const float* x_dev, float* y_dev, const int* position_ids_dev, int B, int S,
+                      int H, int D, int max_pos, float base, float scaling, int rope_style);
+
+/* ---- row kernels ------------------------------------------------------------------------- */
+/* y = Norm(x (+ residual)); VulkanFNN.layernorm backend/fnn.py:1285-1389 (fnn-layernorm.glsl:44-103);
+ * RMS mode snn-rmsnorm.glsl:34-75.  gamma/beta may be NULL. */
+int grilly_layernorm(grilly_ctx* ctx, const float* x_dev, const float* residual_dev, const float* gamma_dev,
+                     const float* beta_dev, void* y_dev, long long rows, int F, float eps, int norm_mode, int flags);
+/* VulkanFNN.activation_softmax backend/fnn.py:574-663 (activation-softmax.glsl:34-84) */
+int grilly_softmax(grilly_ctx* ctx, const float* x_dev, float* y_dev, long long rows, int cols);
+/* activation_gelu/silu/relu, residual, activation_swiglu: backend/fnn.py:232-572,1950-2014
+ * (activation-{gelu,silu,relu,swiglu}.glsl, fnn-residual.glsl).  n = number of OUTPUT elements;
+ * half = output width for GRILLY_ELT_SWIGLU (input rows are 2*half wide). */
+int grilly_eltwise(grilly_ctx* ctx, int op, const float* a_dev, const float* b_dev, float* y_dev, long long n,
+                   int half);
+/* VulkanLearning.embedding_lookup backend/learning.py:811-877 (embedding-lookup.glsl:28-55) */
+int grilly_embedding_lookup(grilly_ctx* ctx, const int* ids_dev, const float* table_dev, float* out_dev,
+                            long long n_tokens, int vocab, int F);
+/* word[id] + type[0] + pos[s] -> LayerNorm, written to padded rows (cu_seqlens_dev NULL) or packed rows.
+ * utils/vulkan_sentence_transformer.py:563-747 */
+int grilly_embed_layernorm(grilly_ctx* ctx, const int* ids_dev, const int* cu_seqlens_dev, const float* word_dev,
+                           const float* pos_dev, const float* type0_dev, const float* gamma_dev, const float* beta_dev,
+                           float* out_dev, int B, int S, int F, int vocab, int max_pos, float eps, int flags);
+/* masked mean over tokens then optional x/(||x||+1e-8): VulkanPooling.mean_pool backend/pooling.py:22-142
+ * (embedding-pool.glsl:61-81) + functional.embedding_normalize functional/embedding.py:42-68 */
+int grilly_mean_pool(grilly_ctx* ctx, const float* x_dev, const float* mask_dev, const int* cu_seqlens_dev,
+                     float* out_dev, int B, int S, int F, int normalize);
+
+/* ---- resident sentence encoder (post-LN BERT / MiniLM shape) ------------------------------ */
+/* VulkanSentenceTransformer.encode utils/vulkan_sentence_transformer.py:1109-1219 with the BERT branch of
+ * _forward_layer :972-1033; weights live on the device between calls. */
+typedef struct grilly_encoder_config {
+  int num_layers, hidden, num_heads, ffn, vocab, max_pos;
+  float embed_ln_eps, layer_ln_eps;
+  int has_token_type;   /* add token-type row 0 (BERT) */
+  int precision;        /* GRILLY_PREC_TF32 or GRILLY_PREC_BF16 */
+  int chunk_tokens;     /* process at most this many tokens at once so activations stay L2-resident; 0 = all */
+} grilly_encoder_config;
+
+int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, grilly_encoder** enc);
+/* name in {word, pos, type, emb_ln_g, emb_ln_b} (layer = -1) or {wqkv, bqkv, wo, bo, ln1_g, ln1_b, w1, b1, w2, b2,
+ * ln2_g, ln2_b} (layer >= 0); data are fp32 host arrays in the reference's (out, in) layout. */
+int grilly_encoder_set_weight(grilly_encoder* enc, const char* name, int layer, const float* data_host, size_t count);
+/* ids_host int32 [B][S]; mask_host fp32 [B][S] (1 = token, 0 = padding) or NULL; out_host fp32 [B][hidden]:
+ * mean-pooled, L2-normalised embeddings.  Includes the host->device and device->host copies. */
+int grilly_encoder_forward(grilly_encoder* enc, const int* ids_host, const float* mask_host, int B, int S,
+                           float* out_host);
+/* same with device buffers and no copies: ids_dev int32 [B][S], lengths_host int32 [B] valid prefix lengths,
+ * out_dev fp32 [B][hidden].  Asynchronous. */
+int grilly_encoder_forward_device(grilly_encoder* enc, const int* ids_dev, const int* lengths_host, int B, int S,
+                                  float* out_dev);
+/* keep a copy of the final hidden states of each forward (off by default; costs one device copy per chunk) */
+int grilly_encoder_keep_hidden(grilly_encoder* enc, int on);
+/* final hidden states of the last forward (packed rows, fp32 [total_tokens][hidden]) for parity checks */
+int grilly_encoder_last_hidden(grilly_encoder* enc, float* out_host, long long max_rows, long long* rows);
+int grilly_encoder_destroy(grilly_encoder* enc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRILLY_B200_H */

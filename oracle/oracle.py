@@ -1,0 +1,299 @@
+"""CPU oracle: a NumPy restatement of grilly's CPU code paths for the dense transformer hot path.
+
+TEST INFRASTRUCTURE ONLY. Nothing in the shipped package imports this module; it is used by
+tests/, by __graft_entry__.smoke() and by bench.py's CPU-baseline leg as the checker / reported
+baseline, never as a compute path of the product.
+
+Parity pin: every function below is checked against outputs of the reference's own Python code
+(imported from its source tree) stored in tests/golden/*.npz by tests/golden/make_golden.py, and
+against the known-answer assertions of the reference's test-suite (tests/test_gpu_operations.py:100-205,
+tests/test_gemm_backward.py:68-76) in tests/test_oracle_golden.py.
+
+Citations are file:line in the reference (grilly 0.1.0), relative to its project root.
+All functions take and return float32 unless stated; accumulation is done in float64 and cast, so
+the oracle is a tighter statement of the maths than the reference's fastmath numba kernels.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+F32 = np.float32
+SQRT_2_OVER_PI = 0.7978845608028654
+
+
+# --------------------------------------------------------------------------- GEMM family
+def linear(x, weights, bias=None):
+    """y = x @ W.T + b with W (out, in): backend/fnn.py:1394-1416, utils/numba_ops.py:203-281,
+    shader fnn-linear.glsl:43-57."""
+    x = np.asarray(x, dtype=F32)
+    w = np.asarray(weights, dtype=F32)
+    y = x.astype(np.float64) @ w.astype(np.float64).T
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64)
+    return y.astype(F32)
+
+
+def gelu(x):
+    """tanh-approximation GELU: utils/numba_ops.py:300-306, backend/fnn.py:292-294,
+    fused-linear-gelu.glsl:42-62 (the shader's +-50 clamp never changes a float32 result)."""
+    x = np.asarray(x, dtype=np.float64)
+    return (0.5 * x * (1.0 + np.tanh(SQRT_2_OVER_PI * (x + 0.044715 * x ** 3)))).astype(F32)
+
+
+def silu(x):
+    """x * sigmoid(x): utils/numba_ops.py:346-349, fused-linear-silu.glsl:43-48."""
+    x = np.asarray(x, dtype=np.float64)
+    return (x / (1.0 + np.exp(-x))).astype(F32)
+
+
+def relu(x):
+    """max(0, x): fused-linear-relu.glsl:63."""
+    return np.maximum(np.asarray(x, dtype=F32), F32(0))
+
+
+def fused_linear_gelu(x, w, b=None):
+    """backend/fnn.py:2022-2123 (falls back to linear then activation_gelu, :2043-2046)."""
+    return gelu(linear(x, w, b))
+
+
+def fused_linear_silu(x, w, b=None):
+    """backend/fnn.py:2214-2303."""
+    return silu(linear(x, w, b))
+
+
+def fused_linear_relu(x, w, b=None):
+    """backend/fnn.py:2125-2212."""
+    return relu(linear(x, w, b))
+
+
+def gemm(a, b):
+    """C = A @ B, all row-major: backend/fnn.py:104-112 (always the NumPy branch), gemm_mnk.glsl:48-87."""
+    return (np.asarray(a, dtype=np.float64) @ np.asarray(b, dtype=np.float64)).astype(F32)
+
+
+def fused_qkv_projection(x, wq, wk, wv, bq=None, bk=None, bv=None):
+    """Stacked projection, output columns [Q | K | V]: fused-qkv-projection.glsl:52-73; equals three
+    linear calls (utils/vulkan_sentence_transformer.py:976-978)."""
+    return np.concatenate([linear(x, wq, bq), linear(x, wk, bk), linear(x, wv, bv)], axis=-1)
+
+
+def layernorm(x, gamma=None, beta=None, eps=1e-5):
+    """gamma * (x - mean) / sqrt(var + eps) + beta, biased variance over the last dim:
+    backend/fnn.py:1285-1313, utils/numba_ops.py:70-87, fnn-layernorm.glsl:55-101."""
+    x = np.asarray(x, dtype=np.float64)
+    mean = x.mean(axis=-1, keepdims=True)
+    var = x.var(axis=-1, keepdims=True)
+    y = (x - mean) / np.sqrt(var + eps)
+    if gamma is not None:
+        y = y * np.asarray(gamma, dtype=np.float64)
+    if beta is not None:
+        y = y + np.asarray(beta, dtype=np.float64)
+    return y.astype(F32)
+
+
+def rmsnorm(x, gamma=None, eps=1e-5):
+    """x / sqrt(mean(x^2) + eps) * gamma: snn-rmsnorm.glsl:45-73, nn/snn.py:374-375."""
+    x = np.asarray(x, dtype=np.float64)
+    y = x / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps)
+    if gamma is not None:
+        y = y * np.asarray(gamma, dtype=np.float64)
+    return y.astype(F32)
+
+
+def fused_layernorm_linear(x, gamma, beta, w, b=None, eps=1e-5):
+    """Linear(LayerNorm(x)): fused-layernorm-linear.glsl:102-126."""
+    return linear(layernorm(x, gamma, beta, eps), w, b)
+
+
+def softmax(x):
+    """Row softmax with max subtraction: activation-softmax.glsl:45-82, utils/numba_ops.py:148-164."""
+    x = np.asarray(x, dtype=np.float64)
+    e = np.exp(x - x.max(axis=-1, keepdims=True))
+    return (e / e.sum(axis=-1, keepdims=True)).astype(F32)
+
+
+def swiglu(x):
+    """Activation form: halves [x1, x2] of the last dim, x1 * silu(x2): activation-swiglu.glsl:32-51,
+    utils/numba_ops.py:527-540."""
+    x = np.asarray(x, dtype=np.float64)
+    h = x.shape[-1] // 2
+    x1, x2 = x[..., :h], x[..., h:]
+    return (x1 * (x2 / (1.0 + np.exp(-x2)))).astype(F32)
+
+
+def fused_swiglu(x, w_gate, w_up, b_gate=None, b_up=None):
+    """(x Wg^T + bg) * silu(x Wu^T + bu): backend/_glu_append.py:47-60, fused-swiglu.glsl:54-78."""
+    g = linear(x, w_gate, b_gate if (b_gate is not None and b_up is not None) else None).astype(np.float64)
+    u = linear(x, w_up, b_up if (b_gate is not None and b_up is not None) else None).astype(np.float64)
+    return (g * (u / (1.0 + np.exp(-u)))).astype(F32)
+
+
+def residual(a, b):
+    """a + b: fnn-residual.glsl:25-34."""
+    return (np.asarray(a, dtype=F32) + np.asarray(b, dtype=F32)).astype(F32)
+
+
+# --------------------------------------------------------------------------- RoPE
+def rope_tables(seq_len, head_dim, base=10000.0, scaling=1.0):
+    """theta[pos, i] = (pos / scaling) * base^(-2 i / D): backend/capsule_transformer.py:756-768,
+    flash-attention2-rope.glsl:74-88."""
+    i = np.arange(head_dim // 2, dtype=np.float64)
+    freqs = np.power(float(base), -2.0 * i / head_dim)
+    theta = np.outer(np.arange(seq_len, dtype=np.float64) / scaling, freqs)
+    return np.cos(theta), np.sin(theta)
+
+
+def rope_interleaved(x, base=10000.0, scaling=1.0):
+    """Pairs (2i, 2i+1) on (B, S, H, D): backend/capsule_transformer.py:775-788,
+    flash-attention2-rope.glsl:101-141."""
+    x = np.asarray(x, dtype=np.float64)
+    _, s, _, d = x.shape
+    cos, sin = rope_tables(s, d, base, scaling)
+    cos, sin = cos[None, :, None, :], sin[None, :, None, :]
+    out = np.empty_like(x)
+    xe, xo = x[..., 0::2], x[..., 1::2]
+    out[..., 0::2] = xe * cos - xo * sin
+    out[..., 1::2] = xe * sin + xo * cos
+    return out.astype(F32)
+
+
+def rope_rotate_half(x, position_ids=None, base=10000.0, scaling=1.0):
+    """Pairs (i, i + D/2) on (B, S, H, D): backend/attention.py:795-835, rope.glsl:76-125,
+    utils/numba_ops.py:726-749."""
+    x = np.asarray(x, dtype=np.float64)
+    b, s, _, d = x.shape
+    half = d // 2
+    if position_ids is None:
+        position_ids = np.tile(np.arange(s), (b, 1))
+    inv_freq = 1.0 / (float(base) ** (np.arange(0, d, 2, dtype=np.float64) / d))
+    theta = (np.asarray(position_ids, dtype=np.float64) / scaling)[..., None] * inv_freq  # (B, S, D/2)
+    cos, sin = np.cos(theta)[:, :, None, :], np.sin(theta)[:, :, None, :]
+    out = np.empty_like(x)
+    a, c = x[..., :half], x[..., half:]
+    out[..., :half] = a * cos - c * sin
+    out[..., half:] = c * cos + a * sin
+    return out.astype(F32)
+
+
+# --------------------------------------------------------------------------- attention
+def attention(q, k, v, scale=None, key_mask=None, causal=False):
+    """softmax(scale * Q K^T + mask) V on the (B, S, H, D) layout.
+
+    Unmasked: nn/modules.py:1421-1456 (FlashAttention2 NumPy branch). Key-padding mask (B, S), 1 = keep,
+    added as (1 - m) * -1e9 on the key axis: utils/vulkan_sentence_transformer.py:1069-1107,
+    flash-attention2.glsl:151-154. Causal: key position > query position is replaced by -1e9
+    (attention-mask.glsl:42-46). The score arithmetic is float32 where the reference's is, so that a fully
+    masked row degenerates the same way (all scores equal -1e9 -> uniform weights)."""
+    q = np.asarray(q, dtype=F32)
+    k = np.asarray(k, dtype=F32)
+    v = np.asarray(v, dtype=F32)
+    b, s, h, d = q.shape
+    if scale is None:
+        scale = 1.0 / np.sqrt(d)
+    qt, kt, vt = (t.transpose(0, 2, 1, 3).astype(np.float64) for t in (q, k, v))
+    scores = (np.einsum("bhqd,bhkd->bhqk", qt, kt) * scale).astype(F32)
+    if key_mask is not None:
+        m = np.asarray(key_mask, dtype=F32)
+        scores = scores + ((F32(1.0) - m) * F32(-1e9))[:, None, None, :]
+    if causal:
+        sk = k.shape[1]
+        future = np.arange(sk)[None, :] > np.arange(s)[:, None]
+        scores = np.where(future[None, None], F32(-1e9), scores)
+    scores = scores.astype(np.float64)
+    e = np.exp(scores - scores.max(axis=-1, keepdims=True))
+    p = e / (e.sum(axis=-1, keepdims=True) + 1e-8)
+    out = np.einsum("bhqk,bhkd->bhqd", p, vt)
+    return out.transpose(0, 2, 1, 3).astype(F32)
+
+
+def flash_attention2(q, k, v, scale=None, mask=None, causal=False):
+    """Intended semantics of VulkanAttention.flash_attention2 (backend/attention.py:361-597)."""
+    return attention(q, k, v, scale=scale, key_mask=mask, causal=causal)
+
+
+def flash_attention2_rope(q, k, v, scale=None, mask=None, causal=False, rope_base=10000.0, rope_scaling=1.0,
+                          rope_style="interleaved"):
+    """Scores on RoPE(q), RoPE(k); V is not rotated: flash-attention2-rope.glsl:101-149."""
+    if rope_style == "interleaved":
+        q, k = rope_interleaved(q, rope_base, rope_scaling), rope_interleaved(k, rope_base, rope_scaling)
+    else:
+        q = rope_rotate_half(q, None, rope_base, rope_scaling)
+        k = rope_rotate_half(k, None, rope_base, rope_scaling)
+    return attention(q, k, v, scale=scale, key_mask=mask, causal=causal)
+
+
+# --------------------------------------------------------------------------- encoder glue
+def embedding_lookup(ids, table):
+    """Row gather, ids outside [0, vocab) give zero rows: embedding-lookup.glsl:36-54,
+    utils/vulkan_sentence_transformer.py:628-637."""
+    ids = np.asarray(ids)
+    table = np.asarray(table, dtype=F32)
+    ok = (ids >= 0) & (ids < table.shape[0])
+    out = table[np.where(ok, ids, 0)]
+    out[~ok] = 0
+    return out.astype(F32)
+
+
+def mean_pool(x, mask=None):
+    """Masked mean over the sequence axis: embedding-pool.glsl:61-81 (m > 0.5, 0 when nothing counts),
+    backend/pooling.py:93-96; the NumPy fallback (utils/vulkan_sentence_transformer.py:1189-1191) divides by
+    (sum(m) + 1e-8), which differs by 1e-8 relative."""
+    x = np.asarray(x, dtype=np.float64)
+    if mask is None:
+        return x.mean(axis=1).astype(F32)
+    keep = (np.asarray(mask) > 0.5).astype(np.float64)[:, :, None]
+    cnt = keep.sum(axis=1)
+    return np.where(cnt > 0, (x * keep).sum(axis=1) / np.maximum(cnt, 1.0), 0.0).astype(F32)
+
+
+def embedding_normalize(x):
+    """x / (||x||_2 + 1e-8): functional/embedding.py:67-68."""
+    x = np.asarray(x, dtype=np.float64)
+    return (x / (np.linalg.norm(x, axis=-1, keepdims=True) + 1e-8)).astype(F32)
+
+
+def encoder_layer(x, lw, mask, num_heads, eps=1e-5):
+    """Post-LN BERT layer: utils/vulkan_sentence_transformer.py:972-1033 (NumPy branches).
+    lw holds attn_{q,k,v,out}_{weight,bias}, attn_ln_{gamma,beta}, ffn_w1/b1/w2/b2, ffn_ln_{gamma,beta}."""
+    b, s, hid = x.shape
+    d = hid // num_heads
+    q = linear(x, lw["attn_q_weight"], lw["attn_q_bias"]).reshape(b, s, num_heads, d)
+    k = linear(x, lw["attn_k_weight"], lw["attn_k_bias"]).reshape(b, s, num_heads, d)
+    v = linear(x, lw["attn_v_weight"], lw["attn_v_bias"]).reshape(b, s, num_heads, d)
+    a = attention(q, k, v, key_mask=mask).reshape(b, s, hid)
+    a = linear(a, lw["attn_out_weight"], lw["attn_out_bias"])
+    x = layernorm(a + x, lw["attn_ln_gamma"], lw["attn_ln_beta"], eps)
+    f = linear(gelu(linear(x, lw["ffn_w1"], lw["ffn_b1"])), lw["ffn_w2"], lw["ffn_b2"])
+    return layernorm(f + x, lw["ffn_ln_gamma"], lw["ffn_ln_beta"], eps)
+
+
+def encoder_forward(ids, mask, w, num_heads, embed_eps=1e-12, layer_eps=1e-5, return_hidden=False):
+    """MiniLM/BERT sentence encoder: embeddings (utils/vulkan_sentence_transformer.py:620-705), embedding
+    LayerNorm (:726-744), the layers (:972-1033), masked mean pool (:1185-1191), L2 normalise (:1196-1201).
+    w: word, pos, type (or None), emb_ln_g, emb_ln_b, layers (list of per-layer dicts)."""
+    ids = np.asarray(ids)
+    b, s = ids.shape
+    x = embedding_lookup(ids, w["word"])
+    if w.get("type") is not None:
+        x = x + w["type"][0][None, None, :]
+    x = x + w["pos"][:s][None, :, :]
+    x = layernorm(x, w["emb_ln_g"], w["emb_ln_b"], embed_eps)
+    mask = np.ones((b, s), dtype=F32) if mask is None else np.asarray(mask, dtype=F32)
+    for lw in w["layers"]:
+        x = encoder_layer(x, lw, mask, num_heads, layer_eps)
+    out = embedding_normalize(mean_pool(x, mask))
+    return (out, x) if return_hidden else out
+
+
+# --------------------------------------------------------------------------- checkers
+def rel_l2(a, b):
+    """||a - b||_2 / ||b||_2 in float64."""
+    a = np.asarray(a, dtype=np.float64).ravel()
+    b = np.asarray(b, dtype=np.float64).ravel()
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def xavier_uniform(rng, out_features, in_features):
+    """U(-l, l), l = sqrt(6 / (in + out)), array shape (out, in): nn/modules.py:38-43."""
+    lim = np.sqrt(6.0 / (in_features + out_features))
+    return rng.uniform(-lim, lim, size=(out_features, in_features)).astype(F32)
