@@ -43,6 +43,10 @@ SIGNATURES = {
     "grilly_set_stream": [_vp, _vp],
     "grilly_sync": [_vp],
     "grilly_launch_count": [_vp, C.POINTER(C.c_uint64)],
+    "grilly_timer_start": [_vp],
+    "grilly_timer_stop": [_vp, C.POINTER(C.c_float)],
+    "grilly_profile_begin": [_vp],
+    "grilly_profile_end": [_vp, C.POINTER(C.c_double)],
     "grilly_alloc": [_vp, _sz, _pp],
     "grilly_free": [_vp, _vp],
     "grilly_upload": [_vp, _vp, _vp, _sz],
@@ -73,6 +77,8 @@ SIGNATURES = {
     "grilly_encoder_keep_hidden": [_vp, _i],
     "grilly_encoder_last_hidden": [_vp, _vp, _ll, C.POINTER(_ll)],
     "grilly_encoder_destroy": [_vp],
+    "grilly_gemm_pick_tile": [_i, _i, _i],
+    "grilly_plan_chunks": [_vp, _i, _i, _vp, _vp, C.POINTER(_ll)],
 }
 _RESTYPE = {"grilly_last_error": C.c_char_p}
 

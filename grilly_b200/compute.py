@@ -1,0 +1,496 @@
+"""``Compute()``: the reference's op namespaces (backend/compute.py:23-128) on top of the CUDA library.
+
+NumPy arrays in, new float32 NumPy arrays out, same method names and positional orders as
+``grilly.Compute()`` for the dense transformer path: ``.fnn`` (backend/fnn.py), ``.attention``
+(backend/attention.py), ``.pooling`` (backend/pooling.py), ``.learning.embedding_lookup``
+(backend/learning.py:811-877). Any argument may also be a :class:`~grilly_b200.device.DeviceTensor`
+(from ``backend.to_device``); then the result stays on the device as well.
+
+There is no CPU fallback: an unsupported shape or a missing GPU raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+
+from . import _lib as L
+from .device import Device, DeviceTensor
+
+_ACT = {None: L.ACT_NONE, "none": L.ACT_NONE, "gelu": L.ACT_GELU, "silu": L.ACT_SILU, "relu": L.ACT_RELU}
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.ptr)
+
+
+class _Namespace:
+    def __init__(self, backend: "Compute"):
+        self._b = backend
+        self.dev = backend.device
+        self.lib = backend.device.lib
+        self.ctx = backend.device.ctx
+
+    # operand staging -------------------------------------------------------------------------
+    @property
+    def _bf16(self) -> bool:
+        return self._b.precision == "bf16"
+
+    def _act_in(self, x, mma_operand: bool = True):
+        """Activation operand -> (DeviceTensor, was_host). GEMM/attention operands are staged in the
+        precision the tensor core consumes (bf16, or fp32 rounded to the nearest tf32 value)."""
+        if isinstance(x, DeviceTensor):
+            return x, False
+        if mma_operand and self._bf16:
+            return self.dev.upload(x, "bf16"), True
+        return self.dev.upload(x, "f32", round_tf32=mma_operand), True
+
+    def _vec(self, v):
+        """Small fp32 parameter vector (bias, gamma, beta): cached like a weight, never rounded."""
+        if v is None:
+            return None
+        return self.dev.weight(v, "f32", round_tf32=False, tag="vec")
+
+    def _out(self, t: DeviceTensor, to_host: bool, shape=None):
+        if shape is not None:
+            t = t.reshape(shape)
+        return t.numpy() if to_host else t
+
+
+class FNN(_Namespace):
+    """backend/fnn.py ``VulkanFNN``: the GEMM family, normalisation and activations."""
+
+    def __init__(self, backend):
+        super().__init__(backend)
+        self.buffer_pool = _PoolView(backend.device)
+
+    # ---- GEMM family ------------------------------------------------------------------------
+    def _linear(self, x, weights, bias, act, residual=None, flags=0, w_tag="", w_transform=None, n_out=None):
+        w_shape = weights.shape
+        if len(w_shape) != 2:
+            raise ValueError("weights must be 2-D (out_features, in_features)")
+        N, K = (int(s) for s in w_shape)
+        x_shape = tuple(x.shape)
+        if x_shape[-1] != K:
+            raise ValueError(f"input feature size {x_shape[-1]} does not match weights {tuple(w_shape)}")
+        elt = 2 if self._bf16 else 4
+        kpad = (-K) % (16 // elt)
+        dt = "bf16" if self._bf16 else "f32"
+        if kpad and not isinstance(x, DeviceTensor):
+            # TMA needs 16-byte row pitches: pad K with zeros on both operands
+            x = np.pad(np.asarray(x, dtype=np.float32).reshape(-1, K), ((0, 0), (0, kpad)))
+            base_tf = w_transform
+            w_transform = (lambda a, f=base_tf: np.pad(np.asarray(f(a) if f else a, dtype=np.float32), ((0, 0), (0, kpad))))
+            w_tag += f"|kpad{kpad}"
+        elif kpad:
+            raise ValueError("device-resident operands need in_features * element size to be a multiple of 16 bytes")
+        xd, host = self._act_in(x)
+        wd = self.dev.weight(weights, dt, round_tf32=True, transform=w_transform, tag="w" + w_tag)
+        n_rows_w = wd.shape[0]
+        bd = self._vec(bias) if not isinstance(bias, DeviceTensor) else bias
+        rd = None
+        if residual is not None:
+            rd, _ = self._act_in(residual, mma_operand=False)
+        M = xd.size // (K + kpad)
+        n_cols = n_out if n_out is not None else n_rows_w
+        y = self.dev.empty((M, n_cols), "f32")
+        self.dev.check(self.lib.grilly_linear(self.ctx, _p(xd), _p(wd), _p(bd), _p(rd), _p(y), M, n_rows_w, K + kpad,
+                                              act, L.PREC_BF16 if self._bf16 else L.PREC_TF32, flags))
+        return self._out(y, host, x_shape[:-1] + (n_cols,))
+
+    def linear(self, x, weights, bias=None):
+        """y = x @ W.T + b, W (out, in): backend/fnn.py:1394-1496."""
+        return self._linear(x, weights, bias, L.ACT_NONE)
+
+    def fused_linear_gelu(self, x, weights, bias=None):
+        """gelu_tanh(x @ W.T + b): backend/fnn.py:2022-2123."""
+        return self._linear(x, weights, bias, L.ACT_GELU)
+
+    def fused_linear_relu(self, x, weights, bias=None):
+        """relu(x @ W.T + b): backend/fnn.py:2125-2212."""
+        return self._linear(x, weights, bias, L.ACT_RELU)
+
+    def fused_linear_silu(self, x, weights, bias=None):
+        """silu(x @ W.T + b): backend/fnn.py:2214-2303."""
+        return self._linear(x, weights, bias, L.ACT_SILU)
+
+    def fused_qkv_projection(self, x, w_qkv, b_qkv=None, num_heads=None, head_dim=None):
+        """x @ [Wq;Wk;Wv].T + [bq;bk;bv] -> (..., 3*H*D), column blocks Q, K, V: fused-qkv-projection.glsl:48-74."""
+        if num_heads is not None and head_dim is not None and w_qkv.shape[0] != 3 * num_heads * head_dim:
+            raise ValueError("stacked QKV weight must have 3 * num_heads * head_dim rows")
+        return self._linear(x, w_qkv, b_qkv, L.ACT_NONE)
+
+    def fused_swiglu(self, x, w_gate, w_up, b_gate=None, b_up=None):
+        """(x Wg^T + bg) * silu(x Wu^T + bu) as ONE GEMM over row-interleaved [g0,u0,g1,u1,...] weights with a
+        pairwise epilogue: backend/_glu_append.py:47-60, fused-swiglu.glsl:48-79."""
+        if tuple(w_gate.shape) != tuple(w_up.shape):
+            raise ValueError("gate and up weights must have the same shape")
+        n = int(w_gate.shape[0])
+        up_host = np.asarray(w_up, dtype=np.float32)
+
+        def interleave(g):
+            out = np.empty((2 * n, g.shape[1]), dtype=np.float32)
+            out[0::2] = np.asarray(g, dtype=np.float32)
+            out[1::2] = up_host
+            return out
+
+        bias = None
+        if b_gate is not None and b_up is not None:
+            bias = np.empty(2 * n, dtype=np.float32)
+            bias[0::2], bias[1::2] = np.asarray(b_gate, np.float32), np.asarray(b_up, np.float32)
+        tag = f"|swiglu{np.asarray(w_up).__array_interface__['data'][0]}"
+        return self._linear(x, w_gate, bias, L.ACT_NONE, flags=L.FLAG_SWIGLU_PAIRS, w_tag=tag, w_transform=interleave,
+                            n_out=n)
+
+    def fused_layernorm_linear(self, x, gamma, beta, weights, bias=None, eps=1e-5, mode="layer"):
+        """Linear(LayerNorm(x)) (or RMSNorm with mode='rms'): fused-layernorm-linear.glsl:67-128. One row-statistics
+        kernel plus the GEMM on the raw rows; gamma/beta are folded into the weights once and cached."""
+        if self._bf16:
+            raise NotImplementedError("fused_layernorm_linear runs in tf32 mode; in bf16 mode call layernorm then linear")
+        N, K = (int(s) for s in weights.shape)
+        x_shape = tuple(x.shape)
+        if x_shape[-1] != K:
+            raise ValueError(f"input feature size {x_shape[-1]} does not match weights {tuple(weights.shape)}")
+        if K % 4:
+            raise ValueError("fused_layernorm_linear needs in_features to be a multiple of 4")
+        key = ("lnfold", id(weights), id(gamma), id(beta), id(bias), mode)
+        fold = self._b._folds.get(key)
+        if fold is None:
+            wd = self.dev.upload(np.asarray(weights, np.float32))
+            gd = self.dev.upload(np.asarray(gamma, np.float32)) if gamma is not None else None
+            bd = self.dev.upload(np.asarray(beta, np.float32)) if (beta is not None and mode == "layer") else None
+            cd = self.dev.upload(np.asarray(bias, np.float32)) if bias is not None else None
+            wf, cs, bf = self.dev.empty((N, K)), self.dev.empty((N,)), self.dev.empty((N,))
+            self.dev.check(self.lib.grilly_fold_layernorm_weights(self.ctx, _p(wd), _p(gd), _p(bd), _p(cd), _p(wf), _p(cs),
+                                                                  _p(bf), N, K, L.PREC_TF32))
+            self.dev.sync()
+            fold = (wf, cs, bf, weights, gamma, beta, bias)  # keep the host arrays alive so ids stay unique
+            self._b._folds[key] = fold
+        wf, cs, bf = fold[:3]
+        xd, host = self._act_in(x, mma_operand=False)  # statistics need the unrounded rows
+        M = xd.size // K
+        y = self.dev.empty((M, N))
+        stats = self.dev.empty((2 * M,))
+        self.dev.check(self.lib.grilly_layernorm_linear(self.ctx, _p(xd), _p(wf), _p(cs), _p(bf), _p(y), _p(stats), M, N, K,
+                                                        float(eps), L.NORM_RMS if mode == "rms" else L.NORM_LAYER,
+                                                        L.ACT_NONE, L.PREC_TF32, 0))
+        out = self._out(y, host, x_shape[:-1] + (N,))
+        stats.free()
+        return out
+
+    def gemm(self, A, B):
+        """C = A @ B, row-major (M,K) x (K,N): backend/fnn.py:104-166, gemm_mnk.glsl:35-88."""
+        if len(A.shape) != 2 or len(B.shape) != 2 or A.shape[1] != B.shape[0]:
+            raise AssertionError(f"K mismatch: {tuple(A.shape)} @ {tuple(B.shape)}")  # the reference asserts (fnn.py:118)
+        M, K = (int(s) for s in A.shape)
+        N = int(B.shape[1])
+        q = 8 if self._bf16 else 4
+        kpad, npad = (-K) % q, (-N) % q
+        if (kpad or npad) and (isinstance(A, DeviceTensor) or isinstance(B, DeviceTensor)):
+            raise ValueError("device-resident gemm operands need K and N to be multiples of 16 bytes")
+        if kpad or npad:
+            A = np.pad(np.asarray(A, np.float32), ((0, 0), (0, kpad)))
+            B = np.pad(np.asarray(B, np.float32), ((0, kpad), (0, npad)))
+        ad, host_a = self._act_in(A)
+        bd, host_b = self._act_in(B)
+        c = self.dev.empty((M, N + npad))
+        self.dev.check(self.lib.grilly_gemm_mnk(self.ctx, _p(ad), _p(bd), _p(c), M, K + kpad, N + npad,
+                                                L.PREC_BF16 if self._bf16 else L.PREC_TF32, 0))
+        if host_a or host_b:
+            out = c.numpy()
+            return np.ascontiguousarray(out[:, :N]) if npad else out
+        return c
+
+    gemm_mnk = gemm
+
+    # ---- normalisation ----------------------------------------------------------------------
+    def _norm(self, x, gamma, beta, eps, mode, residual=None):
+        x_shape = tuple(x.shape)
+        F = int(x_shape[-1])
+        xd, host = self._act_in(x, mma_operand=False)
+        rd = None
+        if residual is not None:
+            rd, _ = self._act_in(residual, mma_operand=False)
+        for name, v in (("gamma", gamma), ("beta", beta)):
+            if v is not None and int(np.prod(v.shape)) != F:
+                raise ValueError(f"{name} has {int(np.prod(v.shape))} entries, expected {F}")
+        rows = xd.size // F
+        y = self.dev.empty((rows, F))
+        self.dev.check(self.lib.grilly_layernorm(self.ctx, _p(xd), _p(rd), _p(self._vec(gamma)), _p(self._vec(beta)), _p(y),
+                                                 rows, F, float(eps), mode, 0))
+        return self._out(y, host, x_shape)
+
+    def layernorm(self, x, gamma=None, beta=None, eps=1e-5):
+        """gamma (x - mean) / sqrt(var + eps) + beta over the last dim: backend/fnn.py:1285-1389."""
+        return self._norm(x, gamma, beta, eps, L.NORM_LAYER)
+
+    def rmsnorm(self, x, gamma=None, eps=1e-5):
+        """x / sqrt(mean(x^2) + eps) * gamma: snn-rmsnorm.glsl:34-75."""
+        return self._norm(x, gamma, None, eps, L.NORM_RMS)
+
+    def residual_layernorm(self, x, module_output, gamma=None, beta=None, eps=1e-5):
+        """LayerNorm(x + module_output) in one pass (the post-LN step of utils/vulkan_sentence_transformer.py:1004)."""
+        return self._norm(x, gamma, beta, eps, L.NORM_LAYER, residual=module_output)
+
+    # ---- activations ------------------------------------------------------------------------
+    def _eltwise(self, op, a, b=None, half=0):
+        shape = tuple(a.shape)
+        ad, host = self._act_in(a, mma_operand=False)
+        bd = None
+        if b is not None:
+            if tuple(b.shape) != shape:
+                raise ValueError(f"shape mismatch: {shape} vs {tuple(b.shape)}")
+            bd, _ = self._act_in(b, mma_operand=False)
+        out_shape = shape if op != L.ELT_SWIGLU else shape[:-1] + (half,)
+        y = self.dev.empty(out_shape)
+        self.dev.check(self.lib.grilly_eltwise(self.ctx, op, _p(ad), _p(bd), _p(y), y.size, half))
+        return self._out(y, host)
+
+    def activation_gelu(self, input_data):
+        """tanh-approximation GELU: backend/fnn.py:285-342."""
+        return self._eltwise(L.ELT_GELU, input_data)
+
+    def activation_silu(self, input_data):
+        """x * sigmoid(x): backend/fnn.py:344-400."""
+        return self._eltwise(L.ELT_SILU, input_data)
+
+    def activation_relu(self, input_data):
+        """max(0, x): backend/fnn.py:232-283."""
+        return self._eltwise(L.ELT_RELU, input_data)
+
+    def activation_swiglu(self, input_data):
+        """x1 * silu(x2) on halves of the last dim: backend/fnn.py:499-572."""
+        if input_data.shape[-1] % 2:
+            raise ValueError("SwiGLU needs an even last dimension")
+        return self._eltwise(L.ELT_SWIGLU, input_data, half=int(input_data.shape[-1]) // 2)
+
+    swiglu = activation_swiglu  # the name the reference's README uses (README.md:108)
+
+    def activation_softmax(self, input_data, axis=-1):
+        """softmax over ``axis``: backend/fnn.py:574-663."""
+        nd = len(input_data.shape)
+        ax = axis % nd
+        if ax != nd - 1:
+            if isinstance(input_data, DeviceTensor):
+                raise ValueError("device-resident softmax runs over the last axis only")
+            moved = np.moveaxis(np.asarray(input_data, np.float32), ax, -1)
+            return np.ascontiguousarray(np.moveaxis(self.activation_softmax(np.ascontiguousarray(moved)), -1, ax))
+        shape = tuple(input_data.shape)
+        xd, host = self._act_in(input_data, mma_operand=False)
+        y = self.dev.empty(shape)
+        cols = int(shape[-1])
+        self.dev.check(self.lib.grilly_softmax(self.ctx, _p(xd), _p(y), xd.size // cols, cols))
+        return self._out(y, host)
+
+    def residual(self, x, module_output):
+        """x + module_output: backend/fnn.py:1950-2014."""
+        return self._eltwise(L.ELT_ADD, x, module_output)
+
+
+class Attention(_Namespace):
+    """backend/attention.py ``VulkanAttention``."""
+
+    architecture = None
+
+    def flash_attention2(self, queries, keys, values, num_heads=None, head_dim=None, tile_size_q=64, tile_size_k=64,
+                         scale=None, mask=None, causal=False, use_rope=False, rope_base=10000.0, rope_scaling=1.0,
+                         rope_style="interleaved"):
+        """softmax(scale Q K^T + mask) V on (B, S, H, D) or (B, S, H*D) inputs: backend/attention.py:361-597.
+
+        ``mask`` is a (B, S) key-padding mask, 1 = keep. ``causal`` masks keys after the query. ``tile_size_*`` are
+        accepted for signature compatibility; the kernel tiles 128 x 128. With ``use_rope`` the scores are taken
+        on rotated q, k (flash-attention2-rope.glsl; ``rope_style`` 'interleaved' or 'rotate_half')."""
+        shape = tuple(queries.shape)
+        if len(shape) == 4:
+            B, S, H, D = (int(s) for s in shape)  # a 4-D input's own shape wins (attention.py:410)
+        elif len(shape) == 3:
+            if num_heads is None or head_dim is None:
+                raise ValueError("3-D inputs need num_heads and head_dim")
+            B, S, _ = (int(s) for s in shape)
+            H, D = int(num_heads), int(head_dim)
+            if shape[2] != H * D:
+                raise ValueError(f"last dimension {shape[2]} != num_heads * head_dim = {H * D}")
+        else:
+            raise ValueError("queries must be (B, S, H, D) or (B, S, H*D)")
+        if tuple(keys.shape) != shape or tuple(values.shape) != shape:
+            raise ValueError("queries, keys and values must have the same shape")
+        if mask is not None and tuple(mask.shape) != (B, S):
+            raise ValueError(f"mask must have shape {(B, S)}")
+        qd, host = self._act_in(queries)
+        kd, _ = self._act_in(keys)
+        vd, _ = self._act_in(values)
+        md = None
+        if mask is not None:
+            md, _ = self._act_in(np.asarray(mask, dtype=np.float32) if not isinstance(mask, DeviceTensor) else mask,
+                                 mma_operand=False)
+        rope = L.ROPE_NONE
+        if use_rope:
+            if rope_style not in ("interleaved", "rotate_half"):
+                raise ValueError("rope_style must be 'interleaved' or 'rotate_half'")
+            rope = L.ROPE_INTERLEAVED if rope_style == "interleaved" else L.ROPE_ROTATE_HALF
+        sc = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+        out = self.dev.empty((B, S, H, D))
+        self.dev.check(self.lib.grilly_flash_attention(
+            self.ctx, _p(qd), _p(kd), _p(vd), _p(out), B, S, H, D, H * D, H * D, None, B * S, _p(md), sc, int(bool(causal)),
+            rope, float(rope_base), float(rope_scaling), L.PREC_BF16 if self._bf16 else L.PREC_TF32, 0))
+        return self._out(out, host)
+
+    def flash_attention2_rope(self, queries, keys, values, num_heads=None, head_dim=None, scale=None, mask=None,
+                              causal=False, rope_base=10000.0, rope_scaling=1.0, rope_style="interleaved"):
+        """flash-attention2-rope.glsl:74-149,165-247 (the reference ships the shader without a Python wrapper)."""
+        return self.flash_attention2(queries, keys, values, num_heads, head_dim, scale=scale, mask=mask, causal=causal,
+                                     use_rope=True, rope_base=rope_base, rope_scaling=rope_scaling, rope_style=rope_style)
+
+    def apply_rope(self, q_or_k, position_ids=None, rope_base=10000.0, rope_scaling=1.0):
+        """Rotate-half RoPE on (B, S, H, D): backend/attention.py:599-676, rope.glsl:52-126."""
+        shape = tuple(q_or_k.shape)
+        if len(shape) != 4 or shape[-1] % 2:
+            raise ValueError("apply_rope expects (B, S, H, D) with an even D")
+        B, S, H, D = (int(s) for s in shape)
+        xd, host = self._act_in(q_or_k, mma_operand=False)
+        pid, max_pos = None, S
+        if position_ids is not None:
+            ph = np.ascontiguousarray(position_ids, dtype=np.int32)
+            if ph.shape != (B, S):
+                raise ValueError(f"position_ids must have shape {(B, S)}")
+            if ph.min() < 0:
+                raise ValueError("position_ids must be non-negative")
+            max_pos = int(ph.max()) + 1
+            pid = self.dev.upload(ph, "i32")
+        y = self.dev.empty(shape)
+        self.dev.check(self.lib.grilly_apply_rope(self.ctx, _p(xd), _p(y), _p(pid), B, S, H, D, max_pos, float(rope_base),
+                                                  float(rope_scaling), L.ROPE_ROTATE_HALF))
+        return self._out(y, host)
+
+    def _unfused(self, name):
+        raise NotImplementedError(
+            f"{name}: the unfused scores/mask/output pipeline (which materialises a (B,H,S,S) tensor) is replaced by "
+            "flash_attention2(q, k, v, mask=..., causal=...)")
+
+    def attention_scores(self, *a, **k):
+        self._unfused("attention_scores")
+
+    def attention_mask(self, *a, **k):
+        self._unfused("attention_mask")
+
+    def attention_output(self, *a, **k):
+        self._unfused("attention_output")
+
+
+class Pooling(_Namespace):
+    """backend/pooling.py ``VulkanPooling`` (sequence pooling only)."""
+
+    def _pool(self, embeddings, mask, normalize):
+        shape = tuple(embeddings.shape)
+        if len(shape) != 3:
+            raise ValueError("embeddings must be (batch, seq_len, dim)")
+        B, S, F = (int(s) for s in shape)
+        if mask is not None and tuple(mask.shape) != (B, S):
+            raise ValueError(f"mask must have shape {(B, S)}")
+        xd, host = self._act_in(embeddings, mma_operand=False)
+        md = None
+        if mask is not None:
+            md, _ = self._act_in(np.asarray(mask, np.float32) if not isinstance(mask, DeviceTensor) else mask, mma_operand=False)
+        out = self.dev.empty((B, F))
+        self.dev.check(self.lib.grilly_mean_pool(self.ctx, _p(xd), _p(md), None, _p(out), B, S, F, int(normalize)))
+        return self._out(out, host)
+
+    def mean_pool(self, embeddings, mask=None):
+        """Masked mean over the sequence axis (mask > 0.5 counts; zero vector when nothing counts):
+        backend/pooling.py:22-142, embedding-pool.glsl:61-81."""
+        return self._pool(embeddings, mask, False)
+
+    def mean_pool_normalize(self, embeddings, mask=None):
+        """mean_pool followed by x / (||x|| + 1e-8) (functional/embedding.py:42-68) in the same kernel."""
+        return self._pool(embeddings, mask, True)
+
+
+class Learning(_Namespace):
+    """backend/learning.py ``VulkanLearning`` (embedding lookup only)."""
+
+    def embedding_lookup(self, token_ids, embedding_table):
+        """Row gather; ids outside the table give zero rows: backend/learning.py:811-877."""
+        if len(embedding_table.shape) != 2:
+            raise ValueError("embedding_table must be (vocab, dim)")
+        V, F = (int(s) for s in embedding_table.shape)
+        ids = np.ascontiguousarray(token_ids, dtype=np.int64)
+        ids32 = np.where((ids < 0) | (ids >= V), -1, ids).astype(np.int32)
+        idd = self.dev.upload(ids32, "i32")
+        td = self.dev.weight(embedding_table, "f32", round_tf32=False, tag="table")
+        out = self.dev.empty(tuple(ids.shape) + (F,))
+        self.dev.check(self.lib.grilly_embedding_lookup(self.ctx, _p(idd), _p(td), _p(out), ids.size, V, F))
+        return out.numpy()
+
+
+class _PoolView:
+    """``backend.fnn.buffer_pool.get_stats()`` (tutorials/06_transformer_components.py:142-145)."""
+
+    def __init__(self, dev: Device):
+        self._dev = dev
+
+    def get_stats(self) -> dict:
+        return self._dev.pool_stats()
+
+
+class Compute:
+    """Drop-in for ``grilly.Compute()`` (``VulkanCompute``, backend/compute.py:23-128) on one B200.
+
+    precision: 'tf32' (fp32 storage, tf32 tensor-core products, fp32 accumulate) or 'bf16'.
+    """
+
+    def __init__(self, shader_dir=None, device: int = 0, precision: str = "tf32"):
+        if precision not in ("tf32", "bf16"):
+            raise ValueError("precision must be 'tf32' or 'bf16'")
+        self.precision = precision
+        self.device = Device(device)
+        self.architecture = None
+        self._folds: dict = {}
+        self.fnn = FNN(self)
+        self.attention = Attention(self)
+        self.pooling = Pooling(self)
+        self.learning = Learning(self)
+        self._alias()
+
+    def _alias(self):
+        # flat aliases the reference exposes (backend/compute.py:99,116-128,153-195,324-326)
+        f = self.fnn
+        for name in ("linear", "layernorm", "residual", "activation_relu", "activation_gelu", "activation_silu",
+                     "activation_swiglu", "activation_softmax", "fused_linear_gelu", "fused_linear_relu",
+                     "fused_linear_silu", "gemm"):
+            setattr(self, name, getattr(f, name))
+        self.flash_attention2 = self.attention.flash_attention2
+        self.apply_rope = self.attention.apply_rope
+        self.mean_pool = self.pooling.mean_pool
+        self.embedding_lookup = self.learning.embedding_lookup
+
+    def set_architecture(self, architecture: str):
+        """backend/compute.py:70-128. There are no per-architecture kernels here: causal masking is a flag."""
+        self.architecture = architecture
+        self.attention.architecture = architecture
+
+    def to_device(self, arr, mma_operand: bool = True) -> DeviceTensor:
+        """Stage an array on the GPU once; ops given DeviceTensors return DeviceTensors."""
+        if self.precision == "bf16" and mma_operand:
+            return self.device.upload(arr, "bf16")
+        return self.device.upload(arr, "f32", round_tf32=mma_operand)
+
+    def invalidate(self, arr=None):
+        """Forget cached device copies of a weight that was modified in place (all weights if None)."""
+        self.device.invalidate(arr)
+        if arr is None:
+            self._folds.clear()
+
+    def synchronize(self):
+        self.device.sync()
+
+    def cleanup(self):
+        """backend/compute.py:56-68."""
+        self._folds.clear()
+        self.device.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.cleanup()

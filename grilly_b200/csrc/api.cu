@@ -11,6 +11,18 @@ int set_error(grilly_ctx* ctx, int code, const std::string& msg) {
   return code;
 }
 
+int prof_begin(grilly_ctx* ctx, int cls, double flops, double bytes) {
+  if (!ctx->profiling) return -1;
+  grilly_ctx::ProfRec r{cls, nullptr, nullptr, flops, bytes};
+  if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return -1;
+  cudaEventRecord(r.a, ctx->stream);
+  ctx->prof.push_back(r);
+  return static_cast<int>(ctx->prof.size()) - 1;
+}
+void prof_end(grilly_ctx* ctx, int idx) {
+  if (idx >= 0) cudaEventRecord(ctx->prof[idx].b, ctx->stream);
+}
+
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 
 static int load_encode(grilly_ctx* ctx) {
@@ -114,6 +126,7 @@ int grilly_shutdown(grilly_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   for (auto& kv : ctx->live) cudaFreeAsync(kv.first, ctx->own_stream);
   for (auto& t : ctx->rope_tables) { cudaFree(t.cos_t); cudaFree(t.sin_t); }
+  if (ctx->timer_a) { cudaEventDestroy(ctx->timer_a); cudaEventDestroy(ctx->timer_b); }
   cudaStreamSynchronize(ctx->own_stream);
   cudaFree(ctx->err_dev);
   cudaFreeHost(ctx->err_host);
@@ -151,6 +164,55 @@ int grilly_sync(grilly_ctx* ctx) {
 int grilly_launch_count(grilly_ctx* ctx, uint64_t* count) {
   if (!ctx || !count) return GRILLY_ERR_INVALID_ARG;
   *count = ctx->launches;
+  return GRILLY_OK;
+}
+
+int grilly_timer_start(grilly_ctx* ctx) {
+  CTX_GUARD(ctx);
+  if (!ctx->timer_a) {
+    GB_CUDA_CHECK(ctx, cudaEventCreate(&ctx->timer_a));
+    GB_CUDA_CHECK(ctx, cudaEventCreate(&ctx->timer_b));
+  }
+  GB_CUDA_CHECK(ctx, cudaEventRecord(ctx->timer_a, ctx->stream));
+  return GRILLY_OK;
+}
+
+int grilly_timer_stop(grilly_ctx* ctx, float* ms) {
+  CTX_GUARD(ctx);
+  if (!ms || !ctx->timer_a) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "timer_stop: no timer running or null output");
+  GB_CUDA_CHECK(ctx, cudaEventRecord(ctx->timer_b, ctx->stream));
+  GB_CUDA_CHECK(ctx, cudaEventSynchronize(ctx->timer_b));
+  GB_CUDA_CHECK(ctx, cudaEventElapsedTime(ms, ctx->timer_a, ctx->timer_b));
+  return GRILLY_OK;
+}
+
+int grilly_profile_begin(grilly_ctx* ctx) {
+  CTX_GUARD(ctx);
+  for (auto& r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  ctx->prof.clear();
+  ctx->profiling = true;
+  return GRILLY_OK;
+}
+
+int grilly_profile_end(grilly_ctx* ctx, double* out) {
+  CTX_GUARD(ctx);
+  if (!out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "profile_end: null output");
+  ctx->profiling = false;
+  GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int i = 0; i < PROF_NCLASS * 4; ++i) out[i] = 0.0;
+  for (auto& r : ctx->prof) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+      out[r.cls * 4 + 0] += 1.0;
+      out[r.cls * 4 + 1] += ms;
+      out[r.cls * 4 + 2] += r.flops;
+      out[r.cls * 4 + 3] += r.bytes;
+    }
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  ctx->prof.clear();
+  cudaGetLastError();
   return GRILLY_OK;
 }
 

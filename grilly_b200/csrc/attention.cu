@@ -25,7 +25,14 @@ static int launch_one(grilly_ctx* ctx, const void* q, const void* k, const void*
     ctx->smem_attr_done.insert(reinterpret_cast<const void*>(kern));
   }
   dim3 grid((args.S + ATTN_TILE - 1) / ATTN_TILE, args.H, args.B);
+  // algorithmic work: 4*D FLOPs per (query, key) pair (half under a causal mask), q/k/v read + out written once
+  double flops = ctx->attn_flops_hint >= 0.0 ? ctx->attn_flops_hint
+                                             : 4.0 * args.B * args.H * static_cast<double>(args.S) * args.S * D * (args.causal ? 0.5 : 1.0);
+  ctx->attn_flops_hint = -1.0;
+  const double bytes = static_cast<double>(total_rows) * args.H * D * (3.0 * ELT + (args.out_bf16 ? 2.0 : 4.0));
+  const int pi = prof_begin(ctx, PROF_ATTN, flops, bytes);
   kern<<<grid, ATTN_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tq, tk, tv, args);
+  prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;

@@ -121,7 +121,7 @@ static int enc_norm(grilly_encoder* e, const float* x, const float* g, const flo
 
 // Runs one chunk: sequences [b0, b1) whose packed rows are [0, rows) of the workspace.
 static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_dev, int b0, int b1, int S, int rows,
-                     int max_len, float* out_dev, long long hidden_row0) {
+                     int max_len, float* out_dev, long long hidden_row0, double sum_len2) {
   grilly_ctx* ctx = e->ctx;
   const auto& c = e->cfg;
   const int F = c.hidden, H = c.num_heads, D = F / H, Bc = b1 - b0;
@@ -137,6 +137,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
     AttnArgs at{};
     at.B = Bc; at.S = max_len; at.H = H; at.D = D; at.cu_seqlens = cu_chunk_dev; at.scale = 1.0f / sqrtf(static_cast<float>(D));
     at.out = e->attn; at.ld_out = F; at.round_tf32 = 1;
+    ctx->attn_flops_hint = 4.0 * H * D * sum_len2;  // valid (query, key) pairs only
     if ((rc = launch_attention(ctx, false, e->qkv, e->qkv + F, e->qkv + 2 * F, 3LL * F, rows, at))) return rc;
     if ((rc = enc_linear(e, e->attn, L.wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE))) return rc;
     if ((rc = enc_norm(e, e->t, L.ln1_g, L.ln1_b, e->x2, rows))) return rc;
@@ -153,7 +154,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
   return GRILLY_OK;
 }
 
-struct ChunkPlan { int b0, b1, rows, max_len, cu_off; };
+struct ChunkPlan { int b0, b1, rows, max_len, cu_off; double sum_len2; };
 
 // Splits the batch into chunks of consecutive sentences and writes chunk-relative row offsets to cu_host.
 static void plan_chunks(const int* lengths, int B, int chunk_tokens, std::vector<ChunkPlan>& plan, int* cu_host, long long* total) {
@@ -161,13 +162,14 @@ static void plan_chunks(const int* lengths, int B, int chunk_tokens, std::vector
   long long tot = 0;
   int b = 0, off = 0;
   while (b < B) {
-    ChunkPlan c{b, b, 0, 0, off};
+    ChunkPlan c{b, b, 0, 0, off, 0.0};
     cu_host[off] = 0;
     while (c.b1 < B) {
       const int len = lengths[c.b1];
       if (chunk_tokens > 0 && c.b1 > c.b0 && c.rows + len > chunk_tokens) break;
       c.rows += len;
       c.max_len = std::max(c.max_len, len);
+      c.sum_len2 += static_cast<double>(len) * len;
       c.b1++;
       cu_host[off + (c.b1 - c.b0)] = c.rows;
     }
@@ -177,6 +179,20 @@ static void plan_chunks(const int* lengths, int B, int chunk_tokens, std::vector
     plan.push_back(c);
   }
   *total = tot;
+}
+
+extern "C" int grilly_plan_chunks(const int* lengths, int B, int chunk_tokens, int* chunk_bounds_out, int* cu_out,
+                                  long long* total_rows_out) {
+  if (!lengths || B <= 0 || !chunk_bounds_out || !cu_out) return GRILLY_ERR_INVALID_ARG;
+  for (int b = 0; b < B; ++b)
+    if (lengths[b] < 0) return GRILLY_ERR_INVALID_ARG;
+  std::vector<ChunkPlan> plan;
+  long long total = 0;
+  plan_chunks(lengths, B, chunk_tokens, plan, cu_out, &total);
+  for (size_t i = 0; i < plan.size(); ++i) chunk_bounds_out[i] = plan[i].b0;
+  chunk_bounds_out[plan.size()] = B;
+  if (total_rows_out) *total_rows_out = total;
+  return static_cast<int>(plan.size());
 }
 
 static int forward_device_nolock(grilly_encoder* e, const int* ids_dev, const int* lengths, int B, int S, float* out_dev,
@@ -208,7 +224,7 @@ static int forward_device_nolock(grilly_encoder* e, const int* ids_dev, const in
                                          static_cast<size_t>(c.b1 - c.b0) * e->cfg.hidden * sizeof(float), ctx->stream));
       continue;
     }
-    if ((rc = run_chunk(e, ids_dev, e->cu_dev + c.cu_off, c.b0, c.b1, S, c.rows, std::max(c.max_len, 1), out_dev, row0))) return rc;
+    if ((rc = run_chunk(e, ids_dev, e->cu_dev + c.cu_off, c.b0, c.b1, S, c.rows, std::max(c.max_len, 1), out_dev, row0, c.sum_len2))) return rc;
     row0 += c.rows;
   }
   e->last_rows = total;

@@ -35,7 +35,13 @@ static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& a
   }
   const int tiles = args.num_m_tiles * args.num_n_tiles;
   const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
+  const double out_cols = args.swiglu_pairs ? args.N / 2.0 : args.N;
+  const double bytes = static_cast<double>(ELT) * (static_cast<double>(args.M) * args.K + static_cast<double>(args.N) * args.K) +
+                       (args.bias ? 4.0 * args.N : 0.0) + static_cast<double>(args.M) * out_cols * (args.out_bf16 ? 2.0 : 4.0) +
+                       (args.residual ? 4.0 * args.M * out_cols : 0.0);
+  const int pi = prof_begin(ctx, PROF_GEMM, 2.0 * args.M * static_cast<double>(args.N) * args.K, bytes);
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, args);
+  prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;
@@ -57,6 +63,13 @@ static int pick_bn(int M, int N, int num_sms) {
   }
   return best_bn;
 }
+
+}  // namespace gb
+extern "C" int grilly_gemm_pick_tile(int M, int N, int num_sms) {
+  if (M <= 0 || N <= 0 || num_sms <= 0) return GRILLY_ERR_INVALID_ARG;
+  return gb::pick_bn(M, N, num_sms);
+}
+namespace gb {
 
 template <bool kBf16, bool kBMn>
 static int dispatch_bn(grilly_ctx* ctx, int bn, const void* a, const void* b, GemmArgs& args) {

@@ -53,6 +53,12 @@ struct grilly_ctx {
   uint64_t tmap_hits = 0, tmap_misses = 0;
   uint64_t launches = 0;
   std::unordered_set<const void*> smem_attr_done;  // kernels whose dynamic-smem limit is already raised
+  // optional per-kernel-class timing (CUDA events on the launching stream), see grilly_profile_begin/end
+  struct ProfRec { int cls; cudaEvent_t a, b; double flops, bytes; };
+  cudaEvent_t timer_a = nullptr, timer_b = nullptr;  // grilly_timer_start / grilly_timer_stop
+  bool profiling = false;
+  std::vector<ProfRec> prof;
+  double attn_flops_hint = -1.0;  // set by a caller that knows the true sequence lengths
   // RoPE tables, keyed by (S, D, base, scaling)
   struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };
   std::vector<RopeTable> rope_tables;
@@ -68,6 +74,11 @@ int set_error(grilly_ctx* ctx, int code, const std::string& msg);
       return gb::set_error(ctx, e__ == cudaErrorMemoryAllocation ? GRILLY_ERR_OOM : GRILLY_ERR_CUDA, \
                            std::string(#expr) + ": " + cudaGetErrorString(e__));                  \
   } while (0)
+
+enum { PROF_GEMM = 0, PROF_ATTN = 1, PROF_NORM = 2, PROF_EMBED = 3, PROF_POOL = 4, PROF_OTHER = 5, PROF_NCLASS = 6 };
+// Brackets one launch with events when profiling is on; algorithmic FLOPs / bytes are recorded with it.
+int prof_begin(grilly_ctx* ctx, int cls, double flops, double bytes);
+void prof_end(grilly_ctx* ctx, int idx);
 
 enum { TM_F32 = 0, TM_BF16 = 1 };
 enum { TM_SW128 = 0, TM_SW128_ATOM32 = 1 };  // 128-byte swizzle of 16-byte chunks, or of 32-byte chunks (tf32 MN-major)

@@ -18,10 +18,13 @@ int launch_norm(grilly_ctx* ctx, const NormArgs& a) {
   const bool aligned = (a.F % 4 == 0) && !(reinterpret_cast<uintptr_t>(a.x) & 15) && !(reinterpret_cast<uintptr_t>(a.y) & 15) &&
                        !(reinterpret_cast<uintptr_t>(a.residual) & 15) && !(reinterpret_cast<uintptr_t>(a.gamma) & 15) &&
                        !(reinterpret_cast<uintptr_t>(a.beta) & 15);
+  const double nbytes = static_cast<double>(a.rows) * a.F * (4.0 + (a.residual ? 4.0 : 0.0) + (a.y ? (a.out_bf16 ? 2.0 : 4.0) : 0.0));
+  const int pi = prof_begin(ctx, PROF_NORM, 8.0 * a.rows * a.F, nbytes);
   if (aligned && a.F <= 128 * 3) norm_rows_kernel<3><<<grid, 256, 0, ctx->stream>>>(a);
   else if (aligned && a.F <= 128 * 8) norm_rows_kernel<8><<<grid, 256, 0, ctx->stream>>>(a);
   else if (aligned && a.F <= 128 * 16) norm_rows_kernel<16><<<grid, 256, 0, ctx->stream>>>(a);
   else norm_rows_generic_kernel<<<grid, 256, 0, ctx->stream>>>(a);
+  prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;
@@ -79,8 +82,10 @@ int launch_embed(grilly_ctx* ctx, const EmbedArgs& a) {
   if (a.B <= 0 || a.S <= 0 || a.F <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "embed: sizes must be positive");
   if (a.F % 4 != 0 || a.F > 128 * 8) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "embed: hidden size must be a multiple of 4 and at most 1024");
   const int grid = grid_for(static_cast<long long>(a.B) * a.S, 8, ctx->num_sms);
+  const int pi = prof_begin(ctx, PROF_EMBED, 0.0, static_cast<double>(a.B) * a.S * (4.0 + 8.0 * a.F));
   if (a.F <= 128 * 3) embed_ln_kernel<3><<<grid, 256, 0, ctx->stream>>>(a);
   else embed_ln_kernel<8><<<grid, 256, 0, ctx->stream>>>(a);
+  prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;
@@ -90,7 +95,9 @@ int launch_pool(grilly_ctx* ctx, const PoolArgs& a) {
   if (a.B <= 0 || a.S <= 0 || a.F <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "mean_pool: sizes must be positive");
   const size_t smem = (static_cast<size_t>(a.F) + 8) * sizeof(float);
   if (smem > 48 * 1024) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "mean_pool: feature size too large");
+  const int pi = prof_begin(ctx, PROF_POOL, 0.0, static_cast<double>(a.B) * a.S * a.F * 4.0);
   pool_normalize_kernel<<<a.B, 128, smem, ctx->stream>>>(a);
+  prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;

@@ -193,6 +193,31 @@ class Device:
         for k in [k for k in self._weights if k[0] == ptr]:
             self._weights.pop(k)[1].free()
 
+    def timer_start(self) -> None:
+        """Record the start event of the device-side stopwatch on the context's stream."""
+        self.check(self.lib.grilly_timer_start(self.ctx))
+
+    def timer_stop(self) -> float:
+        """Record the stop event, wait for it and return the elapsed device time in milliseconds."""
+        ms = C.c_float(0)
+        self.check(self.lib.grilly_timer_stop(self.ctx, C.byref(ms)))
+        return ms.value
+
+    PROFILE_CLASSES = ("gemm", "attention", "norm", "embedding", "pooling", "other")
+
+    def profile_begin(self) -> None:
+        """Start bracketing every launch with CUDA events on the launching stream."""
+        self.check(self.lib.grilly_profile_begin(self.ctx))
+
+    def profile_end(self) -> dict:
+        """Stop and return {class: {launches, ms, flops, bytes}} summed over the bracketed launches."""
+        out = (C.c_double * (len(self.PROFILE_CLASSES) * 4))()
+        self.check(self.lib.grilly_profile_end(self.ctx, out))
+        res = {}
+        for i, name in enumerate(self.PROFILE_CLASSES):
+            res[name] = {"launches": int(out[4 * i]), "ms": out[4 * i + 1], "flops": out[4 * i + 2], "bytes": out[4 * i + 3]}
+        return res
+
     def pool_stats(self) -> dict:
         out = (C.c_uint64 * 8)()
         self.check(self.lib.grilly_pool_stats(self.ctx, out))

@@ -60,6 +60,17 @@ int grilly_sync(grilly_ctx* ctx);
 /* number of kernels this context has launched (monotonic) */
 int grilly_launch_count(grilly_ctx* ctx, uint64_t* count);
 
+/* Per-kernel-class timing with CUDA events on the launching stream (the reference has no profiler; its
+ * tutorials time with perf_counter, tutorials/02_fused_operations.py:29-39). Between begin and end every launch is
+ * bracketed by an event pair. out has 6 classes x 4 doubles: {launches, milliseconds, algorithmic FLOPs,
+ * algorithmic bytes} for class 0 GEMM, 1 attention, 2 norm, 3 embedding, 4 pooling, 5 other. */
+/* Device-side stopwatch: start records an event on the context's stream, stop records a second one, waits for it
+ * and returns the milliseconds between the two. */
+int grilly_timer_start(grilly_ctx* ctx);
+int grilly_timer_stop(grilly_ctx* ctx, float* ms);
+int grilly_profile_begin(grilly_ctx* ctx);
+int grilly_profile_end(grilly_ctx* ctx, double* out);
+
 /* ---- device pool, replaces BufferPool / VMABufferPool (backend/buffer_pool.py:466-651, 120-462;
  *      backend/vma_wrapper.py:268-437) with a stream-ordered cudaMallocAsync pool ------------- */
 /* backend/buffer_pool.py:534-562 acquire() */
@@ -181,6 +192,16 @@ int grilly_encoder_keep_hidden(grilly_encoder* enc, int on);
 /* final hidden states of the last forward (packed rows, fp32 [total_tokens][hidden]) for parity checks */
 int grilly_encoder_last_hidden(grilly_encoder* enc, float* out_host, long long max_rows, long long* rows);
 int grilly_encoder_destroy(grilly_encoder* enc);
+
+/* ---- host-side planning helpers (no GPU needed; exposed so the host logic can be tested on CPU) ------------- */
+/* N-tile (64/128/192/256) the GEMM launcher picks for an M x N output on a GPU with num_sms SMs. */
+int grilly_gemm_pick_tile(int M, int N, int num_sms);
+/* Splits B sentences with the given valid lengths into chunks of consecutive sentences of at most chunk_tokens
+ * packed rows (0 = one chunk; a single sentence longer than the limit gets a chunk of its own).
+ * chunk_bounds_out receives n_chunks+1 sentence indices, cu_out one run of chunk-relative row offsets per chunk
+ * (B + n_chunks ints in total). Returns the number of chunks, or a negative status. */
+int grilly_plan_chunks(const int* lengths, int B, int chunk_tokens, int* chunk_bounds_out, int* cu_out,
+                       long long* total_rows_out);
 
 #ifdef __cplusplus
 }

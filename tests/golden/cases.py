@@ -1,0 +1,60 @@
+"""Seeded inputs of the golden cases, shared by make_golden.py (which runs the reference on them) and by the
+tests (which run the oracle and the CUDA path on them). Only outputs are stored in hotpath_golden.npz."""
+from __future__ import annotations
+
+import numpy as np
+
+f32 = np.float32
+
+
+def linear_cfg0():
+    """BASELINE config 0: x (32,384) ~ N(0,1); W Xavier-uniform in the reference layout (1536,384); zero bias; seed 0."""
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((32, 384)).astype(f32)
+    lim = np.sqrt(6.0 / (384 + 1536))
+    w = rng.uniform(-lim, lim, size=(1536, 384)).astype(f32)
+    b = np.zeros(1536, f32)
+    x3 = rng.standard_normal((3, 5, 50)).astype(f32)
+    w3 = rng.standard_normal((21, 50)).astype(f32)
+    b3 = rng.standard_normal(21).astype(f32)
+    return dict(x=x, w=w, b=b, x3=x3, w3=w3, b3=b3)
+
+
+def rowops():
+    rng = np.random.default_rng(10)
+    return dict(
+        gemm_a=rng.standard_normal((40, 24)).astype(f32), gemm_b=rng.standard_normal((24, 36)).astype(f32),
+        ln_x=(rng.standard_normal((7, 11, 96)) * 3 + 1.5).astype(f32),
+        ln_g=rng.standard_normal(96).astype(f32), ln_b=rng.standard_normal(96).astype(f32),
+        sm_x=rng.standard_normal((13, 37)).astype(f32) * 4,
+        act_x=rng.standard_normal((9, 64)).astype(f32) * 3,
+    )
+
+
+def attention_cfg1(batch=2):
+    """BASELINE config 1 at a reduced batch: q, k, v (batch, 64, 8, 64) in the reference's (B,S,H,D) layout, seed 1."""
+    rng = np.random.default_rng(1)
+    q, k, v = (rng.standard_normal((batch, 64, 8, 64)).astype(f32) for _ in range(3))
+    lens = np.array([64, 17, 1, 40])[:batch]
+    mask = (np.arange(64)[None, :] < lens[:, None]).astype(f32)
+    qs, ks, vs = (rng.standard_normal((2, 50, 12, 32)).astype(f32) for _ in range(3))
+    pid = rng.integers(0, 200, size=(batch, 64)).astype(np.int32)
+    return dict(q=q, k=k, v=v, mask=mask, q32=qs, k32=ks, v32=vs, pid=pid)
+
+
+def encoder_layer_cfg2():
+    """One post-LN BERT layer of the MiniLM shape (hidden 384, 12 heads, ffn 1536), std 0.02, seed 2."""
+    rng = np.random.default_rng(2)
+    hid, ffn, B, S = 384, 1536, 3, 24
+    n = lambda *s: (rng.standard_normal(s) * 0.02).astype(f32)  # noqa: E731
+    lw = {
+        "attn_q_weight": n(hid, hid), "attn_q_bias": n(hid), "attn_k_weight": n(hid, hid), "attn_k_bias": n(hid),
+        "attn_v_weight": n(hid, hid), "attn_v_bias": n(hid), "attn_out_weight": n(hid, hid), "attn_out_bias": n(hid),
+        "attn_ln_gamma": (1 + n(hid)).astype(f32), "attn_ln_beta": n(hid),
+        "ffn_w1": n(ffn, hid), "ffn_b1": n(ffn), "ffn_w2": n(hid, ffn), "ffn_b2": n(hid),
+        "ffn_ln_gamma": (1 + n(hid)).astype(f32), "ffn_ln_beta": n(hid),
+    }
+    x = rng.standard_normal((B, S, hid)).astype(f32)
+    lens = np.array([24, 9, 16])
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(f32)
+    return dict(lw=lw, x=x, mask=mask, num_heads=12)

@@ -1,0 +1,97 @@
+"""Parity of the tcgen05 flash-attention kernel (and its RoPE variant) with the reference's CPU attention."""
+import numpy as np
+import pytest
+
+import cases
+from conftest import TOL_BF16, TOL_TF32
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config1_against_reference_outputs(backend, golden):
+    a = cases.attention_cfg1()
+    o = backend.attention.flash_attention2(a["q"], a["k"], a["v"], 8, 64)
+    assert o.dtype == np.float32 and o.shape == a["q"].shape
+    assert O.rel_l2(o, golden["att_o"]) < TOL_TF32
+    om = backend.attention.flash_attention2(a["q"], a["k"], a["v"], 8, 64, mask=a["mask"])
+    assert O.rel_l2(om, golden["att_o_masked"]) < TOL_TF32
+    o32 = backend.attention.flash_attention2(a["q32"], a["k32"], a["v32"])
+    assert O.rel_l2(o32, golden["att32_o"]) < TOL_TF32
+    # 3-D (B, S, H*D) form and the explicit scale argument
+    B, S, H, D = a["q"].shape
+    o3 = backend.attention.flash_attention2(a["q"].reshape(B, S, H * D), a["k"].reshape(B, S, H * D),
+                                            a["v"].reshape(B, S, H * D), H, D, scale=0.125)
+    assert np.array_equal(o3, o)
+
+
+def test_config1_full_batch(backend):
+    rng = np.random.default_rng(1)
+    q, k, v = (rng.standard_normal((32, 64, 8, 64)).astype(np.float32) for _ in range(3))
+    o = backend.attention.flash_attention2(q, k, v, 8, 64)
+    ref = O.flash_attention2(q, k, v)
+    assert O.rel_l2(o, ref) < TOL_TF32
+    # indices derived from the output: per (b, s, h) argmax over the head dim
+    assert (o.argmax(-1) == ref.argmax(-1)).mean() > 0.995
+
+
+@pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 32), (2, 17, 3, 32), (2, 128, 12, 32), (1, 129, 2, 64), (2, 300, 4, 64),
+                                     (1, 513, 2, 32)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ragged_lengths_masks_causal(backend, B, S, H, D, causal):
+    rng = np.random.default_rng(S * 3 + D)
+    q, k, v = (rng.standard_normal((B, S, H, D)).astype(np.float32) for _ in range(3))
+    lens = rng.integers(1, S + 1, size=B)
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.float32)
+    o = backend.attention.flash_attention2(q, k, v, mask=mask, causal=causal)
+    assert np.isfinite(o).all()
+    assert O.rel_l2(o, O.flash_attention2(q, k, v, mask=mask, causal=causal)) < TOL_TF32
+
+
+def test_mask_with_holes_and_fully_masked_row(backend):
+    rng = np.random.default_rng(11)
+    q, k, v = (rng.standard_normal((3, 40, 2, 32)).astype(np.float32) for _ in range(3))
+    mask = (rng.random((3, 40)) > 0.4).astype(np.float32)
+    mask[1] = 0  # every key masked: the reference's scores all become -1e9 -> uniform weights
+    o = backend.attention.flash_attention2(q, k, v, mask=mask)
+    assert O.rel_l2(o, O.flash_attention2(q, k, v, mask=mask)) < TOL_TF32
+
+
+@pytest.mark.parametrize("style", ["interleaved", "rotate_half"])
+@pytest.mark.parametrize("D", [32, 64])
+def test_rope_variant(backend, style, D):
+    rng = np.random.default_rng(D)
+    q, k, v = (rng.standard_normal((2, 200, 4, D)).astype(np.float32) for _ in range(3))
+    o = backend.attention.flash_attention2_rope(q, k, v, causal=True, rope_base=10000.0, rope_style=style)
+    ref = O.flash_attention2_rope(q, k, v, causal=True, rope_style=style)
+    assert O.rel_l2(o, ref) < TOL_TF32
+    o2 = backend.attention.flash_attention2(q, k, v, use_rope=True, rope_scaling=2.0, rope_base=500.0, rope_style=style)
+    assert O.rel_l2(o2, O.flash_attention2_rope(q, k, v, rope_scaling=2.0, rope_base=500.0, rope_style=style)) < TOL_TF32
+
+
+def test_apply_rope_against_reference_outputs(backend, golden):
+    a = cases.attention_cfg1()
+    q1 = a["q"][:1]
+    assert O.rel_l2(backend.attention.apply_rope(q1), golden["rope_half"]) < 1e-5
+    out = backend.attention.apply_rope(q1, a["pid"][:1], 10000.0, 2.0)
+    assert O.rel_l2(out, golden["rope_half_pid"]) < 1e-4
+
+
+def test_bf16_decoder_shapes(backend_bf16):
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((1, 700, 4, 64)).astype(np.float32) for _ in range(3))
+    o = backend_bf16.attention.flash_attention2_rope(q, k, v, causal=True)
+    assert O.rel_l2(o, O.flash_attention2_rope(q, k, v, causal=True)) < TOL_BF16
+    q, k, v = (rng.standard_normal((1, 256, 2, 128)).astype(np.float32) for _ in range(3))
+    assert O.rel_l2(backend_bf16.attention.flash_attention2(q, k, v), O.flash_attention2(q, k, v)) < TOL_BF16
+
+
+def test_errors(backend):
+    z = np.zeros((1, 4, 2, 48), np.float32)
+    with pytest.raises(Exception):
+        backend.attention.flash_attention2(z, z, z)  # head_dim 48 is not supported: raises, never falls back
+    with pytest.raises(ValueError):
+        backend.attention.flash_attention2(np.zeros((1, 4, 64), np.float32), np.zeros((1, 4, 64), np.float32),
+                                           np.zeros((1, 4, 64), np.float32))
+    with pytest.raises(NotImplementedError):
+        backend.attention.attention_scores(z, z, 2, 48)

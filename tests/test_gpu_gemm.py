@@ -1,0 +1,171 @@
+"""Parity of the tcgen05 GEMM family with the reference's CPU implementation (oracle + golden vectors),
+called through the C ABI. Tolerances: rel-L2 <= 2e-3 in tf32 mode, <= 1e-2 in bf16 mode; argmax identical."""
+import numpy as np
+import pytest
+
+import cases
+from conftest import TOL_BF16, TOL_TF32
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_linear_config0_against_reference_outputs(backend, golden):
+    c = cases.linear_cfg0()
+    y = backend.fnn.linear(c["x"], c["w"], c["b"])
+    assert y.dtype == np.float32 and y.shape == (32, 1536)
+    assert O.rel_l2(y, golden["lin_y"]) < TOL_TF32
+    assert np.array_equal(y.argmax(-1), golden["lin_y"].argmax(-1))
+    for name, fn in (("gelu", backend.fnn.fused_linear_gelu), ("silu", backend.fnn.fused_linear_silu),
+                     ("relu", backend.fnn.fused_linear_relu)):
+        out = fn(c["x"][:8], c["w"], c["b"])
+        ref = golden[f"lin_{name}_y8"]
+        assert O.rel_l2(out, ref) < TOL_TF32, name
+        assert np.array_equal(out.argmax(-1), ref.argmax(-1)), name
+    # 3-D input, ragged sizes (K = 50 is padded to 52 at the boundary), with and without bias
+    assert O.rel_l2(backend.fnn.linear(c["x3"], c["w3"], c["b3"]), golden["lin3_y"]) < TOL_TF32
+    y3 = backend.fnn.linear(c["x3"], c["w3"])
+    assert y3.shape == (3, 5, 21) and O.rel_l2(y3, golden["lin3_nobias_y"]) < TOL_TF32
+
+
+def test_linear_config0_batch_4096(backend):
+    c = cases.linear_cfg0()
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((4096, 384)).astype(np.float32)
+    y = backend.fnn.fused_linear_gelu(x, c["w"], c["b"])
+    ref = O.fused_linear_gelu(x, c["w"], c["b"])
+    assert O.rel_l2(y, ref) < TOL_TF32
+    # top-5 indices per row: identical wherever the oracle's own ranking is not a near-tie within tf32 noise
+    top_ref = np.argsort(-ref, axis=-1)[:, :5]
+    top_gpu = np.argsort(-y, axis=-1)[:, :5]
+    srt = -np.sort(-ref, axis=-1)[:, :6]
+    clear = (np.abs(np.diff(srt, axis=-1)) > 2e-3 * np.abs(srt[:, :1])).all(-1)
+    assert clear.mean() > 0.5
+    assert np.array_equal(top_gpu[clear], top_ref[clear])
+    assert (y.argmax(-1) == ref.argmax(-1)).mean() > 0.995
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 4), (7, 13, 20), (128, 64, 32), (129, 65, 36), (300, 200, 100), (1000, 1152, 384),
+                                   (513, 384, 1536), (64, 2816, 1024)])
+def test_linear_edge_shapes(backend, M, N, K):
+    rng = np.random.default_rng(M * 7 + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    assert O.rel_l2(backend.fnn.linear(x, w, b), O.linear(x, w, b)) < TOL_TF32
+    assert O.rel_l2(backend.fnn.fused_linear_silu(x, w), O.fused_linear_silu(x, w)) < TOL_TF32
+
+
+@pytest.mark.parametrize("bn", [64, 128, 192, 256])
+def test_every_n_tile(backend, bn, monkeypatch):
+    monkeypatch.setenv("GRILLY_GEMM_BN", str(bn))
+    rng = np.random.default_rng(bn)
+    x = rng.standard_normal((700, 384)).astype(np.float32)
+    w = (rng.standard_normal((1000, 384)) / 20).astype(np.float32)
+    assert O.rel_l2(backend.fnn.fused_linear_relu(x, w), O.fused_linear_relu(x, w)) < TOL_TF32
+
+
+def test_linear_is_deterministic_and_weight_cache_is_used(backend):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((256, 384)).astype(np.float32)
+    w = rng.standard_normal((384, 384)).astype(np.float32)
+    before = backend.fnn.buffer_pool.get_stats()["cached_weights"]
+    a = backend.fnn.linear(x, w)
+    b = backend.fnn.linear(x, w)
+    assert np.array_equal(a, b)
+    assert backend.fnn.buffer_pool.get_stats()["cached_weights"] == before + 1
+    # an in-place change is picked up after invalidate()
+    w *= 2
+    backend.invalidate(w)
+    assert O.rel_l2(backend.fnn.linear(x, w), 2 * a) < 1e-6
+
+
+def test_non_contiguous_weight_view(backend):
+    # utils/pytorch_ops.py:48 passes other.T, a strided view, as the weight
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((64, 128)).astype(np.float32)
+    other = rng.standard_normal((128, 96)).astype(np.float32)
+    assert O.rel_l2(backend.fnn.linear(x, other.T), O.linear(x, other.T)) < TOL_TF32
+
+
+def test_shape_errors(backend):
+    with pytest.raises(ValueError):
+        backend.fnn.linear(np.zeros((4, 8), np.float32), np.zeros((3, 9), np.float32))
+    with pytest.raises(AssertionError):
+        backend.fnn.gemm(np.zeros((4, 8), np.float32), np.zeros((9, 3), np.float32))
+
+
+def test_fused_qkv_projection(backend):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((2, 50, 384)).astype(np.float32)
+    ws = [(rng.standard_normal((384, 384)) * 0.05).astype(np.float32) for _ in range(3)]
+    bs = [rng.standard_normal(384).astype(np.float32) for _ in range(3)]
+    out = backend.fnn.fused_qkv_projection(x, np.concatenate(ws, 0), np.concatenate(bs, 0), 12, 32)
+    assert out.shape == (2, 50, 1152)
+    assert O.rel_l2(out, O.fused_qkv_projection(x, *ws, *bs)) < TOL_TF32
+
+
+@pytest.mark.parametrize("mode", ["layer", "rms"])
+def test_fused_layernorm_linear(backend, mode):
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((300, 384)) * 2 + 0.7).astype(np.float32)
+    g, bt = (1 + 0.1 * rng.standard_normal(384)).astype(np.float32), (0.1 * rng.standard_normal(384)).astype(np.float32)
+    w, b = (rng.standard_normal((512, 384)) * 0.05).astype(np.float32), rng.standard_normal(512).astype(np.float32)
+    out = backend.fnn.fused_layernorm_linear(x, g, bt, w, b, eps=1e-5, mode=mode)
+    ref = O.fused_layernorm_linear(x, g, bt, w, b) if mode == "layer" else O.linear(O.rmsnorm(x, g), w, b)
+    assert O.rel_l2(out, ref) < TOL_TF32
+    out2 = backend.fnn.fused_layernorm_linear(x, g, bt, w, b, eps=1e-5, mode=mode)
+    assert np.array_equal(out, out2)
+
+
+def test_fused_swiglu(backend):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((200, 256)).astype(np.float32)
+    wg, wu = ((rng.standard_normal((352, 256)) / 16).astype(np.float32) for _ in range(2))
+    out = backend.fnn.fused_swiglu(x, wg, wu)
+    assert out.shape == (200, 352)
+    assert O.rel_l2(out, O.fused_swiglu(x, wg, wu)) < TOL_TF32
+    bg, bu = rng.standard_normal(352).astype(np.float32), rng.standard_normal(352).astype(np.float32)
+    assert O.rel_l2(backend.fnn.fused_swiglu(x, wg, wu, bg, bu), O.fused_swiglu(x, wg, wu, bg, bu)) < TOL_TF32
+
+
+def test_gemm_mnk_golden_and_sweep(backend, golden):
+    r = cases.rowops()
+    assert O.rel_l2(backend.fnn.gemm(r["gemm_a"], r["gemm_b"]), golden["gemm_c"]) < TOL_TF32
+    for n in (1024, 2048):
+        rng = np.random.default_rng(4 + int(np.log2(n)))
+        a, b = rng.standard_normal((n, n)).astype(np.float32), rng.standard_normal((n, n)).astype(np.float32)
+        assert O.rel_l2(backend.fnn.gemm(a, b), O.gemm(a, b)) < TOL_TF32
+    for m, k, n in ((5, 7, 9), (130, 70, 258), (64, 33, 100)):
+        rng = np.random.default_rng(m)
+        a, b = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32)
+        c = backend.fnn.gemm(a, b)
+        assert c.shape == (m, n) and O.rel_l2(c, O.gemm(a, b)) < TOL_TF32
+
+
+def test_gemm_mnk_full_size_property(backend):
+    """At the sweep's large sizes the O(N^3) oracle is too slow: check C v = A (B v) in float64 for random v
+    (a checksum that any wrong tile, k-block or swizzle would break) on the operands the tensor core sees."""
+    n = 8192
+    rng = np.random.default_rng(4 + 13)
+    a, b = rng.standard_normal((n, n)).astype(np.float32), rng.standard_normal((n, n)).astype(np.float32)
+    c = backend.fnn.gemm(a, b)
+    v = rng.standard_normal((n, 4))
+    lhs = c.astype(np.float64) @ v
+    rhs = a.astype(np.float64) @ (b.astype(np.float64) @ v)
+    assert O.rel_l2(lhs, rhs) < TOL_TF32
+    # row and column checksums localise an error to a tile
+    u = rng.standard_normal((4, n))
+    assert O.rel_l2(u @ c.astype(np.float64), (u @ a.astype(np.float64)) @ b.astype(np.float64)) < TOL_TF32
+
+
+def test_bf16_mode(backend_bf16):
+    c = cases.linear_cfg0()
+    y = backend_bf16.fnn.fused_linear_gelu(c["x"], c["w"], c["b"])
+    assert O.rel_l2(y, O.fused_linear_gelu(c["x"], c["w"], c["b"])) < TOL_BF16
+    rng = np.random.default_rng(3)
+    a, b = rng.standard_normal((1024, 1024)).astype(np.float32), rng.standard_normal((1024, 1024)).astype(np.float32)
+    assert O.rel_l2(backend_bf16.fnn.gemm(a, b), O.gemm(a, b)) < TOL_BF16
+    x = rng.standard_normal((300, 1024)).astype(np.float32)
+    wg, wu = ((rng.standard_normal((2816, 1024)) * 0.02).astype(np.float32) for _ in range(2))
+    assert O.rel_l2(backend_bf16.fnn.fused_swiglu(x, wg, wu), O.fused_swiglu(x, wg, wu)) < TOL_BF16
