@@ -11,8 +11,8 @@
 // One CTA handles 128 queries of one (sequence, head). Warp 4 (one lane) issues
 // TMA loads and tcgen05.mma; warps 0..3 own one query row per thread:
 //   S = Q K_j^T  (smem x smem -> TMEM, 128 fp32 columns)
-//   row max / exp2 / row sum in registers, P written to swizzled shared memory
-//   O_j = P V_j  (V is the MN-major B operand, read as loaded) -> TMEM
+//   row max / exp2 / row sum in registers, P written back over S in TMEM
+//   O_j = P V_j  (P read from TMEM, V is the MN-major smem operand, read as loaded) -> TMEM
 //   O += O_j with the running-max rescale kept in registers.
 // RoPE (interleaved or rotate-half pairs) is applied to the Q and K tiles in
 // shared memory right after the TMA load, before the first MMA reads them.
@@ -33,12 +33,12 @@ template <int D, bool kBf16>
 struct AttnCfg {
   static constexpr int ELT = kBf16 ? 2 : 4;
   static constexpr int NCH = D * ELT / 128;            // 128-B chunks per Q/K/V row
-  static constexpr int PCH = ATTN_TILE * ELT / 128;    // 128-B chunks per P row
   static_assert(D * ELT % 128 == 0 && NCH >= 1 && NCH <= 2, "head_dim*elt must be 128 or 256 bytes");
   static constexpr int Q_BYTES = NCH * ATTN_CHUNK_BYTES;
-  static constexpr int P_BYTES = PCH * ATTN_CHUNK_BYTES;
-  static constexpr int SMEM_BYTES = 3 * Q_BYTES + P_BYTES + 1024 + 128;
-  static constexpr int TMEM_COLS = 256;                // S: 128 columns, O_j: D columns at +128
+  static constexpr int SMEM_BYTES = 3 * Q_BYTES + 1024 + 128;
+  // TMEM columns: S (fp32 scores, overwritten in place by P in the MMA operand precision) at [0,128),
+  // O_j at [128, 128 + D). Two CTAs of 256 columns fit the SM's 512.
+  static constexpr int TMEM_COLS = 256;
 };
 
 // Rotate one row of a Q or K tile in place in swizzled shared memory.
@@ -120,11 +120,10 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   using Cfg = AttnCfg<D, kBf16>;
   constexpr int ELT = Cfg::ELT;
   constexpr int NCH = Cfg::NCH;
-  constexpr int PCH = Cfg::PCH;
   constexpr int CHE = 128 / ELT;            // elements per 128-B chunk
   constexpr int UMMA_K = 32 / ELT;
   constexpr uint32_t IDESC_S = make_idesc(kBf16, 128, ATTN_TILE, false, false);  // Q (K-major) x K (K-major)
-  constexpr uint32_t IDESC_O = make_idesc(kBf16, 128, D, false, true);           // P (K-major) x V (MN-major)
+  constexpr uint32_t IDESC_O = make_idesc(kBf16, 128, D, false, true);           // P (TMEM)    x V (MN-major)
 
   const int qtile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   int row0, L;
@@ -139,19 +138,19 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   if (q0 >= L) return;  // uniform for the CTA; nothing allocated yet
   int n_kv = (L + ATTN_TILE - 1) / ATTN_TILE;
   if (args.causal) n_kv = min(n_kv, qtile + 1);
+  const int q_rows = min(ATTN_TILE, L - q0);   // valid query rows of this tile
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::Q_BYTES;
   uint8_t* sV = sK + Cfg::Q_BYTES;
-  uint8_t* sP = sV + Cfg::Q_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + Cfg::Q_BYTES);
   uint64_t* bar_q = bars + 0;     // Q tile landed
   uint64_t* bar_k = bars + 1;     // K tile landed
   uint64_t* bar_v = bars + 2;     // V tile landed
   uint64_t* bar_s = bars + 3;     // S = Q K^T complete in TMEM
-  uint64_t* bar_p = bars + 4;     // P written (and S, O_j of the previous step fully read)
+  uint64_t* bar_p = bars + 4;     // P written to TMEM (and O_j of the previous step fully read): one arrive per warp
   uint64_t* bar_o = bars + 5;     // O_j = P V complete in TMEM
   uint64_t* bar_rq = bars + 6;    // Q rotated (RoPE)
   uint64_t* bar_rk = bars + 7;    // K rotated (RoPE)
@@ -164,10 +163,11 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 128); mbar_init(bar_o, 1);
-    mbar_init(bar_rq, 128); mbar_init(bar_rk, 128);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
+    mbar_init(bar_rq, 4); mbar_init(bar_rk, 4);
     *abort_flag = 0;
     fence_mbar_init();
+    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
   }
   if (warp == 4) {
     tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
@@ -204,6 +204,9 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       if (!ok) ATTN_FAIL();
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
+        const int kv_len = min(ATTN_TILE, L - j * ATTN_TILE);           // valid keys of this step
+        const int n_s = (kv_len + 15) & ~15;                             // score columns actually computed
+        const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
         if (!mbar_wait(rope ? bar_rk : bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
         tc_fence_after();
         // S = Q K_j^T : D/UMMA_K k-steps of 32 B, walking the 128-B chunks
@@ -212,7 +215,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
           const uint64_t adesc = make_smem_desc_sw128(smem_u32(sQ) + chunk * ATTN_CHUNK_BYTES + off, 16, 1024);
           const uint64_t bdesc = make_smem_desc_sw128(smem_u32(sK) + chunk * ATTN_CHUNK_BYTES + off, 16, 1024);
-          umma_ss<kBf16>(tmem_s, adesc, bdesc, IDESC_S, ks != 0 ? 1u : 0u);
+          umma_ss<kBf16>(tmem_s, adesc, bdesc, idesc_s, ks != 0 ? 1u : 0u);
         }
         umma_commit(bar_s);
         if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
@@ -225,15 +228,12 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         if (!mbar_wait(bar_p, ph, abort_flag)) { ATTN_FAIL(); break; }
         if (!mbar_wait(bar_v, ph, abort_flag)) { ATTN_FAIL(); break; }
         tc_fence_after();
-        // O_j = P V_j : 128/UMMA_K k-steps over the keys
-#pragma unroll
-        for (int ks = 0; ks < ATTN_TILE / UMMA_K; ++ks) {
-          const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
-          const uint64_t adesc = make_smem_desc_sw128(smem_u32(sP) + chunk * ATTN_CHUNK_BYTES + off, 16, 1024);
-          // V chunk c holds head-dim columns [c*CHE, (c+1)*CHE) for all 128 keys (rows):
-          // MN-major with LBO = chunk stride (tf32: the 32-byte-atom swizzle, see make_smem_desc_mn).
+        // O_j = P V_j : P from TMEM (8 columns per k-step in either precision), V as loaded (MN-major);
+        // only the k-steps that cover valid keys are issued (P is zero-filled up to a multiple of 32 keys)
+        const int ksteps = (kv_len + UMMA_K - 1) / UMMA_K;
+        for (int ks = 0; ks < ksteps; ++ks) {
           const uint64_t bdesc = make_smem_desc_mn<kBf16>(smem_u32(sV) + ks * (UMMA_K * 128), ATTN_CHUNK_BYTES);
-          umma_ss<kBf16>(tmem_o, adesc, bdesc, IDESC_O, ks != 0 ? 1u : 0u);
+          umma_ts<kBf16>(tmem_o, tmem_s + ks * 8, bdesc, IDESC_O, ks != 0 ? 1u : 0u);
         }
         umma_commit(bar_o);
         if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
@@ -249,6 +249,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     // ---------------------------------------------------------- softmax / output threads
     const int t = threadIdx.x;            // query row inside the tile, also the TMEM lane
     const int qi = q0 + t;                // query position in its sequence
+    const bool warp_active = warp * 32 < q_rows;   // warps whose 32 rows are all padding only keep the barriers moving
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float kLog2e = 1.4426950408889634f;
     float o_acc[D];
@@ -262,109 +263,105 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       if (mbar_wait(bar_q, 0, abort_flag)) {
         rope_row_inplace<D, kBf16>(sQ, t, min(qi, args.S - 1), args);
         fence_proxy_async_smem();
-        mbar_arrive(bar_rq);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rq);
       } else { ATTN_FAIL(); ok = false; }
     }
 
     for (int j = 0; j < n_kv && ok; ++j) {
       const uint32_t ph = j & 1;
       const int k0 = j * ATTN_TILE;
+      const int kv_len = min(ATTN_TILE, L - k0);
+      const int nchunks = (kv_len + 31) >> 5;      // 32-key chunks that hold at least one valid key
       if (rope) {
         if (!mbar_wait(bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
         rope_row_inplace<D, kBf16>(sK, t, min(k0 + t, args.S - 1), args);
         fence_proxy_async_smem();
-        mbar_arrive(bar_rk);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rk);
       }
       if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
       tc_fence_after();
 
-      // ---- pass 1: row maximum of the masked, scaled scores
-      float m_tile = -INFINITY;
+      float alpha = 1.f, l_tile = 0.f;
+      if (warp_active) {
+        // ---- pass 1: row maximum of the masked, scaled scores
+        float m_tile = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < ATTN_TILE / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = k0 + c * 32 + i;
-          float s = __uint_as_float(r[i]) * args.scale;
-          if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
-          if (args.causal && kidx > qi) s = -1e9f;
-          if (kidx >= L) s = -INFINITY;
-          m_tile = fmaxf(m_tile, s);
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = k0 + c * 32 + i;
+            float s = __uint_as_float(r[i]) * args.scale;
+            if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
+            if (args.causal && kidx > qi) s = -1e9f;
+            if (kidx >= L) s = -INFINITY;
+            m_tile = fmaxf(m_tile, s);
+          }
         }
-      }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float alpha = exp2f((m_run - m_new) * kLog2e);  // 0 on the first step (m_run = -inf)
-      const float m_l2 = m_new * kLog2e;
+        const float m_new = fmaxf(m_run, m_tile);
+        alpha = exp2f((m_run - m_new) * kLog2e);  // 0 on the first step (m_run = -inf)
+        const float m_l2 = m_new * kLog2e;
+        m_run = m_new;
 
-      // ---- pass 2: p = exp(s - m), row sum, P -> swizzled shared memory (K-major A operand)
-      float l_tile = 0.f;
+        // ---- pass 2: p = exp(s - m) in the MMA operand precision, row sum, P written over S in TMEM
 #pragma unroll 1
-      for (int c = 0; c < ATTN_TILE / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        float p[32];
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          float p[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = k0 + c * 32 + i;
-          float s = __uint_as_float(r[i]) * args.scale;
-          if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
-          if (args.causal && kidx > qi) s = -1e9f;
-          if (kidx >= L) s = -INFINITY;
-          float e = exp2f(s * kLog2e - m_l2);
-          if constexpr (kBf16) e = __bfloat162float(__float2bfloat16(e));
-          else e = round_to_tf32(e);
-          p[i] = e;
-          l_tile += e;
-        }
-        if constexpr (kBf16) {
-          // 32 keys = 64 B = 4 pieces of 8; chunk = (c*32)/64, piece within chunk = ((c*32)%64)/8 + q
-          const int chunk = (c * 32) / CHE;
-          const int piece0 = ((c * 32) % CHE) / 8;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(p[8 * q + 0], p[8 * q + 1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(p[8 * q + 2], p[8 * q + 3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(p[8 * q + 4], p[8 * q + 5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(p[8 * q + 6], p[8 * q + 7]);
-            uint4 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-            pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-            const int within = piece0 + q;
-            *reinterpret_cast<uint4*>(sP + chunk * ATTN_CHUNK_BYTES + t * 128 + ((within ^ (t & 7)) << 4)) = pk;
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = k0 + c * 32 + i;
+            float s = __uint_as_float(r[i]) * args.scale;
+            if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
+            if (args.causal && kidx > qi) s = -1e9f;
+            if (kidx >= L) s = -INFINITY;
+            float e = exp2f(s * kLog2e - m_l2);
+            if constexpr (kBf16) e = __bfloat162float(__float2bfloat16(e));
+            else e = round_to_tf32(e);
+            p[i] = e;
+            l_tile += e;
           }
-        } else {
-          // 32 keys = 128 B = one full chunk row: 8 pieces of 4
+          if constexpr (kBf16) {
+            // two bf16 per 32-bit column (even key in the low half): chunk c -> columns [16c, 16c+16).
+            // In-place is safe in increasing c: those columns hold scores of chunk c/2, already consumed.
+            uint32_t pk[16];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            uint4 pk;
-            pk.x = __float_as_uint(p[4 * q + 0]); pk.y = __float_as_uint(p[4 * q + 1]);
-            pk.z = __float_as_uint(p[4 * q + 2]); pk.w = __float_as_uint(p[4 * q + 3]);
-            *reinterpret_cast<uint4*>(sP + c * ATTN_CHUNK_BYTES + t * 128 + ((q ^ (t & 7)) << 4)) = pk;
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+            tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
+          } else {
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pk[i] = __float_as_uint(p[i]);
+            tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
           }
         }
+        tmem_st_wait();
       }
-      fence_proxy_async_smem();   // P visible to the tensor core's reads
-      tc_fence_before();          // and this thread's TMEM reads are complete
-      mbar_arrive(bar_p);
+      tc_fence_before();          // this thread's TMEM reads and writes are ordered before the MMA that follows the barrier
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
 
       l_run = l_run * alpha + l_tile;
-      m_run = m_new;
 #pragma unroll
       for (int d = 0; d < D; ++d) o_acc[d] *= alpha;
 
       if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
       tc_fence_after();
+      if (warp_active) {
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+        }
       }
       tc_fence_before();
     }

@@ -6,7 +6,7 @@
 //
 // One CTA per SM walks output tiles of 128 x BN. Warp 0 feeds a ring of shared
 // memory stages with TMA, warp 1 issues tcgen05.mma into one of two TMEM
-// accumulators, warps 2..5 drain the other accumulator (tcgen05.ld), apply the
+// accumulators, warps 2..9 drain the other accumulator (tcgen05.ld), apply the
 // fused epilogue and store. Element type is fp32 consumed as tf32
 // (kind::tf32) or bf16 (kind::f16); accumulation is always fp32.
 #pragma once
@@ -29,12 +29,15 @@ __device__ __forceinline__ float round_to_tf32(float x) {
 }
 
 __device__ __forceinline__ float act_gelu_tanh(float x) {
-  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), with tanh(u) = 1 - 2/(1+exp(2u))
-  float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  u = fminf(fmaxf(u, -15.f), 15.f);
-  float e = __expf(2.f * u);
-  float t = 1.f - __fdividef(2.f, 1.f + e);
-  return 0.5f * x * (1.f + t);
+  // 0.5 x (1 + tanh(u)) == x * sigmoid(2u) == x / (1 + 2^(-2u log2 e)),  u = sqrt(2/pi) (x + 0.044715 x^3)
+  const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  const float k3 = k1 * 0.044715f;
+  const float t = x * fmaf(k3, x * x, k1);
+  return __fdividef(x, 1.0f + exp2f(t));  // t -> +inf gives x/inf = 0, t -> -inf gives x
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&p);
 }
 __device__ __forceinline__ float act_silu(float x) {
   float xc = fminf(fmaxf(x, -88.f), 88.f);
@@ -64,7 +67,7 @@ struct GemmCfg {
   static_assert(BN % 32 == 0, "epilogue drains 32 columns at a time");
 };
 
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 
 template <int BN, bool kBf16, bool kBMnMajor>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -99,7 +102,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -190,13 +193,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps per TMEM lane quadrant; each takes every other 32-column chunk of the accumulator.
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;          // 0 or 1: which chunks of the tile this warp drains
     int it = 0;
-    const bool vec_ok = !args.out_bf16 && !args.swiglu_pairs && (args.N % 4 == 0) && (args.ld_out % 4 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);
-    const bool res_vec_ok = args.residual && (args.ld_res % 4 == 0) && (args.N % 4 == 0) &&
-                            ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
+    const bool out_al16 = (reinterpret_cast<uintptr_t>(args.out) & 15) == 0;
+    const bool vec_ok = !args.out_bf16 && (args.ld_out % 4 == 0) && out_al16;
+    const bool vec8_ok = args.out_bf16 && (args.ld_out % 8 == 0) && out_al16;
+    const bool res_vec_ok = args.residual && (args.ld_res % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
+    const bool bias_vec_ok = args.bias && ((reinterpret_cast<uintptr_t>(args.bias) & 15) == 0);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int m_blk = tile / args.num_n_tiles;
       const int n_blk = tile % args.num_n_tiles;
@@ -217,7 +223,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half; c < BN / 32; c += 2) {
         uint32_t r[32];
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the lane-dependent skip below
         tmem_ld_32x32(taddr_row + c * 32, r);
@@ -226,20 +232,130 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!row_ok || col0 >= args.N) continue;
         float v[32];
 #pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (col0 + 32 <= args.N) {
+          // ---------------- fast path: the whole 32-column chunk is inside the matrix
+          if (args.row_rstd) {
+            if (args.row_mean) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = rstd * (v[j] - mean * __ldg(args.col_sum + col0 + j));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] *= rstd;
+            }
+          }
+          if (bias_vec_ok) {
+            const float4* bp = reinterpret_cast<const float4*>(args.bias + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 q = __ldg(bp + j);
+              v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+            }
+          } else if (args.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __ldg(args.bias + col0 + j);
+          }
+          if (args.swiglu_pairs) {
+            // (gate, up) pairs -> 16 output columns
+            float o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              o[j] = v[2 * j] * act_silu(v[2 * j + 1]);
+              if (args.round_tf32) o[j] = round_to_tf32(o[j]);
+            }
+            const long long idx = static_cast<long long>(row) * args.ld_out + (col0 >> 1);
+            if (args.out_bf16) {
+              __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + idx;
+              if (vec8_ok) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 8) {
+                  uint4 pk;
+                  pk.x = pack_bf16x2(o[j], o[j + 1]); pk.y = pack_bf16x2(o[j + 2], o[j + 3]);
+                  pk.z = pack_bf16x2(o[j + 4], o[j + 5]); pk.w = pack_bf16x2(o[j + 6], o[j + 7]);
+                  *reinterpret_cast<uint4*>(op + j) = pk;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) op[j] = __float2bfloat16(o[j]);
+              }
+            } else {
+              float* op = reinterpret_cast<float*>(args.out) + idx;
+              if (vec_ok) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) op[j] = o[j];
+              }
+            }
+            continue;
+          }
+          if (args.act == ACT_GELU_TANH) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = act_gelu_tanh(v[j]);
+          } else if (args.act == ACT_SILU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = act_silu(v[j]);
+          } else if (args.act == ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+          }
+          if (args.residual) {
+            const float* rp = args.residual + static_cast<long long>(row) * args.ld_res + col0;
+            if (res_vec_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 q = __ldg(reinterpret_cast<const float4*>(rp) + j);
+                v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += __ldg(rp + j);
+            }
+          }
+          if (args.round_tf32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
+          }
+          if (args.out_bf16) {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
+            if (vec8_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                pk.x = pack_bf16x2(v[j], v[j + 1]); pk.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                pk.z = pack_bf16x2(v[j + 4], v[j + 5]); pk.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(op + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) op[j] = __float2bfloat16(v[j]);
+            }
+          } else {
+            float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
+            if (vec_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) op[j] = v[j];
+            }
+          }
+          continue;
+        }
+        // ---------------- ragged right edge: per-column bounds checks, scalar accesses
+        // (fully unrolled with predicates so that v[] stays in registers)
+#pragma unroll
         for (int j = 0; j < 32; ++j) {
-          float x = __uint_as_float(r[j]);
           const int col = col0 + j;
           if (col < args.N) {
-            if (args.row_rstd) {
-              float cs = args.row_mean ? args.col_sum[col] : 0.f;
-              x = rstd * (x - mean * cs);
-            }
+            float x = v[j];
+            if (args.row_rstd) x = rstd * (x - (args.row_mean ? mean * args.col_sum[col] : 0.f));
             if (args.bias) x += __ldg(args.bias + col);
+            v[j] = x;
           }
-          v[j] = x;
         }
         if (args.swiglu_pairs) {
-          // (gate, up) pairs -> N/2 output columns
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             const int col = col0 + j;
@@ -253,64 +369,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           continue;
         }
-        if (args.act != ACT_NONE) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], args.act);
-        }
-        if (args.residual) {
-          const float* rp = args.residual + static_cast<long long>(row) * args.ld_res + col0;
-          if (res_vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (col0 + j < args.N) {
-                float4 q = __ldg(reinterpret_cast<const float4*>(rp + j));
-                v[j] += q.x; v[j + 1] += q.y; v[j + 2] += q.z; v[j + 3] += q.w;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) v[j] += __ldg(rp + j);
-          }
-        }
-        if (args.round_tf32) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
-        }
-        if (args.out_bf16) {
-          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
-          const bool v8 = (args.N % 8 == 0) && (args.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);
-          if (v8) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j < args.N) {
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                uint4 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&p0);
-                pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                pk.z = *reinterpret_cast<uint32_t*>(&p2);
-                pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(op + j) = pk;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) op[j] = __float2bfloat16(v[j]);
-          }
-        } else {
-          float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
-          if (vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (col0 + j < args.N) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) op[j] = v[j];
+        for (int j = 0; j < 32; ++j) {
+          const int col = col0 + j;
+          if (col < args.N) {
+            float x = apply_act(v[j], args.act);
+            if (args.residual) x += __ldg(args.residual + static_cast<long long>(row) * args.ld_res + col);
+            if (args.round_tf32) x = round_to_tf32(x);
+            const long long idx = static_cast<long long>(row) * args.ld_out + col;
+            if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(x);
+            else reinterpret_cast<float*>(args.out)[idx] = x;
           }
         }
       }
