@@ -44,17 +44,25 @@ def _digest(paths) -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile every .cu for sm_100a and link the shared library. Returns its path."""
+
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, extra_flags=(), suffix: str = "") -> Path:
+    """Compile every .cu for sm_100a and link the shared library. Returns its path.
+
+    ``extra_flags`` (e.g. ``["-DGEMM_EPI_WARPS=16"]``) with a ``suffix`` builds a tuning variant next to the
+    default library; load it by pointing the GRILLY_B200_LIB environment variable at it."""
+    global BUILD, LIB
+    if suffix:
+        BUILD = PKG / ("_build" + suffix)
+        LIB = PKG / "lib" / f"libgrilly_b200{suffix}.so"
     BUILD.mkdir(exist_ok=True)
     LIB.parent.mkdir(exist_ok=True)
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.glob("*.h"))
     stamp = BUILD / "stamp"
-    digest = _digest(deps)
+    digest = _digest(deps) + "|" + " ".join(extra_flags)
     if not force and LIB.exists() and stamp.exists() and stamp.read_text() == digest:
         return LIB
     nvcc = _nvcc()
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+    flags = list(NVCC_FLAGS) + list(extra_flags) + (["-Xptxas", "-v"] if ptxas_info else [])
 
     def compile_one(src: str) -> Path:
         obj = BUILD / (src + ".o")
@@ -77,5 +85,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
+    extra = [a for a in sys.argv[1:] if a.startswith("-D")]
+    sfx = next((a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--suffix=")), "")
+    path = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv, extra_flags=extra, suffix=sfx)
     print(path)

@@ -6,29 +6,38 @@
 
 namespace gb {
 
-template <int BN, bool kBf16, bool kBMn>
+template <int BN, bool kBf16, bool kBMn, bool kSwap>
 static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& args) {
   using Cfg = GemmCfg<BN>;
   constexpr int ELT = kBf16 ? 2 : 4;
   constexpr int BK = 128 / ELT;
+  static_assert(!(kBMn && kSwap), "the swapped orientation is for the K-major weight layout only");
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
   CUtensorMap ta, tb;
-  int rc = get_tmap_2d(ctx, dtype, a, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &ta);
-  if (rc) return rc;
-  if (kBMn) {
-    // B is [K][N] row-major: boxes of 128 B along N by BK k-rows
-    rc = get_tmap_2d(ctx, dtype, b, args.N, args.K, static_cast<uint64_t>(args.N) * ELT, 128 / ELT, BK, &tb,
-                     kBf16 ? TM_SW128 : TM_SW128_ATOM32);
+  int rc;
+  if (kSwap) {
+    // 128-row operand = weights W[N][K]; BN-row operand = activations x[M][K]
+    if ((rc = get_tmap_2d(ctx, dtype, b, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, 128, &ta))) return rc;
+    if ((rc = get_tmap_2d(ctx, dtype, a, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, BN, &tb))) return rc;
+    args.num_m_tiles = (args.N + 127) / 128;
+    args.num_n_tiles = (args.M + BN - 1) / BN;
   } else {
-    // B is [N][K] row-major: boxes of 128 B along K by BN rows
-    rc = get_tmap_2d(ctx, dtype, b, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, BN, &tb);
+    if ((rc = get_tmap_2d(ctx, dtype, a, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &ta))) return rc;
+    if (kBMn) {
+      // B is [K][N] row-major: boxes of 128 B along N by BK k-rows
+      rc = get_tmap_2d(ctx, dtype, b, args.N, args.K, static_cast<uint64_t>(args.N) * ELT, 128 / ELT, BK, &tb,
+                       kBf16 ? TM_SW128 : TM_SW128_ATOM32);
+    } else {
+      // B is [N][K] row-major: boxes of 128 B along K by BN rows
+      rc = get_tmap_2d(ctx, dtype, b, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, BN, &tb);
+    }
+    if (rc) return rc;
+    args.num_m_tiles = (args.M + 127) / 128;
+    args.num_n_tiles = (args.N + BN - 1) / BN;
   }
-  if (rc) return rc;
-  args.num_m_tiles = (args.M + 127) / 128;
-  args.num_n_tiles = (args.N + BN - 1) / BN;
   args.num_k_blocks = (args.K + BK - 1) / BK;
   args.err = ctx->err_dev;
-  auto kern = gemm_tcgen05_kernel<BN, kBf16, kBMn>;
+  auto kern = gemm_tcgen05_kernel<BN, kBf16, kBMn, kSwap>;
   if (!ctx->smem_attr_done.count(reinterpret_cast<const void*>(kern))) {
     GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     ctx->smem_attr_done.insert(reinterpret_cast<const void*>(kern));
@@ -47,37 +56,26 @@ static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& a
   return GRILLY_OK;
 }
 
-// Wave-quantisation estimate: time ~ waves * (tile cost), tile cost ~ BN columns + fixed overhead.
-static int pick_bn(int M, int N, int num_sms) {
-  const int cands[4] = {256, 192, 128, 64};
-  const long long m_tiles = (M + 127) / 128;
-  double best = 1e300;
-  int best_bn = 128;
-  for (int i = 0; i < 4; ++i) {
-    const int bn = cands[i];
-    const long long n_tiles = (N + bn - 1) / bn;
-    const long long tiles = m_tiles * n_tiles;
-    const long long waves = (tiles + num_sms - 1) / num_sms;
-    const double cost = static_cast<double>(waves) * (bn + 24);
-    if (cost < best - 1e-9) { best = cost; best_bn = bn; }
-  }
-  return best_bn;
-}
+// One tcgen05.mma takes about the same time for any N up to 256, so a tile costs the same whatever its width:
+// take the widest tile that is not mostly padding. The swapped orientation (weights as the 128-row operand,
+// tokens as the MMA's N) is used for `linear` whenever the output is wide enough to fill 128 feature rows.
+static bool pick_swap(int N, bool b_mn_major) { return !b_mn_major && N >= 96; }
+static int pick_bn(int cols) { return cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 192 ? 192 : 256; }
 
 }  // namespace gb
 extern "C" int grilly_gemm_pick_tile(int M, int N, int num_sms) {
   if (M <= 0 || N <= 0 || num_sms <= 0) return GRILLY_ERR_INVALID_ARG;
-  return gb::pick_bn(M, N, num_sms);
+  return gb::pick_bn(gb::pick_swap(N, false) ? M : N);
 }
 namespace gb {
 
-template <bool kBf16, bool kBMn>
+template <bool kBf16, bool kBMn, bool kSwap>
 static int dispatch_bn(grilly_ctx* ctx, int bn, const void* a, const void* b, GemmArgs& args) {
   switch (bn) {
-    case 256: return launch_one<256, kBf16, kBMn>(ctx, a, b, args);
-    case 192: return launch_one<192, kBf16, kBMn>(ctx, a, b, args);
-    case 128: return launch_one<128, kBf16, kBMn>(ctx, a, b, args);
-    case 64: return launch_one<64, kBf16, kBMn>(ctx, a, b, args);
+    case 256: return launch_one<256, kBf16, kBMn, kSwap>(ctx, a, b, args);
+    case 192: return launch_one<192, kBf16, kBMn, kSwap>(ctx, a, b, args);
+    case 128: return launch_one<128, kBf16, kBMn, kSwap>(ctx, a, b, args);
+    case 64: return launch_one<64, kBf16, kBMn, kSwap>(ctx, a, b, args);
     default: return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: N tile must be 64, 128, 192 or 256");
   }
 }
@@ -92,15 +90,19 @@ int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, cons
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: operands must be 16-byte aligned");
   if (args.swiglu_pairs && (args.N & 1)) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: SwiGLU pairs need an even N");
+  bool swap = pick_swap(args.N, b_mn_major);
+  if (const char* env = getenv("GRILLY_GEMM_SWAP")) swap = !b_mn_major && atoi(env) != 0;  // tuning/debug override
   if (force_bn <= 0) {
-    // tuning/debug override of the N tile (64, 128, 192 or 256)
+    // tuning/debug override of the tile width (64, 128, 192 or 256)
     if (const char* env = getenv("GRILLY_GEMM_BN")) force_bn = atoi(env);
   }
-  const int bn = force_bn > 0 ? force_bn : pick_bn(args.M, args.N, ctx->num_sms);
+  const int bn = force_bn > 0 ? force_bn : pick_bn(swap ? args.M : args.N);
   if (bf16) {
-    return b_mn_major ? dispatch_bn<true, true>(ctx, bn, a, b, args) : dispatch_bn<true, false>(ctx, bn, a, b, args);
+    if (b_mn_major) return dispatch_bn<true, true, false>(ctx, bn, a, b, args);
+    return swap ? dispatch_bn<true, false, true>(ctx, bn, a, b, args) : dispatch_bn<true, false, false>(ctx, bn, a, b, args);
   }
-  return b_mn_major ? dispatch_bn<false, true>(ctx, bn, a, b, args) : dispatch_bn<false, false>(ctx, bn, a, b, args);
+  if (b_mn_major) return dispatch_bn<false, true, false>(ctx, bn, a, b, args);
+  return swap ? dispatch_bn<false, false, true>(ctx, bn, a, b, args) : dispatch_bn<false, false, false>(ctx, bn, a, b, args);
 }
 
 }  // namespace gb

@@ -1,6 +1,8 @@
 // Persistent, warp-specialised TMA -> tcgen05 GEMM for sm_100a.
 //
 //   D[M,N] = epilogue( A[M,K] * B )      A is K-major (row-major [M][K]).
+//   (`linear` normally runs swapped: the weight matrix is the 128-row operand and 256 tokens are the N dimension of
+//   the MMA, because one tcgen05.mma takes the same time for N = 64 as for N = 256.)
 //   B is either K-major  ([N][K] row-major: the `linear` weight layout W(out,in)),
 //   or          MN-major ([K][N] row-major: the `gemm_mnk` B operand).
 //
@@ -19,12 +21,9 @@ namespace gb {
 
 
 __device__ __forceinline__ float round_to_tf32(float x) {
-  uint32_t u = __float_as_uint(x);
-  // round to nearest even on the 13 dropped mantissa bits; inf/nan pass through
-  if ((u & 0x7F800000u) != 0x7F800000u) {
-    u += 0x00000FFFu + ((u >> 13) & 1u);
-    u &= 0xFFFFE000u;
-  }
+  // nearest tf32 value (10-bit mantissa), returned as an fp32 bit pattern with the low 13 bits clear
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
   return __uint_as_float(u);
 }
 
@@ -52,6 +51,242 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+struct EpiFlags {
+  bool vec_ok, vec8_ok, res_vec_ok, bias_vec_ok;
+};
+
+// Applies the fused epilogue to 32 consecutive accumulator columns of one row and stores them.
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFlags& f, const uint32_t (&r)[32], int row,
+                                               int col0, float mean, float rstd) {
+  const bool vec_ok = f.vec_ok, vec8_ok = f.vec8_ok, res_vec_ok = f.res_vec_ok, bias_vec_ok = f.bias_vec_ok;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (col0 + 32 <= args.N) {
+    // ---------------- fast path: the whole 32-column chunk is inside the matrix
+    if (args.row_rstd) {
+      if (args.row_mean) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = rstd * (v[j] - mean * __ldg(args.col_sum + col0 + j));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= rstd;
+      }
+    }
+    if (bias_vec_ok) {
+      const float4* bp = reinterpret_cast<const float4*>(args.bias + col0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 q = __ldg(bp + j);
+        v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+      }
+    } else if (args.bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += __ldg(args.bias + col0 + j);
+    }
+    if (args.swiglu_pairs) {
+      // (gate, up) pairs -> 16 output columns
+      float o[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        o[j] = v[2 * j] * act_silu(v[2 * j + 1]);
+        if (args.round_tf32) o[j] = round_to_tf32(o[j]);
+      }
+      const long long idx = static_cast<long long>(row) * args.ld_out + (col0 >> 1);
+      if (args.out_bf16) {
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + idx;
+        if (vec8_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 8) {
+            uint4 pk;
+            pk.x = pack_bf16x2(o[j], o[j + 1]); pk.y = pack_bf16x2(o[j + 2], o[j + 3]);
+            pk.z = pack_bf16x2(o[j + 4], o[j + 5]); pk.w = pack_bf16x2(o[j + 6], o[j + 7]);
+            *reinterpret_cast<uint4*>(op + j) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) op[j] = __float2bfloat16(o[j]);
+        }
+      } else {
+        float* op = reinterpret_cast<float*>(args.out) + idx;
+        if (vec_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) op[j] = o[j];
+        }
+      }
+      return;
+    }
+    if (args.act == ACT_GELU_TANH) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = act_gelu_tanh(v[j]);
+    } else if (args.act == ACT_SILU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = act_silu(v[j]);
+    } else if (args.act == ACT_RELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    }
+    if (args.residual) {
+      const float* rp = args.residual + static_cast<long long>(row) * args.ld_res + col0;
+      if (res_vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 q = __ldg(reinterpret_cast<const float4*>(rp) + j);
+          v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += __ldg(rp + j);
+      }
+    }
+    if (args.round_tf32) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
+    }
+    if (args.out_bf16) {
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
+      if (vec8_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk;
+          pk.x = pack_bf16x2(v[j], v[j + 1]); pk.y = pack_bf16x2(v[j + 2], v[j + 3]);
+          pk.z = pack_bf16x2(v[j + 4], v[j + 5]); pk.w = pack_bf16x2(v[j + 6], v[j + 7]);
+          *reinterpret_cast<uint4*>(op + j) = pk;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) op[j] = __float2bfloat16(v[j]);
+      }
+    } else {
+      float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
+      if (vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) op[j] = v[j];
+      }
+    }
+    return;
+  }
+  // ---------------- ragged right edge: per-column bounds checks, scalar accesses
+  // (fully unrolled with predicates so that v[] stays in registers)
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const int col = col0 + j;
+    if (col < args.N) {
+      float x = v[j];
+      if (args.row_rstd) x = rstd * (x - (args.row_mean ? mean * args.col_sum[col] : 0.f));
+      if (args.bias) x += __ldg(args.bias + col);
+      v[j] = x;
+    }
+  }
+  if (args.swiglu_pairs) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const int col = col0 + j;
+      if (col + 1 < args.N) {
+        float o = v[j] * act_silu(v[j + 1]);
+        if (args.round_tf32) o = round_to_tf32(o);
+        const long long idx = static_cast<long long>(row) * args.ld_out + (col >> 1);
+        if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(o);
+        else reinterpret_cast<float*>(args.out)[idx] = o;
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const int col = col0 + j;
+    if (col < args.N) {
+      float x = apply_act(v[j], args.act);
+      if (args.residual) x += __ldg(args.residual + static_cast<long long>(row) * args.ld_res + col);
+      if (args.round_tf32) x = round_to_tf32(x);
+      const long long idx = static_cast<long long>(row) * args.ld_out + col;
+      if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(x);
+      else reinterpret_cast<float*>(args.out)[idx] = x;
+    }
+  }
+}
+
+// Swapped orientation (the 128-row operand is the weight matrix, so TMEM lanes are output features and the
+// accumulator columns are tokens): r[] holds 32 consecutive tokens t0.. for feature f. For a fixed register the
+// 32 lanes of a warp touch 32 consecutive features of one token, i.e. one 128-byte line of the row-major output.
+__device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, const uint32_t (&r)[32], int f, int t0) {
+  const bool f_ok = f < args.N;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  const bool full = t0 + 32 <= args.M;
+  if (args.row_rstd) {
+    const float cs = (args.row_mean && f_ok) ? __ldg(args.col_sum + f) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (full || t0 + j < args.M) {
+        const float rs = __ldg(args.row_rstd + t0 + j);
+        const float mu = args.row_mean ? __ldg(args.row_mean + t0 + j) : 0.f;
+        v[j] = rs * (v[j] - mu * cs);
+      }
+    }
+  }
+  if (args.bias) {
+    const float b = f_ok ? __ldg(args.bias + f) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += b;
+  }
+  if (args.swiglu_pairs) {
+    // features come as (gate, up) pairs in neighbouring lanes: even lanes produce out[:, f/2]
+    const bool writer = f_ok && (f + 1 < args.N) && !(f & 1);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+      if (writer && (full || t0 + j < args.M)) {
+        float o = v[j] * act_silu(up);
+        if (args.round_tf32) o = round_to_tf32(o);
+        const long long idx = static_cast<long long>(t0 + j) * args.ld_out + (f >> 1);
+        if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(o);
+        else reinterpret_cast<float*>(args.out)[idx] = o;
+      }
+    }
+    return;
+  }
+  if (!f_ok) return;
+  if (args.act == ACT_GELU_TANH) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = act_gelu_tanh(v[j]);
+  } else if (args.act == ACT_SILU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = act_silu(v[j]);
+  } else if (args.act == ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+  }
+  if (args.residual) {
+    const float* rp = args.residual + static_cast<long long>(t0) * args.ld_res + f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || t0 + j < args.M) v[j] += __ldg(rp + static_cast<long long>(j) * args.ld_res);
+  }
+  if (args.round_tf32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
+  }
+  if (args.out_bf16) {
+    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = __float2bfloat16(v[j]);
+  } else {
+    float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = v[j];
+  }
+}
+
 template <int BN>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -67,9 +302,13 @@ struct GemmCfg {
   static_assert(BN % 32 == 0, "epilogue drains 32 columns at a time");
 };
 
-constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+#ifndef GEMM_EPI_WARPS
+#define GEMM_EPI_WARPS 16
+#endif
+static_assert(GEMM_EPI_WARPS % 4 == 0 && GEMM_EPI_WARPS >= 4 && GEMM_EPI_WARPS <= 16, "epilogue warps come in groups of 4");
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;  // warp 0 TMA, warp 1 MMA, the rest epilogue
 
-template <int BN, bool kBf16, bool kBMnMajor>
+template <int BN, bool kBf16, bool kBMnMajor, bool kSwap>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmArgs args) {
@@ -102,7 +341,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 8);
+      mbar_init(&tmem_empty[a], GEMM_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -124,9 +363,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+#ifdef GEMM_EXPERIMENT_NOLOAD
+      int issued = 0;
+#endif
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile / args.num_n_tiles;
-        const int n_blk = tile % args.num_n_tiles;
+        // un-swapped: column blocks fastest (neighbouring CTAs share the A rows); swapped: the weight blocks
+        // (128-row operand) fastest, so neighbouring CTAs share one block of tokens
+        const int m_blk = kSwap ? tile % args.num_m_tiles : tile / args.num_n_tiles;
+        const int n_blk = kSwap ? tile / args.num_m_tiles : tile % args.num_n_tiles;
         for (int kb = 0; kb < args.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             if (!*abort_flag) atomicCAS(args.err, 0, ERR_WAIT_EMPTY);
@@ -136,6 +380,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
+#ifdef GEMM_EXPERIMENT_NOLOAD
+          // timing experiment only: after the ring has been filled once, hand stages over without reloading them
+          if (issued >= STAGES) { mbar_arrive(&full_bar[stage]); if (++stage == STAGES) { stage = 0; phase ^= 1u; } continue; }
+          ++issued;
+#endif
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * 128);
           if constexpr (kBMnMajor) {
@@ -156,6 +405,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      constexpr uint32_t B_KSTEP_BYTES = kBMnMajor ? UMMA_K * 128 : 32;  // advance of B per 32-byte k-step
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_base, 16, 1024);
+      const uint64_t b_desc0 = kBMnMajor ? make_smem_desc_mn<kBf16>(smem_base + Cfg::A_BYTES, BK * 128)
+                                         : make_smem_desc_sw128(smem_base + Cfg::A_BYTES, 16, 1024);
+      const uint32_t a_desc_lo = static_cast<uint32_t>(a_desc0), a_desc_hi = static_cast<uint32_t>(a_desc0 >> 32);
+      const uint32_t b_desc_lo = static_cast<uint32_t>(b_desc0), b_desc_hi = static_cast<uint32_t>(b_desc0 >> 32);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
@@ -174,18 +430,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
-          const uint32_t sb = sa + Cfg::A_BYTES;
+          // descriptors differ from the stage-0 / k-step-0 ones only in the 14-bit start-address field
+          // (units of 16 bytes), so a 32-bit add on the low word replaces rebuilding them for every MMA
+          const uint32_t a_lo = a_desc_lo + stage * (Cfg::STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_desc_lo + stage * (Cfg::STAGE_BYTES >> 4);
+#ifndef GEMM_EXPERIMENT_NOMMA
 #pragma unroll
           for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint64_t adesc = make_smem_desc_sw128(sa + ks * 32, 16, 1024);
-            uint64_t bdesc;
-            if constexpr (kBMnMajor)
-              bdesc = make_smem_desc_mn<kBf16>(sb + ks * (UMMA_K * 128), BK * 128);
-            else
-              bdesc = make_smem_desc_sw128(sb + ks * 32, 16, 1024);
+            const uint64_t adesc = (static_cast<uint64_t>(a_desc_hi) << 32) | (a_lo + ks * 2);
+            const uint64_t bdesc = (static_cast<uint64_t>(b_desc_hi) << 32) | (b_lo + ks * (B_KSTEP_BYTES >> 4));
             umma_ss<kBf16>(d_tmem, adesc, bdesc, IDESC, (kb | ks) != 0 ? 1u : 0u);
           }
+#endif
           umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -193,19 +449,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..9)
-    // Two warps per TMEM lane quadrant; each takes every other 32-column chunk of the accumulator.
+    // ------------------------------------------------------------ epilogue (warps 2 .. 2+GEMM_EPI_WARPS-1)
+    // GEMM_EPI_WARPS/4 warps per TMEM lane quadrant share the 32-column chunks of the accumulator round-robin.
+    // The TMEM load of a warp's next chunk is in flight while it works on the current one.
+    constexpr int NCHUNK = BN / 32;
+    constexpr int G = GEMM_EPI_WARPS / 4;
+    constexpr int MAXIT = (NCHUNK + G - 1) / G;
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;          // 0 or 1: which chunks of the tile this warp drains
+    const int group = (warp - 2) >> 2;         // which chunks of the tile this warp drains: group, group+G, ...
     int it = 0;
+    EpiFlags f;
     const bool out_al16 = (reinterpret_cast<uintptr_t>(args.out) & 15) == 0;
-    const bool vec_ok = !args.out_bf16 && (args.ld_out % 4 == 0) && out_al16;
-    const bool vec8_ok = args.out_bf16 && (args.ld_out % 8 == 0) && out_al16;
-    const bool res_vec_ok = args.residual && (args.ld_res % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
-    const bool bias_vec_ok = args.bias && ((reinterpret_cast<uintptr_t>(args.bias) & 15) == 0);
+    f.vec_ok = !args.out_bf16 && (args.ld_out % 4 == 0) && out_al16;
+    f.vec8_ok = args.out_bf16 && (args.ld_out % 8 == 0) && out_al16;
+    f.res_vec_ok = args.residual && (args.ld_res % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
+    f.bias_vec_ok = args.bias && ((reinterpret_cast<uintptr_t>(args.bias) & 15) == 0);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int m_blk = tile / args.num_n_tiles;
-      const int n_blk = tile % args.num_n_tiles;
+      const int m_blk = kSwap ? tile % args.num_m_tiles : tile / args.num_n_tiles;
+      const int n_blk = kSwap ? tile / args.num_m_tiles : tile % args.num_n_tiles;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) {
@@ -214,172 +475,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         break;
       }
       tc_fence_after();
-      const int row = m_blk * 128 + quad * 32 + lane;
-      const bool row_ok = row < args.M;
+      const int row = m_blk * 128 + quad * 32 + lane;   // un-swapped: output row; swapped: output feature
+      const bool row_ok = kSwap ? true : row < args.M;
       float mean = 0.f, rstd = 1.f;
-      if (args.row_rstd && row_ok) {
+      if (!kSwap && args.row_rstd && row_ok) {
         rstd = args.row_rstd[row];
         if (args.row_mean) mean = args.row_mean[row];
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = half; c < BN / 32; c += 2) {
-        uint32_t r[32];
-        __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the lane-dependent skip below
-        tmem_ld_32x32(taddr_row + c * 32, r);
-        tmem_ld_wait();
+      uint32_t ra[32], rb[32];
+      __syncwarp();
+      if (group < NCHUNK) tmem_ld_32x32(taddr_row + group * 32, ra);
+#pragma unroll
+      for (int i = 0; i < MAXIT; ++i) {
+        const int c = group + i * G;           // warp-uniform
+        uint32_t (&cur)[32] = (i & 1) ? rb : ra;
+        uint32_t (&nxt)[32] = (i & 1) ? ra : rb;
+        __syncwarp();                          // tcgen05.ld / wait are warp-collective: reconverge first
+        if (c < NCHUNK) tmem_ld_wait();
+        if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
         const int col0 = n_blk * BN + c * 32;
-        if (!row_ok || col0 >= args.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (col0 + 32 <= args.N) {
-          // ---------------- fast path: the whole 32-column chunk is inside the matrix
-          if (args.row_rstd) {
-            if (args.row_mean) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = rstd * (v[j] - mean * __ldg(args.col_sum + col0 + j));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] *= rstd;
-            }
-          }
-          if (bias_vec_ok) {
-            const float4* bp = reinterpret_cast<const float4*>(args.bias + col0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 q = __ldg(bp + j);
-              v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
-            }
-          } else if (args.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += __ldg(args.bias + col0 + j);
-          }
-          if (args.swiglu_pairs) {
-            // (gate, up) pairs -> 16 output columns
-            float o[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              o[j] = v[2 * j] * act_silu(v[2 * j + 1]);
-              if (args.round_tf32) o[j] = round_to_tf32(o[j]);
-            }
-            const long long idx = static_cast<long long>(row) * args.ld_out + (col0 >> 1);
-            if (args.out_bf16) {
-              __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + idx;
-              if (vec8_ok) {
-#pragma unroll
-                for (int j = 0; j < 16; j += 8) {
-                  uint4 pk;
-                  pk.x = pack_bf16x2(o[j], o[j + 1]); pk.y = pack_bf16x2(o[j + 2], o[j + 3]);
-                  pk.z = pack_bf16x2(o[j + 4], o[j + 5]); pk.w = pack_bf16x2(o[j + 6], o[j + 7]);
-                  *reinterpret_cast<uint4*>(op + j) = pk;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) op[j] = __float2bfloat16(o[j]);
-              }
-            } else {
-              float* op = reinterpret_cast<float*>(args.out) + idx;
-              if (vec_ok) {
-#pragma unroll
-                for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) op[j] = o[j];
-              }
-            }
-            continue;
-          }
-          if (args.act == ACT_GELU_TANH) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = act_gelu_tanh(v[j]);
-          } else if (args.act == ACT_SILU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = act_silu(v[j]);
-          } else if (args.act == ACT_RELU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-          }
-          if (args.residual) {
-            const float* rp = args.residual + static_cast<long long>(row) * args.ld_res + col0;
-            if (res_vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 q = __ldg(reinterpret_cast<const float4*>(rp) + j);
-                v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] += __ldg(rp + j);
-            }
-          }
-          if (args.round_tf32) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
-          }
-          if (args.out_bf16) {
-            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
-            if (vec8_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                pk.x = pack_bf16x2(v[j], v[j + 1]); pk.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                pk.z = pack_bf16x2(v[j + 4], v[j + 5]); pk.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(op + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) op[j] = __float2bfloat16(v[j]);
-            }
-          } else {
-            float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(row) * args.ld_out + col0;
-            if (vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(op + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) op[j] = v[j];
-            }
-          }
-          continue;
-        }
-        // ---------------- ragged right edge: per-column bounds checks, scalar accesses
-        // (fully unrolled with predicates so that v[] stays in registers)
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = col0 + j;
-          if (col < args.N) {
-            float x = v[j];
-            if (args.row_rstd) x = rstd * (x - (args.row_mean ? mean * args.col_sum[col] : 0.f));
-            if (args.bias) x += __ldg(args.bias + col);
-            v[j] = x;
-          }
-        }
-        if (args.swiglu_pairs) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const int col = col0 + j;
-            if (col + 1 < args.N) {
-              float o = v[j] * act_silu(v[j + 1]);
-              if (args.round_tf32) o = round_to_tf32(o);
-              const long long idx = static_cast<long long>(row) * args.ld_out + (col >> 1);
-              if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(o);
-              else reinterpret_cast<float*>(args.out)[idx] = o;
-            }
-          }
-          continue;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = col0 + j;
-          if (col < args.N) {
-            float x = apply_act(v[j], args.act);
-            if (args.residual) x += __ldg(args.residual + static_cast<long long>(row) * args.ld_res + col);
-            if (args.round_tf32) x = round_to_tf32(x);
-            const long long idx = static_cast<long long>(row) * args.ld_out + col;
-            if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(x);
-            else reinterpret_cast<float*>(args.out)[idx] = x;
-          }
+        if constexpr (kSwap) {
+          if (c < NCHUNK && col0 < args.M) epilogue_chunk_swapped(args, cur, row, col0);
+        } else {
+          if (c < NCHUNK && row_ok && col0 < args.N) epilogue_chunk(args, f, cur, row, col0, mean, rstd);
         }
       }
       // this warp has finished reading the accumulator

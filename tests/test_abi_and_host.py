@@ -76,9 +76,12 @@ def test_product_does_not_import_the_oracle():
 
 
 def test_gemm_tile_choice(lib):
-    # tiles divide the encoder's output widths on a 148-SM part, and a skinny problem gets the narrow tile
-    assert lib.grilly_gemm_pick_tile(131072, 1152, 148) in (128, 192)
+    # a wide output runs swapped (tokens are the MMA's N): many tokens get the widest tile, few get the narrow one
+    assert lib.grilly_gemm_pick_tile(131072, 1152, 148) == 256
     assert lib.grilly_gemm_pick_tile(32, 1536, 148) == 64
+    assert lib.grilly_gemm_pick_tile(100, 1536, 148) == 128
+    # a narrow output stays un-swapped and tiles its own width
+    assert lib.grilly_gemm_pick_tile(4096, 64, 148) == 64
     assert lib.grilly_gemm_pick_tile(16384, 16384, 148) == 256
     assert lib.grilly_gemm_pick_tile(0, 5, 148) < 0
 
