@@ -1,6 +1,7 @@
 // Host launcher for the tcgen05 flash-attention kernel.
 #include "attention.cuh"
 #include "internal.h"
+#include <cstdlib>
 
 namespace gb {
 
@@ -38,14 +39,57 @@ static int launch_one(grilly_ctx* ctx, const void* q, const void* k, const void*
   return GRILLY_OK;
 }
 
+template <int D, bool kBf16>
+static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
+                        long long total_rows, AttnArgs& args) {
+  using Cfg = AttnShortCfg<D, kBf16>;
+  constexpr int ELT = kBf16 ? 2 : 4;
+  const int dtype = kBf16 ? TM_BF16 : TM_F32;
+  const uint64_t width = static_cast<uint64_t>(args.H) * D;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tq))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tk))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tv,
+                        kBf16 ? TM_SW128 : TM_SW128_ATOM32))) return rc;
+  args.err = ctx->err_dev;
+  auto kern = flash_attn_short_kernel<D, kBf16>;
+  if (!ctx->smem_attr_done.count(reinterpret_cast<const void*>(kern))) {
+    GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    ctx->smem_attr_done.insert(reinterpret_cast<const void*>(kern));
+  }
+  // one CTA per sequence walking all heads, split into head groups only while the grid is too small to fill the GPU
+  int hpc = args.H;
+  while (hpc > 1 && static_cast<long long>(args.B) * ((args.H + hpc - 1) / hpc) < 4LL * ctx->num_sms) hpc = (hpc + 1) / 2;
+  dim3 grid(args.B, (args.H + hpc - 1) / hpc, 1);
+  double flops = ctx->attn_flops_hint >= 0.0 ? ctx->attn_flops_hint : 4.0 * args.B * args.H * static_cast<double>(args.S) * args.S * D;
+  ctx->attn_flops_hint = -1.0;
+  const double bytes = static_cast<double>(total_rows) * args.H * D * (3.0 * ELT + (args.out_bf16 ? 2.0 : 4.0));
+  const int pi = prof_begin(ctx, PROF_ATTN, flops, bytes);
+  kern<<<grid, ATTN_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tq, tk, tv, args, hpc);
+  prof_end(ctx, pi);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+
 int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_qkv,
                      long long total_rows, AttnArgs& args) {
   const int elt = bf16 ? 2 : 4;
   if (args.B <= 0 || args.S <= 0 || args.H <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: B, S, H must be positive");
-  if (args.H > 65535 || args.B > 65535) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: B and H are limited to 65535");
   if ((ld_qkv * elt) % 16 != 0) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: row pitch must be a multiple of 16 bytes");
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: q, k, v must be 16-byte aligned");
+  // every sequence fits one key tile and nothing needs per-tile state: the multi-head kernel
+  const bool short_ok = args.S <= ATTN_TILE && !args.causal && args.rope_style == ROPE_NONE && args.scale > 0.f &&
+                        args.B <= 2147483647 && getenv("GRILLY_ATTN_GENERAL") == nullptr;
+  if (short_ok) {
+    if (!bf16 && args.D == 32) return launch_short<32, false>(ctx, q, k, v, ld_qkv, total_rows, args);
+    if (!bf16 && args.D == 64) return launch_short<64, false>(ctx, q, k, v, ld_qkv, total_rows, args);
+    if (bf16 && args.D == 64) return launch_short<64, true>(ctx, q, k, v, ld_qkv, total_rows, args);
+    if (bf16 && args.D == 128) return launch_short<128, true>(ctx, q, k, v, ld_qkv, total_rows, args);
+  }
+  if (args.H > 65535 || args.B > 65535) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: B and H are limited to 65535 for sequences longer than 128");
   if (!bf16 && args.D == 32) return launch_one<32, false>(ctx, q, k, v, ld_qkv, total_rows, args);
   if (!bf16 && args.D == 64) return launch_one<64, false>(ctx, q, k, v, ld_qkv, total_rows, args);
   if (bf16 && args.D == 64) return launch_one<64, true>(ctx, q, k, v, ld_qkv, total_rows, args);
