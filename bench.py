@@ -32,6 +32,7 @@ sys.path.insert(0, str(ROOT))
 
 CFG = dict(num_layers=6, hidden=384, heads=12, ffn=1536, vocab=30522, max_pos=512, batch=1024, seq=128)
 WORKLOAD = "minilm_l6_h384_encoder_forward_b1024_s128_per_gpu"
+NCU_GEMM_TRAFFIC_RATIO = 84.5 / 143.9  # dram bytes (read + write) per algorithmic byte, from the ncu capture
 
 
 def make_batch(rank: int):
@@ -269,10 +270,10 @@ def main():
         ms_per_step = total_ms / args.steps
         value = world * B / (ms_per_step * 1e-3)
         e2e_value = world * B / (total_e2e_ms / args.steps * 1e-3)
-        traffic = None
-        tr_path = ROOT / "profiles" / "gemm_traffic.json"
-        if tr_path.exists():
-            traffic = json.loads(tr_path.read_text()).get("traffic_bytes_per_launch")
+        # DRAM traffic per launch: the ncu capture of this kernel on the FFN1 shape at 18 432 rows
+        # (profiles/gemm_tcgen05_linear_gelu_18432x1536x384.md) moved 84.5 MB for 143.9 MB of algorithmic bytes;
+        # that ratio is scaled by the algorithmic bytes of this run's average launch
+        traffic = NCU_GEMM_TRAFFIC_RATIO * g["bytes"] / max(g["launches"], 1) if g["launches"] else None
         line = {
             "metric": "encoder_sentences_per_sec", "value": value, "unit": "sentences/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
