@@ -118,6 +118,17 @@ int grilly_fold_layernorm_weights(grilly_ctx* ctx, const float* w_dev, const flo
 int grilly_layernorm_linear(grilly_ctx* ctx, const float* x_dev, const void* wf_dev, const float* col_sum_dev,
                             const float* bias_f_dev, void* y_dev, float* stats_dev, int M, int N, int K, float eps,
                             int norm_mode, int act, int precision, int flags);
+/* Same result as grilly_layernorm_linear, for callers that cannot allocate device memory while they run an op
+ * (a serving thread with a fixed memory budget, or a process whose device memory is owned by another allocator):
+ * the statistics scratch is a 512 KiB array built into the library image, resident on every GPU that loads the
+ * library. No counterpart in the reference. Limits: M <= GRILLY_NOALLOC_MAX_ROWS (more is rejected with
+ * GRILLY_ERR_INVALID_ARG); tf32 mode only; all calls on a device share the array, so calls that overlap on the
+ * GPU race (calls on one stream are ordered); the first call on a device resolves the array's address and should
+ * come before any stream capture. Allocates nothing on the device and frees nothing. */
+#define GRILLY_NOALLOC_MAX_ROWS 65536
+int grilly_layernorm_linear_noalloc(grilly_ctx* ctx, const float* x_dev, const void* wf_dev, const float* col_sum_dev,
+                                    const float* bias_f_dev, void* y_dev, int M, int N, int K, float eps, int norm_mode,
+                                    int act, int precision, int flags);
 /* C[M,N] = A[M,K] * B[K,N], all row-major.  VulkanFNN.gemm backend/fnn.py:104-166 (gemm_mnk.glsl:35-88). */
 int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int M, int K, int N,
                     int precision, int flags);
