@@ -31,6 +31,48 @@ def _time(dev, fn, warmup, reps):
     return dev.timer_stop() / reps
 
 
+def _nsplit(a):
+    """C = A B with B column-split across the ranks (one process per GPU, NCCL all-gather of C per row slab)."""
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    from .compute import Compute
+    from .dist import CudaLocalGemm, gemm_nsplit
+
+    rank_local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(rank_local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank_local))
+    world = dist.get_world_size()
+    backend = Compute(device=rank_local, precision=a.precision)
+    rng = np.random.default_rng(4)
+    A = rng.standard_normal((a.m, a.k)).astype(np.float32)
+    B = rng.standard_normal((a.k, a.n)).astype(np.float32)
+    local = CudaLocalGemm(backend)
+    n_loc = a.n // world
+    local.prepare(A, B[:, dist.get_rank() * n_loc:(dist.get_rank() + 1) * n_loc])
+    for _ in range(a.warmup):
+        gemm_nsplit(A, B, local=local, return_tensor=True, prepared=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.reps):
+        gemm_nsplit(A, B, local=local, return_tensor=True, prepared=True)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / a.reps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if dist.get_rank() == 0:
+        ms = t.item()
+        sent = (world - 1) / world * a.m * a.n * 4.0
+        print(f"gemm n-split x{world} {a.m}x{a.n}x{a.k} {a.precision}: {ms * 1e3:.1f} us (max over ranks)  "
+              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s aggregate  all-gather {sent / ms / 1e6:.1f} GB/s sent per GPU")
+    backend.cleanup()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("op", choices=["linear", "gemm", "attention", "layernorm"])
@@ -50,7 +92,11 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--nsplit", action="store_true",
+                    help="gemm: split B by columns over the ranks of a torch.distributed.run launch and all-gather C")
     a = ap.parse_args(argv)
+    if a.nsplit:
+        return _nsplit(a)
 
     dev = Device(a.device)
     lib, ctx = dev.lib, dev.ctx
