@@ -303,7 +303,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           }
         }
         const float m_new = fmaxf(m_run, m_tile);
-        alpha = exp2f((m_run - m_new) * kLog2e);  // 0 on the first step (m_run = -inf)
+        alpha = fast_exp2((m_run - m_new) * kLog2e);  // 0 on the first step (m_run = -inf)
         const float m_l2 = m_new * kLog2e;
         m_run = m_new;
 
@@ -321,7 +321,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
             if (args.causal && kidx > qi) s = -1e9f;
             if (kidx >= L) s = -INFINITY;
-            float e = exp2f(s * kLog2e - m_l2);
+            float e = fast_exp2(s * kLog2e - m_l2);
             if constexpr (kBf16) e = __bfloat162float(__float2bfloat16(e));
             else e = round_to_tf32(e);
             p[i] = e;
@@ -583,11 +583,11 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
               float x = fmaf(__uint_as_float(r[j]), sl2, -m_l2);
               if (kidx >= L) x = -INFINITY;
               else if (kmask && __ldg(kmask + kidx) < 0.5f) x = -1e9f * 1.4426950408889634f - m_l2;
-              p[j] = exp2f(x);
+              p[j] = fast_exp2(x);
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) p[j] = exp2f(fmaf(__uint_as_float(r[j]), sl2, -m_l2));
+            for (int j = 0; j < 32; ++j) p[j] = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_l2));
           }
           if constexpr (kBf16) {
             uint32_t pk[16];

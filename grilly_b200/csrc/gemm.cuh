@@ -32,7 +32,7 @@ __device__ __forceinline__ float act_gelu_tanh(float x) {
   const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
   const float k3 = k1 * 0.044715f;
   const float t = x * fmaf(k3, x * x, k1);
-  return __fdividef(x, 1.0f + exp2f(t));  // t -> +inf gives x/inf = 0, t -> -inf gives x
+  return __fdividef(x, 1.0f + fast_exp2(t));  // t -> +inf gives x/inf = 0, t -> -inf gives x
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
@@ -266,9 +266,14 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
   }
   if (args.residual) {
     const float* rp = args.residual + static_cast<long long>(t0) * args.ld_res + f;
+    if (full) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (full || t0 + j < args.M) v[j] += __ldg(rp + static_cast<long long>(j) * args.ld_res);
+      for (int j = 0; j < 32; ++j) v[j] += __ldg(rp + static_cast<long long>(j) * args.ld_res);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (t0 + j < args.M) v[j] += __ldg(rp + static_cast<long long>(j) * args.ld_res);
+    }
   }
   if (args.round_tf32) {
 #pragma unroll
@@ -281,9 +286,14 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
       if (full || t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = __float2bfloat16(v[j]);
   } else {
     float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
+    if (full) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (full || t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = v[j];
+      for (int j = 0; j < 32; ++j) op[static_cast<long long>(j) * args.ld_out] = v[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = v[j];
+    }
   }
 }
 
