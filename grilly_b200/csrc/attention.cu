@@ -6,18 +6,18 @@
 namespace gb {
 
 template <int D, bool kBf16>
-static int launch_one(grilly_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
-                      long long total_rows, AttnArgs& args) {
+static int launch_one(grilly_ctx* ctx, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
+                      long long ld_v, long long total_rows, AttnArgs& args) {
   using Cfg = AttnCfg<D, kBf16>;
   constexpr int ELT = kBf16 ? 2 : 4;
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
   const uint64_t width = static_cast<uint64_t>(args.H) * D;  // columns reachable from each base pointer
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tq))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tk))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_q * ELT, 128 / ELT, ATTN_TILE, &tq))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_k * ELT, 128 / ELT, ATTN_TILE, &tk))) return rc;
   // V is consumed as the MN-major operand of P V: tf32 needs the 32-byte-atom swizzle
-  if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tv,
+  if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_v * ELT, 128 / ELT, ATTN_TILE, &tv,
                         kBf16 ? TM_SW128 : TM_SW128_ATOM32))) return rc;
   args.err = ctx->err_dev;
   auto kern = flash_attn_tcgen05_kernel<D, kBf16>;
@@ -40,17 +40,17 @@ static int launch_one(grilly_ctx* ctx, const void* q, const void* k, const void*
 }
 
 template <int D, bool kBf16>
-static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const void* v, long long ld_qkv,
-                        long long total_rows, AttnArgs& args) {
+static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
+                        long long ld_v, long long total_rows, AttnArgs& args) {
   using Cfg = AttnShortCfg<D, kBf16>;
   constexpr int ELT = kBf16 ? 2 : 4;
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
   const uint64_t width = static_cast<uint64_t>(args.H) * D;
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tq))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tk))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_qkv * ELT, 128 / ELT, ATTN_TILE, &tv,
+  if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_q * ELT, 128 / ELT, ATTN_TILE, &tq))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_k * ELT, 128 / ELT, ATTN_TILE, &tk))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_v * ELT, 128 / ELT, ATTN_TILE, &tv,
                         kBf16 ? TM_SW128 : TM_SW128_ATOM32))) return rc;
   args.err = ctx->err_dev;
   auto kern = flash_attn_short_kernel<D, kBf16>;
@@ -73,27 +73,27 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
   return GRILLY_OK;
 }
 
-int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_qkv,
-                     long long total_rows, AttnArgs& args) {
+int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
+                     long long ld_v, long long total_rows, AttnArgs& args) {
   const int elt = bf16 ? 2 : 4;
   if (args.B <= 0 || args.S <= 0 || args.H <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: B, S, H must be positive");
-  if ((ld_qkv * elt) % 16 != 0) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: row pitch must be a multiple of 16 bytes");
+  if ((ld_q * elt) % 16 != 0 || (ld_k * elt) % 16 != 0 || (ld_v * elt) % 16 != 0) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: row pitch must be a multiple of 16 bytes");
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: q, k, v must be 16-byte aligned");
   // every sequence fits one key tile and nothing needs per-tile state: the multi-head kernel
   const bool short_ok = args.S <= ATTN_TILE && !args.causal && args.rope_style == ROPE_NONE && args.scale > 0.f &&
                         args.B <= 2147483647 && getenv("GRILLY_ATTN_GENERAL") == nullptr;
   if (short_ok) {
-    if (!bf16 && args.D == 32) return launch_short<32, false>(ctx, q, k, v, ld_qkv, total_rows, args);
-    if (!bf16 && args.D == 64) return launch_short<64, false>(ctx, q, k, v, ld_qkv, total_rows, args);
-    if (bf16 && args.D == 64) return launch_short<64, true>(ctx, q, k, v, ld_qkv, total_rows, args);
-    if (bf16 && args.D == 128) return launch_short<128, true>(ctx, q, k, v, ld_qkv, total_rows, args);
+    if (!bf16 && args.D == 32) return launch_short<32, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+    if (!bf16 && args.D == 64) return launch_short<64, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+    if (bf16 && args.D == 64) return launch_short<64, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+    if (bf16 && args.D == 128) return launch_short<128, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   }
   if (args.H > 65535 || args.B > 65535) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: B and H are limited to 65535 for sequences longer than 128");
-  if (!bf16 && args.D == 32) return launch_one<32, false>(ctx, q, k, v, ld_qkv, total_rows, args);
-  if (!bf16 && args.D == 64) return launch_one<64, false>(ctx, q, k, v, ld_qkv, total_rows, args);
-  if (bf16 && args.D == 64) return launch_one<64, true>(ctx, q, k, v, ld_qkv, total_rows, args);
-  if (bf16 && args.D == 128) return launch_one<128, true>(ctx, q, k, v, ld_qkv, total_rows, args);
+  if (!bf16 && args.D == 32) return launch_one<32, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+  if (!bf16 && args.D == 64) return launch_one<64, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+  if (bf16 && args.D == 64) return launch_one<64, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+  if (bf16 && args.D == 128) return launch_one<128, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   return set_error(ctx, GRILLY_ERR_UNSUPPORTED,
                    "attention: head_dim must be 32 or 64 (tf32 mode) or 64 or 128 (bf16 mode)");
 }

@@ -41,6 +41,23 @@ struct AttnCfg {
   static constexpr int TMEM_COLS = 256;
 };
 
+// Reductions over 32 registers with four independent chains (a single chain of 32 dependent ops is latency-bound).
+__device__ __forceinline__ float row_max32(const uint32_t (&r)[32]) {
+  float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
+#pragma unroll
+  for (int i = 4; i < 32; i += 4) {
+    m0 = fmaxf(m0, __uint_as_float(r[i])); m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+    m2 = fmaxf(m2, __uint_as_float(r[i + 2])); m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+__device__ __forceinline__ float row_sum32(const float (&p)[32]) {
+  float s0 = p[0], s1 = p[1], s2 = p[2], s3 = p[3];
+#pragma unroll
+  for (int i = 4; i < 32; i += 4) { s0 += p[i]; s1 += p[i + 1]; s2 += p[i + 2]; s3 += p[i + 3]; }
+  return (s0 + s1) + (s2 + s3);
+}
+
 // Rotate one row of a Q or K tile in place in swizzled shared memory.
 template <int D, bool kBf16>
 __device__ __forceinline__ void rope_row_inplace(uint8_t* tile, int r, int pos, const AttnArgs& a) {
@@ -81,10 +98,18 @@ __device__ __forceinline__ void rope_row_inplace(uint8_t* tile, int r, int pos, 
       uint4* p = piece_ptr(pc);
       float f[EPP];
       unpack(*p, f);
+      // pairs (pc*EPP/2 .. +EPP/2) are consecutive table entries: one vector load each for cos and sin
+      float cs[EPP / 2], sn[EPP / 2];
+      if constexpr (EPP == 8) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(ct) + pc), s4 = __ldg(reinterpret_cast<const float4*>(st) + pc);
+        cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w; sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+      } else {
+        const float2 c2 = __ldg(reinterpret_cast<const float2*>(ct) + pc), s2 = __ldg(reinterpret_cast<const float2*>(st) + pc);
+        cs[0] = c2.x; cs[1] = c2.y; sn[0] = s2.x; sn[1] = s2.y;
+      }
 #pragma unroll
       for (int e = 0; e < EPP; e += 2) {
-        const int i = (pc * EPP + e) >> 1;  // pair index
-        const float c = __ldg(ct + i), s = __ldg(st + i);
+        const float c = cs[e >> 1], s = sn[e >> 1];
         const float x0 = f[e], x1 = f[e + 1];
         f[e] = x0 * c - x1 * s;
         f[e + 1] = x0 * s + x1 * c;
@@ -99,10 +124,17 @@ __device__ __forceinline__ void rope_row_inplace(uint8_t* tile, int r, int pos, 
       float f0[EPP], f1[EPP];
       unpack(*p0, f0);
       unpack(*p1, f1);
+      float cs[EPP], sn[EPP];  // pairs (i, i + D/2), i = pc*EPP .. +EPP: consecutive table entries
+#pragma unroll
+      for (int q = 0; q < EPP / 4; ++q) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(ct + pc * EPP) + q);
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(st + pc * EPP) + q);
+        cs[4 * q] = c4.x; cs[4 * q + 1] = c4.y; cs[4 * q + 2] = c4.z; cs[4 * q + 3] = c4.w;
+        sn[4 * q] = s4.x; sn[4 * q + 1] = s4.y; sn[4 * q + 2] = s4.z; sn[4 * q + 3] = s4.w;
+      }
 #pragma unroll
       for (int e = 0; e < EPP; ++e) {
-        const int i = pc * EPP + e;  // pair (i, i + D/2)
-        const float c = __ldg(ct + i), s = __ldg(st + i);
+        const float c = cs[e], s = sn[e];
         const float x0 = f0[e], x1 = f1[e];
         f0[e] = x0 * c - x1 * s;
         f1[e] = x1 * c + x0 * s;
@@ -285,21 +317,30 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 
       float alpha = 1.f, l_tile = 0.f;
       if (warp_active) {
-        // ---- pass 1: row maximum of the masked, scaled scores
+        // Only tiles that touch the end of the sequence, the causal diagonal or a key mask need per-element
+        // mask logic (warp-uniform test); interior tiles work on the raw scores: max, then exp2(s*c - m*c).
+        const bool tile_mask = kmask != nullptr || k0 + ATTN_TILE > L || (args.causal && k0 + ATTN_TILE - 1 > q0) ||
+                               !(args.scale > 0.f);
+        const float sl2 = args.scale * kLog2e;
+        // ---- pass 1: row maximum
         float m_tile = -INFINITY;
 #pragma unroll 1
         for (int c = 0; c < nchunks; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
           tmem_ld_wait();
+          if (tile_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kidx = k0 + c * 32 + i;
-            float s = __uint_as_float(r[i]) * args.scale;
-            if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
-            if (args.causal && kidx > qi) s = -1e9f;
-            if (kidx >= L) s = -INFINITY;
-            m_tile = fmaxf(m_tile, s);
+            for (int i = 0; i < 32; ++i) {
+              const int kidx = k0 + c * 32 + i;
+              float s = __uint_as_float(r[i]) * args.scale;
+              if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
+              if (args.causal && kidx > qi) s = -1e9f;
+              if (kidx >= L) s = -INFINITY;
+              m_tile = fmaxf(m_tile, s);
+            }
+          } else {
+            m_tile = fmaxf(m_tile, row_max32(r) * args.scale);
           }
         }
         const float m_new = fmaxf(m_run, m_tile);
@@ -314,18 +355,19 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
           tmem_ld_wait();
           float p[32];
+          if (tile_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kidx = k0 + c * 32 + i;
-            float s = __uint_as_float(r[i]) * args.scale;
-            if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
-            if (args.causal && kidx > qi) s = -1e9f;
-            if (kidx >= L) s = -INFINITY;
-            float e = fast_exp2(s * kLog2e - m_l2);
-            if constexpr (kBf16) e = __bfloat162float(__float2bfloat16(e));
-            else e = round_to_tf32(e);
-            p[i] = e;
-            l_tile += e;
+            for (int i = 0; i < 32; ++i) {
+              const int kidx = k0 + c * 32 + i;
+              float s = __uint_as_float(r[i]) * args.scale;
+              if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
+              if (args.causal && kidx > qi) s = -1e9f;
+              if (kidx >= L) s = -INFINITY;
+              p[i] = fast_exp2(s * kLog2e - m_l2);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -m_l2));
           }
           if constexpr (kBf16) {
             // two bf16 per 32-bit column (even key in the low half): chunk c -> columns [16c, 16c+16).
@@ -333,11 +375,16 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             uint32_t pk[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+            l_tile += row_sum32(p);   // the unrounded sum: bf16 rounding of P averages out over the row
             tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
           } else {
             uint32_t pk[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) pk[i] = __float_as_uint(p[i]);
+            for (int i = 0; i < 32; ++i) {
+              p[i] = round_to_tf32(p[i]);
+              pk[i] = __float_as_uint(p[i]);
+            }
+            l_tile += row_sum32(p);
             tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
           }
         }
@@ -560,8 +607,7 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
               m_raw = fmaxf(m_raw, s);
             }
           } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) m_raw = fmaxf(m_raw, __uint_as_float(r[j]));
+            m_raw = fmaxf(m_raw, row_max32(r));
           }
         }
         // masked keys carry the score -1e9 (the reference adds (mask-1)*1e9): they only matter when every key is masked
@@ -592,21 +638,17 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           if constexpr (kBf16) {
             uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const __nv_bfloat162 hh = __floats2bfloat162_rn(p[2 * j], p[2 * j + 1]);
-              pk[j] = *reinterpret_cast<const uint32_t*>(&hh);
-              const float2 back = __bfloat1622float2(hh);
-              l_sum += back.x + back.y;
-            }
+            for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(p[2 * j], p[2 * j + 1]);
+            l_sum += row_sum32(p);
             tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
           } else {
             uint32_t pk[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float e = round_to_tf32(p[j]);
-              pk[j] = __float_as_uint(e);
-              l_sum += e;
+              p[j] = round_to_tf32(p[j]);
+              pk[j] = __float_as_uint(p[j]);
             }
+            l_sum += row_sum32(p);
             tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
           }
         }

@@ -138,7 +138,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
     at.B = Bc; at.S = max_len; at.H = H; at.D = D; at.cu_seqlens = cu_chunk_dev; at.scale = 1.0f / sqrtf(static_cast<float>(D));
     at.out = e->attn; at.ld_out = F; at.round_tf32 = 1;
     ctx->attn_flops_hint = 4.0 * H * D * sum_len2;  // valid (query, key) pairs only
-    if ((rc = launch_attention(ctx, false, e->qkv, e->qkv + F, e->qkv + 2 * F, 3LL * F, rows, at))) return rc;
+    if ((rc = launch_attention(ctx, false, e->qkv, e->qkv + F, e->qkv + 2 * F, 3LL * F, 3LL * F, 3LL * F, rows, at))) return rc;
     if ((rc = enc_linear(e, e->attn, L.wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE))) return rc;
     if ((rc = enc_norm(e, e->t, L.ln1_g, L.ln1_b, e->x2, rows))) return rc;
     if ((rc = enc_linear(e, e->x2, L.w1, L.b1, nullptr, e->h, rows, c.ffn, F, ACT_GELU_TANH))) return rc;

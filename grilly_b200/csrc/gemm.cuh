@@ -505,6 +505,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (c < NCHUNK) tmem_ld_wait();
         if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
         const int col0 = n_blk * BN + c * 32;
+#ifdef GEMM_EXPERIMENT_NOEPI
+        if (c < NCHUNK && col0 < 0) epilogue_chunk_swapped(args, cur, row, col0);  // timing experiment: drain only
+        continue;
+#endif
         if constexpr (kSwap) {
           if (c < NCHUNK && col0 < args.M) epilogue_chunk_swapped(args, cur, row, col0);
         } else {

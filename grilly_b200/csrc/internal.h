@@ -95,8 +95,8 @@ struct PoolArgs;
 // gemm.cu
 int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, const void* b, GemmArgs& args, int force_bn);
 // attention.cu
-int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_qkv,
-                     long long total_rows, AttnArgs& args);
+int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
+                     long long ld_v, long long total_rows, AttnArgs& args);
 // rowops.cu
 int launch_norm(grilly_ctx* ctx, const NormArgs& a);
 int launch_softmax(grilly_ctx* ctx, const float* x, float* y, long long rows, int cols);
@@ -110,6 +110,8 @@ int launch_pool(grilly_ctx* ctx, const PoolArgs& a);
 int launch_fold_ln(grilly_ctx* ctx, const float* w, const float* gamma, const float* beta, const float* bias, void* wf,
                    float* col_sum, float* bias_f, int N, int K, bool bf16);
 int get_rope_table(grilly_ctx* ctx, int S, int D, float base, float scaling, const float** cos_t, const float** sin_t);
+int launch_rope_rows(grilly_ctx* ctx, bool bf16, const void* src, void* dst, long long rows, long long pitch, int H, int D,
+                     int S, const int* cu_seqlens, int B, const float* cos_t, const float* sin_t, int style);
 int launch_rope_apply(grilly_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,
                       const int* position_ids, int B, int S, int H, int D, int style);
 

@@ -166,6 +166,22 @@ int get_rope_table(grilly_ctx* ctx, int S, int D, float base, float scaling, con
   return GRILLY_OK;
 }
 
+int launch_rope_rows(grilly_ctx* ctx, bool bf16, const void* src, void* dst, long long rows, long long pitch, int H, int D,
+                     int S, const int* cu_seqlens, int B, const float* cos_t, const float* sin_t, int style) {
+  const int elt = bf16 ? 2 : 4;
+  const int pieces = D / (16 / elt);
+  const long long total = rows * H * (style == 1 ? pieces : pieces / 2);
+  if (total <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "rope: sizes must be positive");
+  const int grid = grid_for(total, 256, ctx->num_sms, 16);
+  const int pi = prof_begin(ctx, PROF_OTHER, 0.0, 2.0 * rows * H * D * elt);
+  if (bf16) rope_rows_kernel<true><<<grid, 256, 0, ctx->stream>>>(src, dst, rows, pitch, H, D, S, cu_seqlens, B, cos_t, sin_t, style);
+  else rope_rows_kernel<false><<<grid, 256, 0, ctx->stream>>>(src, dst, rows, pitch, H, D, S, cu_seqlens, B, cos_t, sin_t, style);
+  prof_end(ctx, pi);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+
 int launch_rope_apply(grilly_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,
                       const int* position_ids, int B, int S, int H, int D, int style) {
   const long long n_pairs = static_cast<long long>(B) * S * H * (D / 2);

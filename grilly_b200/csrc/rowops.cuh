@@ -327,6 +327,87 @@ __global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__
   }
 }
 
+// RoPE pre-pass for long-sequence attention: rotates every head of a 2-D view [rows][pitch] (head h in columns
+// [h*D, (h+1)*D)) into a dense [rows][H*D] copy. A row's position is its index inside its sequence (padded: row % S,
+// packed: row - cu_seqlens[b]). One thread per 16-byte piece (interleaved) or per pair of pieces (rotate-half).
+template <bool kBf16>
+__global__ void __launch_bounds__(256) rope_rows_kernel(const void* __restrict__ src, void* __restrict__ dst, long long rows,
+                                                        long long pitch, int H, int D, int S, const int* __restrict__ cu_seqlens,
+                                                        int B, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                        int style) {
+  constexpr int ELT = kBf16 ? 2 : 4;
+  constexpr int EPP = 16 / ELT;
+  const int pieces = D / EPP;
+  const int work_per_head = style == 1 ? pieces : pieces / 2;
+  const long long total = rows * H * work_per_head;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const int w = static_cast<int>(idx % work_per_head);
+    const long long rh = idx / work_per_head;
+    const int h = static_cast<int>(rh % H);
+    const long long row = rh / H;
+    int pos;
+    if (cu_seqlens) {
+      int lo = 0, hi = B;  // last b with cu_seqlens[b] <= row
+      while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (cu_seqlens[mid] <= row) lo = mid; else hi = mid; }
+      pos = static_cast<int>(row - cu_seqlens[lo]);
+    } else {
+      pos = static_cast<int>(row % S);
+    }
+    pos = min(pos, S - 1);
+    const float* ct = cos_t + static_cast<long long>(pos) * (D / 2);
+    const float* st = sin_t + static_cast<long long>(pos) * (D / 2);
+    const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(src) + (row * pitch + h * D) * ELT);
+    uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst) + (row * H + h) * static_cast<long long>(D) * ELT);
+    auto unpack = [&](const uint4& q, float* f) {
+      if constexpr (kBf16) {
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(hh[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+      } else {
+        f[0] = __uint_as_float(q.x); f[1] = __uint_as_float(q.y); f[2] = __uint_as_float(q.z); f[3] = __uint_as_float(q.w);
+      }
+    };
+    auto pack = [&](const float* f) -> uint4 {
+      uint4 q;
+      if constexpr (kBf16) {
+        q.x = pack_bf16x2(f[0], f[1]); q.y = pack_bf16x2(f[2], f[3]); q.z = pack_bf16x2(f[4], f[5]); q.w = pack_bf16x2(f[6], f[7]);
+      } else {
+        q.x = __float_as_uint(round_to_tf32(f[0])); q.y = __float_as_uint(round_to_tf32(f[1]));
+        q.z = __float_as_uint(round_to_tf32(f[2])); q.w = __float_as_uint(round_to_tf32(f[3]));
+      }
+      return q;
+    };
+    if (style == 1) {
+      float f[EPP];
+      unpack(sp[w], f);
+#pragma unroll
+      for (int e = 0; e < EPP; e += 2) {
+        const int i = (w * EPP + e) >> 1;
+        const float c = __ldg(ct + i), sn = __ldg(st + i);
+        const float x0 = f[e], x1 = f[e + 1];
+        f[e] = x0 * c - x1 * sn;
+        f[e + 1] = x0 * sn + x1 * c;
+      }
+      dp[w] = pack(f);
+    } else {
+      float f0[EPP], f1[EPP];
+      unpack(sp[w], f0);
+      unpack(sp[w + pieces / 2], f1);
+#pragma unroll
+      for (int e = 0; e < EPP; ++e) {
+        const int i = w * EPP + e;
+        const float c = __ldg(ct + i), sn = __ldg(st + i);
+        const float x0 = f0[e], x1 = f1[e];
+        f0[e] = x0 * c - x1 * sn;
+        f1[e] = x1 * c + x0 * sn;
+      }
+      dp[w] = pack(f0);
+      dp[w + pieces / 2] = pack(f1);
+    }
+  }
+}
+
 // Stand-alone RoPE on a [B][S][H][D] tensor (apply_rope): out may alias x.
 __global__ void __launch_bounds__(256) rope_apply_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,

@@ -69,6 +69,19 @@ def test_rope_variant(backend, style, D):
     assert O.rel_l2(o2, O.flash_attention2_rope(q, k, v, rope_scaling=2.0, rope_base=500.0, rope_style=style)) < TOL_TF32
 
 
+@pytest.mark.parametrize("style", ["interleaved", "rotate_half"])
+def test_rope_long_sequences_use_the_prepass(backend, style):
+    """Beyond 256 positions Q and K are rotated once into scratch instead of on every tile load: same result."""
+    rng = np.random.default_rng(77)
+    q, k, v = (rng.standard_normal((1, 600, 3, 64)).astype(np.float32) for _ in range(3))
+    o = backend.attention.flash_attention2_rope(q, k, v, causal=True, rope_style=style)
+    assert O.rel_l2(o, O.flash_attention2_rope(q, k, v, causal=True, rope_style=style)) < TOL_TF32
+    lens = np.array([311])
+    mask = (np.arange(600)[None, :] < lens[:, None]).astype(np.float32)
+    o = backend.attention.flash_attention2_rope(q, k, v, mask=mask, rope_style=style, rope_scaling=4.0)
+    assert O.rel_l2(o, O.flash_attention2_rope(q, k, v, mask=mask, rope_style=style, rope_scaling=4.0)) < TOL_TF32
+
+
 def test_apply_rope_against_reference_outputs(backend, golden):
     a = cases.attention_cfg1()
     q1 = a["q"][:1]
