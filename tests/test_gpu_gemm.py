@@ -159,6 +159,20 @@ def test_gemm_mnk_full_size_property(backend):
     assert O.rel_l2(u @ c.astype(np.float64), (u @ a.astype(np.float64)) @ b.astype(np.float64)) < TOL_TF32
 
 
+def test_gemm_mnk_largest_sweep_size(backend):
+    """M = N = K = 16384, the largest size of the sweep, through the same checksum property (1 GiB per matrix)."""
+    n = 16384
+    rng = np.random.default_rng(4 + 14)
+    a = rng.standard_normal((n, n), dtype=np.float32)
+    b = rng.standard_normal((n, n), dtype=np.float32)
+    c = backend.fnn.gemm(a, b)
+    # float32 matrix-vector products here (error ~1e-5, far below the tolerance) keep the check to a few seconds
+    v = rng.standard_normal((n, 2)).astype(np.float32)
+    assert O.rel_l2(c @ v, a @ (b @ v)) < TOL_TF32
+    u = rng.standard_normal((2, n)).astype(np.float32)
+    assert O.rel_l2(u @ c, (u @ a) @ b) < TOL_TF32
+
+
 def test_bf16_mode(backend_bf16):
     c = cases.linear_cfg0()
     y = backend_bf16.fnn.fused_linear_gelu(c["x"], c["w"], c["b"])
