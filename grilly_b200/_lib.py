@@ -43,6 +43,7 @@ SIGNATURES = {
     "grilly_set_stream": [_vp, _vp],
     "grilly_sync": [_vp],
     "grilly_launch_count": [_vp, C.POINTER(C.c_uint64)],
+    "grilly_selftest_wait_timeout": [_vp, _i],
     "grilly_timer_start": [_vp],
     "grilly_timer_stop": [_vp, C.POINTER(C.c_float)],
     "grilly_profile_begin": [_vp],

@@ -76,9 +76,9 @@ def _nsplit(a):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("op", choices=["linear", "gemm", "attention", "layernorm"])
-    ap.add_argument("--m", type=int, default=18432)
-    ap.add_argument("--n", type=int, default=1536)
-    ap.add_argument("--k", type=int, default=384)
+    ap.add_argument("--m", "--dim-m", dest="m", type=int, default=18432)
+    ap.add_argument("--n", "--dim-n", dest="n", type=int, default=1536)
+    ap.add_argument("--k", "--dim-k", dest="k", type=int, default=384)
     ap.add_argument("--act", default="none", choices=["none", "gelu", "silu", "relu"])
     ap.add_argument("--residual", action="store_true")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])

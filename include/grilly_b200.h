@@ -64,6 +64,10 @@ int grilly_launch_count(grilly_ctx* ctx, uint64_t* count);
  * tutorials time with perf_counter, tutorials/02_fused_operations.py:29-39). Between begin and end every launch is
  * bracketed by an event pair. out has 6 classes x 4 doubles: {launches, milliseconds, algorithmic FLOPs,
  * algorithmic bytes} for class 0 GEMM, 1 attention, 2 norm, 3 embedding, 4 pooling, 5 other. */
+/* Failure-detection self-test: launches a kernel whose only wait (on a barrier nothing signals) runs out after
+ * budget_ms (1..1000). The kernel returns normally; the next grilly_sync() reports GRILLY_ERR_TIMEOUT once and the
+ * context keeps working. The reference has no counterpart (its dispatch blocks in vkQueueWaitIdle, backend/core.py:418). */
+int grilly_selftest_wait_timeout(grilly_ctx* ctx, int budget_ms);
 /* Device-side stopwatch: start records an event on the context's stream, stop records a second one, waits for it
  * and returns the milliseconds between the two. */
 int grilly_timer_start(grilly_ctx* ctx);

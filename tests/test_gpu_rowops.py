@@ -82,3 +82,19 @@ def test_device_resident_chain(backend):
     assert isinstance(y, DeviceTensor)
     ref = O.linear(O.fused_linear_gelu(O.layernorm(x), w1), w2)
     assert O.rel_l2(y.numpy(), ref) < 2e-3
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(backend):
+    """Failure detection without a GPU fault: a device-side wait on a flag nothing sets gives up after its budget,
+    the host reads GRILLY_ERR_TIMEOUT, and the same context then computes correctly."""
+    from grilly_b200 import _lib as L
+
+    dev = backend.device
+    dev.sync()
+    dev.check(dev.lib.grilly_selftest_wait_timeout(dev.ctx, 50))
+    with pytest.raises(L.GrillyError) as ei:
+        dev.sync()
+    assert ei.value.code == L.ERR_TIMEOUT
+    dev.sync()  # the status word was cleared: no second report
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    assert np.array_equal(backend.fnn.activation_relu(x - 5), np.maximum(x - 5, 0))
