@@ -363,19 +363,68 @@ class Attention(_Namespace):
                                                   float(rope_scaling), L.ROPE_ROTATE_HALF))
         return self._out(y, host)
 
-    def _unfused(self, name):
-        raise NotImplementedError(
-            f"{name}: the unfused scores/mask/output pipeline (which materialises a (B,H,S,S) tensor) is replaced by "
-            "flash_attention2(q, k, v, mask=..., causal=...)")
+    # ---- the unfused pipeline (what VulkanSentenceTransformer._attention_gpu calls): kept for drop-in use;
+    #      flash_attention2 computes the same result without the (B,H,S,S) tensor
+    def _bshd(self, t, num_heads, head_dim):
+        shape = tuple(t.shape)
+        if len(shape) == 4:
+            return tuple(int(s) for s in shape)
+        if len(shape) == 3 and shape[2] == num_heads * head_dim:
+            return int(shape[0]), int(shape[1]), int(num_heads), int(head_dim)
+        raise ValueError("expected (B, S, H, D) or (B, S, H*D)")
 
-    def attention_scores(self, *a, **k):
-        self._unfused("attention_scores")
+    def attention_scores(self, queries, keys, num_heads, head_dim, scale=None):
+        """scale * Q K^T -> (B, H, S, S): backend/attention.py:41-126."""
+        B, S, H, D = self._bshd(queries, num_heads, head_dim)
+        if tuple(keys.shape) != tuple(queries.shape):
+            raise ValueError("queries and keys must have the same shape")
+        qd, host = self._act_in(queries, mma_operand=False)
+        kd, _ = self._act_in(keys, mma_operand=False)
+        out = self.dev.empty((B, H, S, S))
+        sc = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+        self.dev.check(self.lib.grilly_attention_scores(self.ctx, _p(qd), _p(kd), _p(out), B, S, H, D, sc))
+        return self._out(out, host)
 
-    def attention_mask(self, *a, **k):
-        self._unfused("attention_mask")
+    def attention_mask(self, attention_scores, use_causal=True, mask_value=-1e9, custom_mask=None):
+        """Causal or key-padding mask on (B, H, S, S) scores: backend/attention.py:128-203."""
+        shape = tuple(int(s) for s in attention_scores.shape)
+        if len(shape) != 4 or shape[2] != shape[3]:
+            raise ValueError("attention_scores must be (B, H, S, S)")
+        B, H, S, _ = shape
+        if not use_causal and custom_mask is None:
+            return np.asarray(attention_scores, dtype=np.float32) if not isinstance(attention_scores, DeviceTensor) else attention_scores
+        if isinstance(attention_scores, DeviceTensor):
+            sd, host = attention_scores, False
+        else:
+            sd, host = self.dev.upload(np.asarray(attention_scores, np.float32)), True
+        md = None
+        if not use_causal:
+            if tuple(custom_mask.shape) != (B, S):
+                raise ValueError(f"custom_mask must have shape {(B, S)}")
+            md, _ = self._act_in(np.asarray(custom_mask, np.float32) if not isinstance(custom_mask, DeviceTensor) else custom_mask,
+                                 mma_operand=False)
+        self.dev.check(self.lib.grilly_attention_mask(self.ctx, _p(sd), _p(md), B, H, S, int(bool(use_causal)), float(mask_value)))
+        return self._out(sd, host)
 
-    def attention_output(self, *a, **k):
-        self._unfused("attention_output")
+    def attention_output(self, attention_weights, values, num_heads, head_dim):
+        """weights @ V -> (B, S, H, D): backend/attention.py:205-300."""
+        wshape = tuple(int(s) for s in attention_weights.shape)
+        if len(wshape) != 4:
+            raise ValueError("attention_weights must be (B, H, S, S)")
+        B, H, S, _ = wshape
+        vB, vS, vH, D = self._bshd(values, num_heads, head_dim)
+        if (vB, vS, vH) != (B, S, H):
+            raise ValueError("values do not match the attention weights")
+        wd, host = self._act_in(attention_weights, mma_operand=False)
+        vd, _ = self._act_in(values, mma_operand=False)
+        out = self.dev.empty((B, S, H, D))
+        self.dev.check(self.lib.grilly_attention_output(self.ctx, _p(wd), _p(vd), _p(out), B, S, H, D))
+        return self._out(out, host)
+
+    def attention_concat_heads(self, attention_output):
+        """(B, S, H, D) -> (B, S, H*D): backend/attention.py:302-359 (a reshape in this layout)."""
+        B, S, H, D = (int(s) for s in attention_output.shape)
+        return attention_output.reshape(B, S, H * D)
 
 
 class Pooling(_Namespace):

@@ -437,6 +437,24 @@ int grilly_flash_attention(grilly_ctx* ctx, const void* q, const void* k, const 
   return launch_attention(ctx, bf16, q, k, v, ld_qkv, ld_qkv, ld_qkv, total_rows, a);
 }
 
+int grilly_attention_scores(grilly_ctx* ctx, const float* q, const float* k, float* scores, int B, int S, int H, int D, float scale) {
+  CTX_GUARD(ctx);
+  if (!q || !k || !scores) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_scores: null operand");
+  return launch_attn_scores(ctx, q, k, scores, B, S, H, D, scale);
+}
+
+int grilly_attention_mask(grilly_ctx* ctx, float* scores, const float* mask, int B, int H, int S, int use_causal, float mask_value) {
+  CTX_GUARD(ctx);
+  if (!scores) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_mask: null operand");
+  return launch_attn_mask(ctx, scores, mask, B, H, S, use_causal ? 1 : 0, mask_value);
+}
+
+int grilly_attention_output(grilly_ctx* ctx, const float* weights, const float* v, float* out, int B, int S, int H, int D) {
+  CTX_GUARD(ctx);
+  if (!weights || !v || !out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_output: null operand");
+  return launch_attn_output(ctx, weights, v, out, B, S, H, D);
+}
+
 int grilly_apply_rope(grilly_ctx* ctx, const float* x, float* y, const int* position_ids, int B, int S, int H, int D,
                       int max_pos, float base, float scaling, int rope_style) {
   CTX_GUARD(ctx);

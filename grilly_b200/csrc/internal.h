@@ -110,6 +110,9 @@ int launch_pool(grilly_ctx* ctx, const PoolArgs& a);
 int launch_fold_ln(grilly_ctx* ctx, const float* w, const float* gamma, const float* beta, const float* bias, void* wf,
                    float* col_sum, float* bias_f, int N, int K, bool bf16);
 int get_rope_table(grilly_ctx* ctx, int S, int D, float base, float scaling, const float** cos_t, const float** sin_t);
+int launch_attn_scores(grilly_ctx* ctx, const float* q, const float* k, float* scores, int B, int S, int H, int D, float scale);
+int launch_attn_mask(grilly_ctx* ctx, float* scores, const float* mask, int B, int H, int S, int use_causal, float mask_value);
+int launch_attn_output(grilly_ctx* ctx, const float* w, const float* v, float* out, int B, int S, int H, int D);
 int launch_rope_rows(grilly_ctx* ctx, bool bf16, const void* src, void* dst, long long rows, long long pitch, int H, int D,
                      int S, const int* cu_seqlens, int B, const float* cos_t, const float* sin_t, int style);
 int launch_rope_apply(grilly_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,

@@ -166,6 +166,30 @@ int get_rope_table(grilly_ctx* ctx, int S, int D, float base, float scaling, con
   return GRILLY_OK;
 }
 
+int launch_attn_scores(grilly_ctx* ctx, const float* q, const float* k, float* scores, int B, int S, int H, int D, float scale) {
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_scores: sizes must be positive");
+  attn_scores_kernel<<<grid_for(static_cast<long long>(B) * H * S, 8, ctx->num_sms), 256, 0, ctx->stream>>>(q, k, scores, B, S, H, D, scale);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+int launch_attn_mask(grilly_ctx* ctx, float* scores, const float* mask, int B, int H, int S, int use_causal, float mask_value) {
+  const long long n = static_cast<long long>(B) * H * S * S;
+  if (n <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_mask: sizes must be positive");
+  if (!use_causal && !mask) return GRILLY_OK;  // nothing to apply (backend/attention.py:157-160)
+  attn_mask_kernel<<<grid_for(n, 256 * 4, ctx->num_sms, 16), 256, 0, ctx->stream>>>(scores, mask, n, H, S, use_causal, mask_value);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+int launch_attn_output(grilly_ctx* ctx, const float* w, const float* v, float* out, int B, int S, int H, int D) {
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_output: sizes must be positive");
+  attn_output_kernel<<<grid_for(static_cast<long long>(B) * H * S, 8, ctx->num_sms), 256, 0, ctx->stream>>>(w, v, out, B, S, H, D);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+
 int launch_rope_rows(grilly_ctx* ctx, bool bf16, const void* src, void* dst, long long rows, long long pitch, int H, int D,
                      int S, const int* cu_seqlens, int B, const float* cos_t, const float* sin_t, int style) {
   const int elt = bf16 ? 2 : 4;

@@ -313,6 +313,60 @@ __global__ void __launch_bounds__(128) pool_normalize_kernel(const PoolArgs a) {
   for (int f = threadIdx.x; f < a.F; f += blockDim.x) a.out[static_cast<long long>(b) * a.F + f] = pooled[f] * inv;
 }
 
+// ---- unfused attention (compatibility with callers of attention_scores / attention_mask / attention_output) ----
+// These materialise the (B,H,S,S) tensor exactly as the reference's three dispatches do; plain fp32 FMAs.
+// scores[b,h,q,k] = scale * sum_d Q[b,q,h,d] K[b,k,h,d]; one warp per (b,h,q), lanes over keys.
+__global__ void __launch_bounds__(256) attn_scores_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                                          float* __restrict__ scores, int B, int S, int H, int D, float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long n_rows = static_cast<long long>(B) * H * S;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < n_rows;
+       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const int qi = static_cast<int>(row % S);
+    const int h = static_cast<int>((row / S) % H);
+    const int b = static_cast<int>(row / (static_cast<long long>(S) * H));
+    const float* qp = q + ((static_cast<long long>(b) * S + qi) * H + h) * D;
+    for (int kk = lane; kk < S; kk += 32) {
+      const float* kp = k + ((static_cast<long long>(b) * S + kk) * H + h) * D;
+      float acc = 0.f;
+      for (int d = 0; d < D; ++d) acc = fmaf(__ldg(qp + d), __ldg(kp + d), acc);
+      scores[row * S + kk] = acc * scale;
+    }
+  }
+}
+// causal: key > query -> mask_value; otherwise key-padding mask (B,S), < 0.5 -> mask_value (attention-mask.glsl:42-53)
+__global__ void __launch_bounds__(256) attn_mask_kernel(float* __restrict__ scores, const float* __restrict__ mask, long long n,
+                                                        int H, int S, int use_causal, float mask_value) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int kk = static_cast<int>(i % S);
+    const int qi = static_cast<int>((i / S) % S);
+    const long long b = i / (static_cast<long long>(S) * S * H);
+    if (use_causal) { if (kk > qi) scores[i] = mask_value; }
+    else if (mask[b * S + kk] < 0.5f) scores[i] = mask_value;
+  }
+}
+// out[b,q,h,:] = sum_k W[b,h,q,k] V[b,k,h,:]; one warp per (b,h,q), lanes over the head dim.
+__global__ void __launch_bounds__(256) attn_output_kernel(const float* __restrict__ w, const float* __restrict__ v,
+                                                          float* __restrict__ out, int B, int S, int H, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long n_rows = static_cast<long long>(B) * H * S;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < n_rows;
+       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const int qi = static_cast<int>(row % S);
+    const int h = static_cast<int>((row / S) % H);
+    const int b = static_cast<int>(row / (static_cast<long long>(S) * H));
+    const float* wp = w + row * S;
+    for (int d = lane; d < D; d += 32) {
+      float acc = 0.f;
+      for (int kk = 0; kk < S; ++kk) acc = fmaf(__ldg(wp + kk), __ldg(v + ((static_cast<long long>(b) * S + kk) * H + h) * D + d), acc);
+      out[((static_cast<long long>(b) * S + qi) * H + h) * D + d] = acc;
+    }
+  }
+}
+
 // cos/sin tables for RoPE: theta(pos, i) = (pos / scaling) * base^(-2 i / D), computed in double.
 __global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__ sin_t, int S, int D, float base, float scaling) {
   const int half = D / 2;

@@ -149,6 +149,19 @@ int grilly_flash_attention(grilly_ctx* ctx, const void* q_dev, const void* k_dev
                            int B, int S, int H, int D, long long ld_qkv, long long ld_out, const int* cu_seqlens_dev,
                            long long total_rows, const float* key_mask_dev, float scale, int causal, int rope_style,
                            float rope_base, float rope_scaling, int precision, int flags);
+/* The unfused pipeline the reference's encoder calls today (utils/vulkan_sentence_transformer.py:1037-1067), kept so
+ * that code runs unchanged; it materialises (B,H,S,S) like the reference does. fp32 FMAs, no tensor cores.
+ * VulkanAttention.attention_scores backend/attention.py:41-126 (attention-scores.glsl:33-65): q,k (B,S,H,D) ->
+ * scores (B,H,S,S) = scale * Q K^T. */
+int grilly_attention_scores(grilly_ctx* ctx, const float* q_dev, const float* k_dev, float* scores_dev, int B, int S, int H,
+                            int D, float scale);
+/* attention_mask backend/attention.py:128-203 (attention-mask.glsl:26-55), in place: use_causal -> key > query gets
+ * mask_value; else key-padding mask_dev (B,S), < 0.5 gets mask_value (NULL = no change). */
+int grilly_attention_mask(grilly_ctx* ctx, float* scores_dev, const float* mask_dev, int B, int H, int S, int use_causal,
+                          float mask_value);
+/* attention_output backend/attention.py:205-300 (attention-output.glsl:28-70): weights (B,H,S,S), v (B,S,H,D) -> (B,S,H,D) */
+int grilly_attention_output(grilly_ctx* ctx, const float* weights_dev, const float* v_dev, float* out_dev, int B, int S,
+                            int H, int D);
 /* stand-alone RoPE on (B,S,H,D) fp32, VulkanAttention.apply_rope backend/attention.py:599-676 (rope.glsl:52-126);
  * position_ids_dev int32 [B][S] or NULL for 0..S-1; max_pos = number of table rows to build. */
 int grilly_apply_rope(grilly_ctx* ctx, const float* x_dev, float* y_dev, const int* position_ids_dev, int B, int S,

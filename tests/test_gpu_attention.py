@@ -106,5 +106,31 @@ def test_errors(backend):
     with pytest.raises(ValueError):
         backend.attention.flash_attention2(np.zeros((1, 4, 64), np.float32), np.zeros((1, 4, 64), np.float32),
                                            np.zeros((1, 4, 64), np.float32))
-    with pytest.raises(NotImplementedError):
-        backend.attention.attention_scores(z, z, 2, 48)
+
+
+def test_unfused_pipeline_matches_flash_and_oracle(backend):
+    """The four calls the reference's encoder makes today (utils/vulkan_sentence_transformer.py:1037-1067):
+    attention_scores -> attention_mask(custom) -> activation_softmax -> attention_output."""
+    rng = np.random.default_rng(5)
+    B, S, H, D = 3, 50, 12, 32
+    q, k, v = (rng.standard_normal((B, S, H, D)).astype(np.float32) for _ in range(3))
+    lens = np.array([50, 7, 31])
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.float32)
+    a = backend.attention
+    scores = a.attention_scores(q, k, H, D)
+    assert scores.shape == (B, H, S, S)
+    ref_scores = np.einsum("bqhd,bkhd->bhqk", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(D)
+    assert O.rel_l2(scores, ref_scores) < 1e-6
+    masked = a.attention_mask(scores, use_causal=False, mask_value=-1e9, custom_mask=mask)
+    assert np.all(masked[1, :, :, 7:] == np.float32(-1e9)) and np.array_equal(masked[0], scores[0])
+    w = backend.fnn.activation_softmax(masked.reshape(-1, S), axis=-1).reshape(masked.shape)
+    out = a.attention_output(w, v, H, D)
+    assert out.shape == (B, S, H, D)
+    ref = O.attention(q, k, v, key_mask=mask)
+    assert O.rel_l2(out, ref) < 1e-5                                     # fp32 path
+    assert O.rel_l2(a.flash_attention2(q, k, v, mask=mask), out) < TOL_TF32
+    assert a.attention_concat_heads(out).shape == (B, S, H * D)
+    # causal variant and the 3-D input form
+    cm = a.attention_mask(a.attention_scores(q.reshape(B, S, H * D), k.reshape(B, S, H * D), H, D), use_causal=True)
+    assert np.all(cm[:, :, 3, 4:] == np.float32(-1e9)) and np.all(cm[:, :, 3, :4] == scores[:, :, 3, :4])
+    assert np.array_equal(a.attention_mask(scores, use_causal=False), scores)
