@@ -94,6 +94,7 @@ static int ensure_io(grilly_encoder* e, int B, int S) {
   if ((rc = enc_alloc(e, static_cast<size_t>(nB) * nS * sizeof(int), reinterpret_cast<void**>(&e->ids_dev)))) return rc;
   if ((rc = enc_alloc(e, static_cast<size_t>(2 * nB + 2) * sizeof(int), reinterpret_cast<void**>(&e->cu_dev)))) return rc;
   if ((rc = enc_alloc(e, static_cast<size_t>(nB) * e->cfg.hidden * sizeof(float), reinterpret_cast<void**>(&e->out_dev)))) return rc;
+  if ((rc = enc_alloc(e, static_cast<size_t>(nB) * nS * sizeof(float), reinterpret_cast<void**>(&e->mask_dev)))) return rc;
   GB_CUDA_CHECK(e->ctx, cudaMallocHost(&e->ids_pin, static_cast<size_t>(nB) * nS * sizeof(int)));
   GB_CUDA_CHECK(e->ctx, cudaMallocHost(&e->cu_pin, static_cast<size_t>(2 * nB + 2) * sizeof(int)));
   GB_CUDA_CHECK(e->ctx, cudaMallocHost(&e->out_pin, static_cast<size_t>(nB) * e->cfg.hidden * sizeof(float)));
@@ -121,7 +122,8 @@ static int enc_norm(grilly_encoder* e, const float* x, const float* g, const flo
 
 // Runs one chunk: sequences [b0, b1) whose packed rows are [0, rows) of the workspace.
 static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_dev, int b0, int b1, int S, int rows,
-                     int max_len, float* out_dev, long long hidden_row0, double sum_len2) {
+                     int max_len, float* out_dev, long long hidden_row0, double sum_len2,
+                     const float* key_mask_dev = nullptr) {
   grilly_ctx* ctx = e->ctx;
   const auto& c = e->cfg;
   const int F = c.hidden, H = c.num_heads, D = F / H, Bc = b1 - b0;
@@ -137,6 +139,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
     AttnArgs at{};
     at.B = Bc; at.S = max_len; at.H = H; at.D = D; at.cu_seqlens = cu_chunk_dev; at.scale = 1.0f / sqrtf(static_cast<float>(D));
     at.out = e->attn; at.ld_out = F; at.round_tf32 = 1;
+    at.key_mask = key_mask_dev;   // padded layout only (cu_chunk_dev is null then)
     ctx->attn_flops_hint = 4.0 * H * D * sum_len2;  // valid (query, key) pairs only
     if ((rc = launch_attention(ctx, false, e->qkv, e->qkv + F, e->qkv + 2 * F, 3LL * F, 3LL * F, 3LL * F, rows, at))) return rc;
     if ((rc = enc_linear(e, e->attn, L.wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE))) return rc;
@@ -146,7 +149,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
     if ((rc = enc_norm(e, e->t, L.ln2_g, L.ln2_b, e->x, rows))) return rc;
   }
   PoolArgs p{};
-  p.x = e->x; p.cu_seqlens = cu_chunk_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
+  p.x = e->x; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
   if ((rc = launch_pool(ctx, p))) return rc;
   if (e->keep_hidden && e->hidden_all)
     GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->hidden_all + hidden_row0 * F, e->x, static_cast<size_t>(rows) * F * sizeof(float),
@@ -226,6 +229,32 @@ static int forward_device_nolock(grilly_encoder* e, const int* ids_dev, const in
     }
     if ((rc = run_chunk(e, ids_dev, e->cu_dev + c.cu_off, c.b0, c.b1, S, c.rows, std::max(c.max_len, 1), out_dev, row0, c.sum_len2))) return rc;
     row0 += c.rows;
+  }
+  e->last_rows = total;
+  return GRILLY_OK;
+}
+
+// Masks that are not a run of ones followed by zeros cannot be packed: run on the padded layout (B*S rows) with the
+// mask applied as a key mask in attention and as the pooling mask, exactly as the reference does.
+static int forward_padded_nolock(grilly_encoder* e, const int* ids_dev, const float* mask_dev, int B, int S, float* out_dev) {
+  grilly_ctx* ctx = e->ctx;
+  if (S > e->cfg.max_pos) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sequence length exceeds the position table");
+  int per_chunk = B;
+  if (e->cfg.chunk_tokens > 0) per_chunk = std::max(1, e->cfg.chunk_tokens / S);
+  int rc = ensure_workspace(e, static_cast<long long>(std::min(per_chunk, B)) * S);
+  if (rc) return rc;
+  const long long total = static_cast<long long>(B) * S;
+  if (e->keep_hidden && total > e->hidden_cap) {
+    enc_release(e, e->hidden_all);
+    e->hidden_all = nullptr;
+    if ((rc = enc_alloc(e, static_cast<size_t>(total) * e->cfg.hidden * sizeof(float), reinterpret_cast<void**>(&e->hidden_all)))) return rc;
+    e->hidden_cap = total;
+  }
+  for (int b0 = 0; b0 < B; b0 += per_chunk) {
+    const int b1 = std::min(B, b0 + per_chunk);
+    const int rows = (b1 - b0) * S;
+    if ((rc = run_chunk(e, ids_dev, nullptr, b0, b1, S, rows, S, out_dev, static_cast<long long>(b0) * S,
+                        static_cast<double>(b1 - b0) * S * S, mask_dev + static_cast<long long>(b0) * S))) return rc;
   }
   e->last_rows = total;
   return GRILLY_OK;
@@ -338,21 +367,28 @@ int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* 
   if (rc) return rc;
   // valid lengths from the mask; the packed path needs every mask row to be a prefix of ones
   std::vector<int> lengths(B);
-  for (int b = 0; b < B; ++b) {
+  bool holes = false;
+  for (int b = 0; b < B && !holes; ++b) {
     int len = S;
     if (mask_host) {
       const float* m = mask_host + static_cast<size_t>(b) * S;
       len = 0;
       while (len < S && m[len] > 0.5f) ++len;
       for (int s = len; s < S; ++s)
-        if (m[s] > 0.5f) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder_forward: attention_mask rows must be a run of ones followed by zeros");
+        if (m[s] > 0.5f) { holes = true; break; }
     }
     lengths[b] = len;
   }
   const size_t n_ids = static_cast<size_t>(B) * S;
   std::memcpy(e->ids_pin, ids_host, n_ids * sizeof(int));
   GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->ids_dev, e->ids_pin, n_ids * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-  if ((rc = forward_device_nolock(e, e->ids_dev, lengths.data(), B, S, e->out_dev, e->cu_pin))) return rc;
+  if (holes) {
+    GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->mask_dev, mask_host, n_ids * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    rc = forward_padded_nolock(e, e->ids_dev, e->mask_dev, B, S, e->out_dev);
+  } else {
+    rc = forward_device_nolock(e, e->ids_dev, lengths.data(), B, S, e->out_dev, e->cu_pin);
+  }
+  if (rc) return rc;
   const size_t out_bytes = static_cast<size_t>(B) * e->cfg.hidden * sizeof(float);
   GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->out_pin, e->out_dev, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
   GB_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->err_host, ctx->err_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));

@@ -94,7 +94,7 @@ class SentenceEncoder:
             self._set("ln2_g", i, lw["ffn_ln_gamma"]); self._set("ln2_b", i, lw["ffn_ln_beta"])
 
     def encode_ids(self, input_ids, attention_mask=None, out: np.ndarray | None = None) -> np.ndarray:
-        """input_ids (B, S) ints, attention_mask (B, S) 1 = token / 0 = padding (a run of ones then zeros per row).
+        """input_ids (B, S) ints, attention_mask (B, S) 1 = token / 0 = padding (prefix masks run packed, masks with holes run padded).
         Returns float32 (B, hidden). Host buffers in, host buffer out: both copies are part of the call."""
         ids = np.ascontiguousarray(input_ids, dtype=np.int32)
         if ids.ndim != 2:

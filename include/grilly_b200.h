@@ -208,7 +208,9 @@ int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, gri
  * ln2_g, ln2_b} (layer >= 0); data are fp32 host arrays in the reference's (out, in) layout. */
 int grilly_encoder_set_weight(grilly_encoder* enc, const char* name, int layer, const float* data_host, size_t count);
 /* ids_host int32 [B][S]; mask_host fp32 [B][S] (1 = token, 0 = padding) or NULL; out_host fp32 [B][hidden]:
- * mean-pooled, L2-normalised embeddings.  Includes the host->device and device->host copies. */
+ * mean-pooled, L2-normalised embeddings.  Includes the host->device and device->host copies.  Rows of ones followed
+ * by zeros run packed (padding rows never exist on the device); a mask with holes runs the whole batch on the padded
+ * layout with the mask as attention key mask and pooling mask. */
 int grilly_encoder_forward(grilly_encoder* enc, const int* ids_host, const float* mask_host, int B, int S,
                            float* out_host);
 /* same with device buffers and no copies: ids_dev int32 [B][S], lengths_host int32 [B] valid prefix lengths,
