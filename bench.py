@@ -63,7 +63,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.gpu), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -152,6 +152,8 @@ def main():
     ap.add_argument("--impl", default="grilly_b200", choices=["grilly_b200", "reference"])
     ap.add_argument("--chunk-tokens", type=int, default=int(os.environ.get("GRILLY_CHUNK_TOKENS", "0")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"],
+                    help="tf32 (default, the fp32-parity mode the headline is quoted in) or bf16")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -184,7 +186,8 @@ def main():
     dev = grilly_b200.Device(local_rank)
     rng = np.random.default_rng(2)  # same weights on every rank (replicated model)
     weights = grilly_b200.EncoderWeights.random(rng, CFG["num_layers"], CFG["hidden"], CFG["ffn"], CFG["vocab"], CFG["max_pos"])
-    enc = grilly_b200.SentenceEncoder(weights, num_heads=CFG["heads"], device=dev, chunk_tokens=args.chunk_tokens)
+    enc = grilly_b200.SentenceEncoder(weights, num_heads=CFG["heads"], device=dev, chunk_tokens=args.chunk_tokens,
+                                      precision=args.precision)
     ids, lens, mask = make_batch(rank)
     B, S, F = CFG["batch"], CFG["seq"], CFG["hidden"]
 
@@ -228,7 +231,6 @@ def main():
         step_ms.append(dev.timer_stop())
     barrier()
     launches = dev.launch_count() - launches0 - args.steps  # minus the flush launches
-    clocks = sampler.stop()
 
     # ---- timed region 2: end to end through the public API (host ids in, host embeddings out)
     e2e_ms = []
@@ -247,6 +249,7 @@ def main():
         l2_flush()
         step_device()
     prof = dev.profile_end()
+    clocks = sampler.stop()  # sampled across the three measurement passes (device-timed, end-to-end, per-kernel)
 
     total_ms, total_e2e_ms = sum(step_ms), sum(e2e_ms)
     if dist is not None:
@@ -261,8 +264,12 @@ def main():
             peaks = json.loads(pk_path.read_text())
         bf16_sustained = peaks.get("bf16_tflops_sustained")
         peak_tf32 = (bf16_sustained / 2.0) if bf16_sustained else 1590.0 / 2.0 * (1400.0 / 1590.0)
+        if args.precision == "bf16":
+            peak_tf32 *= 2.0
         peak_note = ("0.5 x measured sustained bf16 cuBLAS TFLOP/s (tf32 MMA rate is half the bf16 rate); of measured"
                      if bf16_sustained else "0.5 x fallback sustained bf16 figure; of fallback")
+        if args.precision == "bf16":
+            peak_note = "measured sustained bf16 cuBLAS TFLOP/s; of measured" if bf16_sustained else "fallback sustained bf16 figure; of fallback"
         g = prof["gemm"]
         gemm_tflops = g["flops"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else None
         a = prof["attention"]
@@ -277,7 +284,8 @@ def main():
         line = {
             "metric": "encoder_sentences_per_sec", "value": value, "unit": "sentences/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "tf32 (fp32 storage, fp32 accumulate)", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "tf32 (fp32 storage, fp32 accumulate)" if args.precision == "tf32" else "bf16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "global_batch": world * B, "seq_len": S, "valid_tokens_per_gpu": int(lens.sum()),
                        "parallelism": f"batch-sharded x{world}, no collective", "l2": "256 MB buffer rewritten between timed steps",
                        "chunk_tokens": args.chunk_tokens, "timing": "CUDA events around each step on the launching stream; L2 flush outside the events"},

@@ -14,6 +14,7 @@ struct GemmArgs {
   const float* bias;      // [N] (pre-activation) or null
   const float* residual;  // [M][ld_res] fp32, added after the activation, or null
   long long ld_res;
+  int residual_bf16;      // the residual tensor is bf16 instead of fp32
   void* out;              // [M][ld_out] fp32 or bf16
   long long ld_out;
   int out_bf16;
@@ -71,6 +72,7 @@ struct EmbedArgs {
   int B, S, F, vocab, max_pos;
   float eps;
   int round_tf32;
+  int out_bf16;            // write bf16 rows (bf16 encoder mode)
 };
 
 struct PoolArgs {

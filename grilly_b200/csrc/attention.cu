@@ -61,6 +61,7 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
   // one CTA per sequence walking all heads, split into head groups only while the grid is too small to fill the GPU
   int hpc = args.H;
   while (hpc > 1 && static_cast<long long>(args.B) * ((args.H + hpc - 1) / hpc) < 4LL * ctx->num_sms) hpc = (hpc + 1) / 2;
+  hpc = (hpc + Cfg::HPR - 1) / Cfg::HPR * Cfg::HPR;   // heads that share a loaded row chunk stay in one CTA
   dim3 grid(args.B, (args.H + hpc - 1) / hpc, 1);
   double flops = ctx->attn_flops_hint >= 0.0 ? ctx->attn_flops_hint : 4.0 * args.B * args.H * static_cast<double>(args.S) * args.S * D;
   ctx->attn_flops_hint = -1.0;
@@ -86,6 +87,7 @@ int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, c
   if (short_ok) {
     if (!bf16 && args.D == 32) return launch_short<32, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
     if (!bf16 && args.D == 64) return launch_short<64, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+    if (bf16 && args.D == 32) return launch_short<32, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
     if (bf16 && args.D == 64) return launch_short<64, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
     if (bf16 && args.D == 128) return launch_short<128, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   }
@@ -95,7 +97,7 @@ int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, c
   if (bf16 && args.D == 64) return launch_one<64, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   if (bf16 && args.D == 128) return launch_one<128, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   return set_error(ctx, GRILLY_ERR_UNSUPPORTED,
-                   "attention: head_dim must be 32 or 64 (tf32 mode) or 64 or 128 (bf16 mode)");
+                   "attention: head_dim must be 32 or 64 (tf32 mode), 64 or 128 (bf16 mode), or 32 in bf16 mode for sequences up to 128");
 }
 
 }  // namespace gb

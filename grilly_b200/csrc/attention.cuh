@@ -460,9 +460,13 @@ namespace gb {
 template <int D, bool kBf16>
 struct AttnShortCfg {
   static constexpr int ELT = kBf16 ? 2 : 4;
-  static constexpr int NCH = D * ELT / 128;
-  static_assert(D * ELT % 128 == 0 && NCH >= 1 && NCH <= 2, "head_dim*elt must be 128 or 256 bytes");
-  static constexpr int HEAD_BYTES = 3 * NCH * ATTN_CHUNK_BYTES;   // Q, K, V tiles of one head
+  static constexpr int ROW_BYTES = D * ELT;                       // bytes of one head in a token row
+  static_assert(ROW_BYTES == 64 || ROW_BYTES == 128 || ROW_BYTES == 256, "head_dim*elt must be 64, 128 or 256 bytes");
+  // A 64-byte head (head_dim 32 in bf16) is loaded together with its neighbour: the 128-byte swizzled row then
+  // holds two heads side by side and each head's MMAs start 0 or 64 bytes into the row.
+  static constexpr int HPR = ROW_BYTES < 128 ? 128 / ROW_BYTES : 1;   // heads per loaded row chunk
+  static constexpr int NCH = ROW_BYTES <= 128 ? 1 : ROW_BYTES / 128;
+  static constexpr int HEAD_BYTES = 3 * NCH * ATTN_CHUNK_BYTES;   // Q, K, V tiles of one head (or head pair)
   static constexpr int SMEM_BYTES = 2 * HEAD_BYTES + 1024 + 128;
   static constexpr int TMEM_COLS = 256;                           // S/P at [0,128), O at [128,128+D)
 };
@@ -474,6 +478,7 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   using Cfg = AttnShortCfg<D, kBf16>;
   constexpr int ELT = Cfg::ELT;
   constexpr int NCH = Cfg::NCH;
+  constexpr int HPR = Cfg::HPR;
   constexpr int CHE = 128 / ELT;
   constexpr int UMMA_K = 32 / ELT;
   constexpr int TILE_BYTES = NCH * ATTN_CHUNK_BYTES;
@@ -538,7 +543,8 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     if (lane == 0) {
       // -------------------------------------------------------- TMA + MMA issuer
       const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
-      auto load_head = [&](int h, int buf) {
+      // one load brings the Q, K, V tiles of HPR neighbouring heads (h_begin is a multiple of HPR)
+      auto load_group = [&](int h, int buf) {
         uint8_t* base = smem + buf * Cfg::HEAD_BYTES;
         mbar_expect_tx(&bar_load[buf], Cfg::HEAD_BYTES);
 #pragma unroll
@@ -548,16 +554,20 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           tma_load_2d(base + 2 * TILE_BYTES + c * ATTN_CHUNK_BYTES, &tmap_v, &bar_load[buf], h * D + c * CHE, row0);
         }
       };
-      load_head(h_begin, 0);
-      int i = 0;
+      load_group(h_begin, 0);
+      int i = 0, gi = -1, buf = 0;
       for (int h = h_begin; h < h_end; ++h, ++i) {
-        const int buf = i & 1;
         const uint32_t ph = i & 1;
-        // the other buffer was last read by the P V MMA of head h-1, whose completion was awaited below
-        if (h + 1 < h_end) load_head(h + 1, buf ^ 1);
-        if (!mbar_wait(&bar_load[buf], (i >> 1) & 1, abort_flag)) { ATTN_FAIL(); break; }
+        const int u = (h - h_begin) % HPR;            // position of this head inside its loaded group
+        if (u == 0) {
+          ++gi;
+          buf = gi & 1;
+          // the other buffer was last read by the P V MMA of the previous head, whose completion was awaited below
+          if (h + HPR < h_end) load_group(h + HPR, buf ^ 1);
+          if (!mbar_wait(&bar_load[buf], (gi >> 1) & 1, abort_flag)) { ATTN_FAIL(); break; }
+        }
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + buf * Cfg::HEAD_BYTES), sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
+        const uint32_t sQ = smem_u32(smem + buf * Cfg::HEAD_BYTES) + u * Cfg::ROW_BYTES, sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
 #pragma unroll
         for (int ks = 0; ks < D / UMMA_K; ++ks) {
           const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;

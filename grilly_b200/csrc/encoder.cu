@@ -23,6 +23,8 @@ using namespace gb;
 struct EncLayer {
   float *wqkv = nullptr, *bqkv = nullptr, *wo = nullptr, *bo = nullptr, *ln1_g = nullptr, *ln1_b = nullptr;
   float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+  // bf16 mode: the GEMM weights as bf16 (the fp32 slots above are then only the upload staging)
+  void *wqkv_h = nullptr, *wo_h = nullptr, *w1_h = nullptr, *w2_h = nullptr;
 };
 
 struct grilly_encoder {
@@ -32,7 +34,11 @@ struct grilly_encoder {
   std::vector<EncLayer> layers;
   // activation workspace for one chunk
   long long cap_rows = 0;
-  float *x = nullptr, *x2 = nullptr, *t = nullptr, *attn = nullptr, *qkv = nullptr, *h = nullptr;
+  // tf32 mode: all fp32. bf16 mode: x, x2, attn, qkv, h are bf16 (MMA operands and the residual they carry), the
+  // pre-LayerNorm sums t and the final hidden states xf stay fp32.
+  void *x = nullptr, *x2 = nullptr, *attn = nullptr, *qkv = nullptr, *h = nullptr;
+  float *t = nullptr, *xf = nullptr;
+  bool bf16 = false;
   // per-call buffers
   int cap_B = 0, cap_S = 0;
   int* ids_dev = nullptr;      // [B][S]
@@ -68,12 +74,14 @@ static void enc_release(grilly_encoder* e, void* p) {
 static int ensure_workspace(grilly_encoder* e, long long rows) {
   if (rows <= e->cap_rows) return GRILLY_OK;
   const int F = e->cfg.hidden, ffn = e->cfg.ffn;
-  float** bufs[6] = {&e->x, &e->x2, &e->t, &e->attn, &e->qkv, &e->h};
-  const long long widths[6] = {F, F, F, F, 3LL * F, ffn};
-  for (int i = 0; i < 6; ++i) {
+  const size_t act = e->bf16 ? 2 : 4;  // bytes per activation element that feeds an MMA
+  void** bufs[7] = {&e->x, &e->x2, reinterpret_cast<void**>(&e->t), &e->attn, &e->qkv, &e->h, reinterpret_cast<void**>(&e->xf)};
+  const size_t row_bytes[7] = {F * act, F * act, F * sizeof(float), F * act, 3 * F * act, ffn * act, e->bf16 ? F * sizeof(float) : 0};
+  for (int i = 0; i < 7; ++i) {
     enc_release(e, *bufs[i]);
     *bufs[i] = nullptr;
-    int rc = enc_alloc(e, static_cast<size_t>(rows) * widths[i] * sizeof(float), reinterpret_cast<void**>(bufs[i]));
+    if (row_bytes[i] == 0) continue;
+    int rc = enc_alloc(e, static_cast<size_t>(rows) * row_bytes[i], bufs[i]);
     if (rc) { e->cap_rows = 0; return rc; }
   }
   e->cap_rows = rows;
@@ -102,21 +110,26 @@ static int ensure_io(grilly_encoder* e, int B, int S) {
   return GRILLY_OK;
 }
 
-static int enc_linear(grilly_encoder* e, const float* x, const float* w, const float* bias, const float* residual, float* y,
-                      int M, int N, int K, int act) {
+static int enc_linear(grilly_encoder* e, const void* x, const void* w, const float* bias, const void* residual, void* y,
+                      int M, int N, int K, int act, bool out_fp32) {
   GemmArgs a{};
   a.M = M; a.N = N; a.K = K;
-  a.bias = bias; a.residual = residual; a.ld_res = N;
+  a.bias = bias; a.residual = reinterpret_cast<const float*>(residual); a.ld_res = N;
+  a.residual_bf16 = (residual && e->bf16) ? 1 : 0;
   a.out = y; a.ld_out = N;
   a.act = act;
-  a.round_tf32 = residual ? 0 : 1;  // outputs that feed an MMA directly are rounded; pre-LayerNorm sums stay fp32
-  return launch_gemm(e->ctx, false, false, x, w, a, 0);
+  a.out_bf16 = (e->bf16 && !out_fp32) ? 1 : 0;
+  // tf32 mode: outputs that feed an MMA directly are rounded to tf32; pre-LayerNorm sums stay full fp32
+  a.round_tf32 = (!e->bf16 && !out_fp32) ? 1 : 0;
+  return launch_gemm(e->ctx, e->bf16, false, x, w, a, 0);
 }
 
-static int enc_norm(grilly_encoder* e, const float* x, const float* g, const float* b, float* y, int rows) {
+static int enc_norm(grilly_encoder* e, const float* x, const float* g, const float* b, void* y, int rows, bool out_fp32) {
   NormArgs n{};
   n.x = x; n.gamma = g; n.beta = b; n.y = y; n.rows = rows; n.F = e->cfg.hidden; n.eps = e->cfg.layer_ln_eps;
-  n.mode = NORM_LAYER; n.round_tf32 = 1;
+  n.mode = NORM_LAYER;
+  n.out_bf16 = (e->bf16 && !out_fp32) ? 1 : 0;
+  n.round_tf32 = e->bf16 ? 0 : 1;
   return launch_norm(e->ctx, n);
 }
 
@@ -128,31 +141,41 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
   const auto& c = e->cfg;
   const int F = c.hidden, H = c.num_heads, D = F / H, Bc = b1 - b0;
   int rc;
+  const size_t act = e->bf16 ? 2 : 4;
   EmbedArgs em{};
   em.ids = ids_dev + static_cast<long long>(b0) * S; em.cu_seqlens = cu_chunk_dev; em.word = e->word; em.pos = e->pos;
-  em.type0 = c.has_token_type ? e->type : nullptr; em.gamma = e->emb_g; em.beta = e->emb_b; em.out = e->x;
-  em.B = Bc; em.S = S; em.F = F; em.vocab = c.vocab; em.max_pos = c.max_pos; em.eps = c.embed_ln_eps; em.round_tf32 = 1;
+  em.type0 = c.has_token_type ? e->type : nullptr; em.gamma = e->emb_g; em.beta = e->emb_b; em.out = reinterpret_cast<float*>(e->x);
+  em.B = Bc; em.S = S; em.F = F; em.vocab = c.vocab; em.max_pos = c.max_pos; em.eps = c.embed_ln_eps;
+  em.round_tf32 = e->bf16 ? 0 : 1; em.out_bf16 = e->bf16 ? 1 : 0;
   if ((rc = launch_embed(ctx, em))) return rc;
+  float* final_hidden = e->bf16 ? e->xf : reinterpret_cast<float*>(e->x);
   for (int l = 0; l < c.num_layers; ++l) {
     const EncLayer& L = e->layers[l];
-    if ((rc = enc_linear(e, e->x, L.wqkv, L.bqkv, nullptr, e->qkv, rows, 3 * F, F, ACT_NONE))) return rc;
+    const bool last = l + 1 == c.num_layers;
+    const void* wqkv = e->bf16 ? L.wqkv_h : static_cast<const void*>(L.wqkv);
+    const void* wo = e->bf16 ? L.wo_h : static_cast<const void*>(L.wo);
+    const void* w1 = e->bf16 ? L.w1_h : static_cast<const void*>(L.w1);
+    const void* w2 = e->bf16 ? L.w2_h : static_cast<const void*>(L.w2);
+    if ((rc = enc_linear(e, e->x, wqkv, L.bqkv, nullptr, e->qkv, rows, 3 * F, F, ACT_NONE, false))) return rc;
     AttnArgs at{};
     at.B = Bc; at.S = max_len; at.H = H; at.D = D; at.cu_seqlens = cu_chunk_dev; at.scale = 1.0f / sqrtf(static_cast<float>(D));
-    at.out = e->attn; at.ld_out = F; at.round_tf32 = 1;
+    at.out = e->attn; at.ld_out = F; at.round_tf32 = e->bf16 ? 0 : 1; at.out_bf16 = e->bf16 ? 1 : 0;
     at.key_mask = key_mask_dev;   // padded layout only (cu_chunk_dev is null then)
     ctx->attn_flops_hint = 4.0 * H * D * sum_len2;  // valid (query, key) pairs only
-    if ((rc = launch_attention(ctx, false, e->qkv, e->qkv + F, e->qkv + 2 * F, 3LL * F, 3LL * F, 3LL * F, rows, at))) return rc;
-    if ((rc = enc_linear(e, e->attn, L.wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE))) return rc;
-    if ((rc = enc_norm(e, e->t, L.ln1_g, L.ln1_b, e->x2, rows))) return rc;
-    if ((rc = enc_linear(e, e->x2, L.w1, L.b1, nullptr, e->h, rows, c.ffn, F, ACT_GELU_TANH))) return rc;
-    if ((rc = enc_linear(e, e->h, L.w2, L.b2, e->x2, e->t, rows, F, c.ffn, ACT_NONE))) return rc;
-    if ((rc = enc_norm(e, e->t, L.ln2_g, L.ln2_b, e->x, rows))) return rc;
+    const char* qkv = reinterpret_cast<const char*>(e->qkv);
+    if ((rc = launch_attention(ctx, e->bf16, qkv, qkv + F * act, qkv + 2 * F * act, 3LL * F, 3LL * F, 3LL * F, rows, at))) return rc;
+    if ((rc = enc_linear(e, e->attn, wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE, true))) return rc;
+    if ((rc = enc_norm(e, e->t, L.ln1_g, L.ln1_b, e->x2, rows, false))) return rc;
+    if ((rc = enc_linear(e, e->x2, w1, L.b1, nullptr, e->h, rows, c.ffn, F, ACT_GELU_TANH, false))) return rc;
+    if ((rc = enc_linear(e, e->h, w2, L.b2, e->x2, e->t, rows, F, c.ffn, ACT_NONE, true))) return rc;
+    // the last LayerNorm of the model feeds the pooling, which reads fp32
+    if ((rc = enc_norm(e, e->t, L.ln2_g, L.ln2_b, (last && e->bf16) ? static_cast<void*>(e->xf) : e->x, rows, last && e->bf16))) return rc;
   }
   PoolArgs p{};
-  p.x = e->x; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
+  p.x = final_hidden; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
   if ((rc = launch_pool(ctx, p))) return rc;
   if (e->keep_hidden && e->hidden_all)
-    GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->hidden_all + hidden_row0 * F, e->x, static_cast<size_t>(rows) * F * sizeof(float),
+    GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->hidden_all + hidden_row0 * F, final_hidden, static_cast<size_t>(rows) * F * sizeof(float),
                                        cudaMemcpyDeviceToDevice, ctx->stream));
   return GRILLY_OK;
 }
@@ -266,17 +289,20 @@ int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, gri
   if (!ctx || !cfg || !out) return GRILLY_ERR_INVALID_ARG;
   std::lock_guard<std::mutex> lock(ctx->mu);
   *out = nullptr;
-  if (cfg->precision != GRILLY_PREC_TF32) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: only GRILLY_PREC_TF32 is implemented");
+  if (cfg->precision != GRILLY_PREC_TF32 && cfg->precision != GRILLY_PREC_BF16) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: precision must be GRILLY_PREC_TF32 or GRILLY_PREC_BF16");
   if (cfg->num_layers <= 0 || cfg->hidden <= 0 || cfg->num_heads <= 0 || cfg->ffn <= 0 || cfg->vocab <= 0 || cfg->max_pos <= 0)
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sizes must be positive");
   if (cfg->hidden % cfg->num_heads) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: hidden must be divisible by num_heads");
   const int D = cfg->hidden / cfg->num_heads;
   if (D != 32 && D != 64) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: head_dim must be 32 or 64");
+  if (cfg->precision == GRILLY_PREC_BF16 && (cfg->hidden % 8 || cfg->ffn % 8))
+    return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: bf16 mode needs hidden and ffn to be multiples of 8");
   if (cfg->hidden % 4 || cfg->ffn % 4 || cfg->hidden > 1024) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: hidden and ffn must be multiples of 4, hidden at most 1024");
   cudaSetDevice(ctx->device);
   grilly_encoder* e = new grilly_encoder();
   e->ctx = ctx;
   e->cfg = *cfg;
+  e->bf16 = cfg->precision == GRILLY_PREC_BF16;
   e->layers.resize(cfg->num_layers);
   const size_t F = cfg->hidden, ffn = cfg->ffn;
   int rc = 0;
@@ -286,6 +312,10 @@ int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, gri
   for (auto& L : e->layers) {
     A(&L.wqkv, 3 * F * F); A(&L.bqkv, 3 * F); A(&L.wo, F * F); A(&L.bo, F); A(&L.ln1_g, F); A(&L.ln1_b, F);
     A(&L.w1, ffn * F); A(&L.b1, ffn); A(&L.w2, F * ffn); A(&L.b2, F); A(&L.ln2_g, F); A(&L.ln2_b, F);
+    if (e->bf16) {
+      auto Hh = [&](void** p, size_t n) { if (!rc) rc = enc_alloc(e, n * 2, p); };
+      Hh(&L.wqkv_h, 3 * F * F); Hh(&L.wo_h, F * F); Hh(&L.w1_h, ffn * F); Hh(&L.w2_h, F * ffn);
+    }
   }
   if (rc) {
     for (void* p : e->owned) cudaFree(p);
@@ -303,6 +333,7 @@ int grilly_encoder_set_weight(grilly_encoder* e, const char* name, int layer, co
   cudaSetDevice(ctx->device);
   const size_t F = e->cfg.hidden, ffn = e->cfg.ffn;
   float* dst = nullptr;
+  void* dst_h = nullptr;   // bf16 copy of a GEMM weight (bf16 mode)
   size_t expect = 0;
   bool is_gemm_weight = false;
   const std::string n(name);
@@ -314,15 +345,15 @@ int grilly_encoder_set_weight(grilly_encoder* e, const char* name, int layer, co
     else if (n == "emb_ln_b") { dst = e->emb_b; expect = F; }
   } else if (layer < e->cfg.num_layers) {
     EncLayer& L = e->layers[layer];
-    if (n == "wqkv") { dst = L.wqkv; expect = 3 * F * F; is_gemm_weight = true; }
+    if (n == "wqkv") { dst = L.wqkv; dst_h = L.wqkv_h; expect = 3 * F * F; is_gemm_weight = true; }
     else if (n == "bqkv") { dst = L.bqkv; expect = 3 * F; }
-    else if (n == "wo") { dst = L.wo; expect = F * F; is_gemm_weight = true; }
+    else if (n == "wo") { dst = L.wo; dst_h = L.wo_h; expect = F * F; is_gemm_weight = true; }
     else if (n == "bo") { dst = L.bo; expect = F; }
     else if (n == "ln1_g") { dst = L.ln1_g; expect = F; }
     else if (n == "ln1_b") { dst = L.ln1_b; expect = F; }
-    else if (n == "w1") { dst = L.w1; expect = ffn * F; is_gemm_weight = true; }
+    else if (n == "w1") { dst = L.w1; dst_h = L.w1_h; expect = ffn * F; is_gemm_weight = true; }
     else if (n == "b1") { dst = L.b1; expect = ffn; }
-    else if (n == "w2") { dst = L.w2; expect = F * ffn; is_gemm_weight = true; }
+    else if (n == "w2") { dst = L.w2; dst_h = L.w2_h; expect = F * ffn; is_gemm_weight = true; }
     else if (n == "b2") { dst = L.b2; expect = F; }
     else if (n == "ln2_g") { dst = L.ln2_g; expect = F; }
     else if (n == "ln2_b") { dst = L.ln2_b; expect = F; }
@@ -332,7 +363,8 @@ int grilly_encoder_set_weight(grilly_encoder* e, const char* name, int layer, co
   GB_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, data, count * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
   int rc = GRILLY_OK;
   // GEMM weights are consumed as tf32: round them to nearest once here instead of letting the MMA truncate
-  if (is_gemm_weight) rc = launch_round_tf32(ctx, dst, dst, static_cast<long long>(count));
+  if (is_gemm_weight && e->bf16) rc = launch_f32_to_bf16(ctx, dst, dst_h, static_cast<long long>(count));
+  else if (is_gemm_weight) rc = launch_round_tf32(ctx, dst, dst, static_cast<long long>(count));
   GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));  // the host array may be freed by the caller
   return rc;
 }

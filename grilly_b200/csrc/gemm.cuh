@@ -129,7 +129,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
     }
-    if (args.residual) {
+    if (args.residual && args.residual_bf16) {
+      const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(args.residual) + static_cast<long long>(row) * args.ld_res + col0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(rb[j]);
+    } else if (args.residual) {
       const float* rp = args.residual + static_cast<long long>(row) * args.ld_res + col0;
       if (res_vec_ok) {
 #pragma unroll
@@ -203,7 +207,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
     const int col = col0 + j;
     if (col < args.N) {
       float x = apply_act(v[j], args.act);
-      if (args.residual) x += __ldg(args.residual + static_cast<long long>(row) * args.ld_res + col);
+      if (args.residual) x += args.residual_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.residual)[static_cast<long long>(row) * args.ld_res + col]) : __ldg(args.residual + static_cast<long long>(row) * args.ld_res + col);
       if (args.round_tf32) x = round_to_tf32(x);
       const long long idx = static_cast<long long>(row) * args.ld_out + col;
       if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(x);
@@ -264,7 +268,12 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
   }
-  if (args.residual) {
+  if (args.residual && args.residual_bf16) {
+    const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(args.residual) + static_cast<long long>(t0) * args.ld_res + f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || t0 + j < args.M) v[j] += __bfloat162float(rp[static_cast<long long>(j) * args.ld_res]);
+  } else if (args.residual) {
     const float* rp = args.residual + static_cast<long long>(t0) * args.ld_res + f;
     if (full) {
 #pragma unroll

@@ -275,7 +275,14 @@ __global__ void __launch_bounds__(256) embed_ln_kernel(const EmbedArgs a) {
           o.w = (o.w - mean) * rstd * g.w + bt.w;
         }
         if (a.round_tf32) { o.x = round_to_tf32(o.x); o.y = round_to_tf32(o.y); o.z = round_to_tf32(o.z); o.w = round_to_tf32(o.w); }
-        op[idx] = o;
+        if (a.out_bf16) {
+          uint2 pk;
+          pk.x = pack_bf16x2(o.x, o.y);
+          pk.y = pack_bf16x2(o.z, o.w);
+          reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.F)[idx] = pk;
+        } else {
+          op[idx] = o;
+        }
       }
     }
   }

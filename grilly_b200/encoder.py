@@ -53,10 +53,17 @@ class EncoderWeights:
 
 
 class SentenceEncoder:
-    """Post-LN BERT/MiniLM encoder with mean pooling and L2 normalisation, resident on one GPU."""
+    """Post-LN BERT/MiniLM encoder with mean pooling and L2 normalisation, resident on one GPU.
+
+    precision 'tf32': fp32 activations, tf32 tensor-core products (parity tolerance 2e-3).
+    precision 'bf16': bf16 weights and activations between the GEMMs, fp32 accumulation, fp32 LayerNorm inputs and
+    pooling (tolerance 1e-2); with head_dim 32 it handles sequences up to 128 tokens."""
 
     def __init__(self, weights: EncoderWeights, num_heads: int = 12, embed_ln_eps: float = 1e-12,
-                 layer_ln_eps: float = 1e-5, device: Device | int = 0, chunk_tokens: int = 0):
+                 layer_ln_eps: float = 1e-5, device: Device | int = 0, chunk_tokens: int = 0, precision: str = "tf32"):
+        if precision not in ("tf32", "bf16"):
+            raise ValueError("precision must be 'tf32' or 'bf16'")
+        self.precision = precision
         self.dev = device if isinstance(device, Device) else Device(device)
         self._own_dev = not isinstance(device, Device)
         self.lib = self.dev.lib
@@ -66,7 +73,8 @@ class SentenceEncoder:
             num_layers=len(weights.layers), hidden=self.hidden, num_heads=num_heads,
             ffn=int(weights.layers[0]["ffn_w1"].shape[0]), vocab=int(weights.word.shape[0]),
             max_pos=int(weights.pos.shape[0]), embed_ln_eps=embed_ln_eps, layer_ln_eps=layer_ln_eps,
-            has_token_type=int(weights.type is not None), precision=L.PREC_TF32, chunk_tokens=int(chunk_tokens))
+            has_token_type=int(weights.type is not None), precision=L.PREC_BF16 if precision == "bf16" else L.PREC_TF32,
+            chunk_tokens=int(chunk_tokens))
         h = C.c_void_p()
         self.dev.check(self.lib.grilly_encoder_create(self.dev.ctx, C.byref(cfg), C.byref(h)))
         self.handle = h

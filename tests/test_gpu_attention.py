@@ -99,6 +99,17 @@ def test_bf16_decoder_shapes(backend_bf16):
     assert O.rel_l2(backend_bf16.attention.flash_attention2(q, k, v), O.flash_attention2(q, k, v)) < TOL_BF16
 
 
+def test_bf16_head_dim_32_short_sequences(backend_bf16):
+    """head_dim 32 in bf16 is 64 bytes per head: two neighbouring heads share one 128-byte swizzled row."""
+    rng = np.random.default_rng(9)
+    for B, S, H in ((2, 128, 12), (3, 77, 5), (1, 16, 1)):
+        q, k, v = (rng.standard_normal((B, S, H, 32)).astype(np.float32) for _ in range(3))
+        lens = rng.integers(1, S + 1, size=B)
+        mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.float32)
+        o = backend_bf16.attention.flash_attention2(q, k, v, mask=mask)
+        assert O.rel_l2(o, O.flash_attention2(q, k, v, mask=mask)) < TOL_BF16
+
+
 def test_errors(backend):
     z = np.zeros((1, 4, 2, 48), np.float32)
     with pytest.raises(Exception):

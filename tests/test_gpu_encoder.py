@@ -133,6 +133,26 @@ def test_masks_with_holes_run_on_the_padded_layout(small_model):
     assert O.rel_l2(padded[:5], packed[:5]) < 1e-3
 
 
+def test_encoder_bf16_mode(small_model):
+    import grilly_b200
+    from conftest import TOL_BF16
+
+    w, enc = small_model
+    rng = np.random.default_rng(44)
+    ids, lens, mask = make_batch(rng, 40, 128, lo=8)
+    e16 = grilly_b200.SentenceEncoder(w, num_heads=12, device=enc.dev, precision="bf16")
+    try:
+        e16.keep_hidden(True)
+        out = e16.encode_ids(ids, mask)
+        ref, hidden = O.encoder_forward(ids, mask, w.as_dict(), 12, return_hidden=True)
+        assert O.rel_l2(out, ref) < TOL_BF16
+        packed_ref = np.concatenate([hidden[i, : lens[i]] for i in range(40)], 0)
+        assert O.rel_l2(e16.last_hidden(), packed_ref) < TOL_BF16
+        assert O.rel_l2(out, enc.encode_ids(ids, mask)) < TOL_BF16
+    finally:
+        e16.close()
+
+
 def test_encoder_rejects_bad_input(small_model):
     _, enc = small_model
     with pytest.raises(ValueError):
