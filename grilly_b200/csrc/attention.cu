@@ -61,6 +61,7 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
   // one CTA per sequence walking all heads, split into head groups only while the grid is too small to fill the GPU
   int hpc = args.H;
   while (hpc > 1 && static_cast<long long>(args.B) * ((args.H + hpc - 1) / hpc) < 4LL * ctx->num_sms) hpc = (hpc + 1) / 2;
+  if (const char* env = getenv("GRILLY_ATTN_HPC")) hpc = atoi(env) > 0 ? atoi(env) : hpc;  // heads per CTA, for tuning runs
   hpc = (hpc + Cfg::HPR - 1) / Cfg::HPR * Cfg::HPR;   // heads that share a loaded row chunk stay in one CTA
   dim3 grid(args.B, (args.H + hpc - 1) / hpc, 1);
   double flops = ctx->attn_flops_hint >= 0.0 ? ctx->attn_flops_hint : 4.0 * args.B * args.H * static_cast<double>(args.S) * args.S * D;

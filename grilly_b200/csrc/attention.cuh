@@ -41,6 +41,9 @@ struct AttnCfg {
   static constexpr int TMEM_COLS = 256;
 };
 
+// low n bits set (n <= 0 -> none, n >= 32 -> all)
+__device__ __forceinline__ uint32_t prefix_bits(int n) { return n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u)); }
+
 // Reductions over 32 registers with four independent chains (a single chain of 32 dependent ops is latency-bound).
 __device__ __forceinline__ float row_max32(const uint32_t (&r)[32]) {
   float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
@@ -237,7 +240,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       for (int j = 0; j < n_kv && ok; ++j) {
         const uint32_t ph = j & 1;
         const int kv_len = min(ATTN_TILE, L - j * ATTN_TILE);           // valid keys of this step
-        const int n_s = (kv_len + 15) & ~15;                             // score columns actually computed
+        const int n_s = (kv_len + 31) & ~31;                             // score columns computed (multiples of 32: N = 16 mod 32 is slow)
         const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
         if (!mbar_wait(rope ? bar_rk : bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
         tc_fence_after();
@@ -324,21 +327,30 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const float sl2 = args.scale * kLog2e;
         // ---- pass 1: row maximum
         float m_tile = -INFINITY;
+        // bit i of validw: key kc + i exists; of the returned word: it also passes the key mask and the causal rule
+        // (warp-wide call: the key mask word comes from one load per lane and a ballot)
+        auto keep_word = [&](int kc, uint32_t validw) {
+          uint32_t w = validw;
+          if (args.causal) w &= prefix_bits(qi - kc + 1);
+          if (kmask) w &= __ballot_sync(0xffffffffu, kc + lane < L && __ldg(kmask + kc + lane) >= 0.5f);
+          return w;
+        };
 #pragma unroll 1
         for (int c = 0; c < nchunks; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
           tmem_ld_wait();
           if (tile_mask) {
+            // masked keys score -1e9 (what the reference adds), absent ones -inf
+            const int kc = k0 + c * 32;
+            const uint32_t validw = prefix_bits(L - kc);
+            const uint32_t keepw = keep_word(kc, validw);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int kidx = k0 + c * 32 + i;
-              float s = __uint_as_float(r[i]) * args.scale;
-              if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
-              if (args.causal && kidx > qi) s = -1e9f;
-              if (kidx >= L) s = -INFINITY;
-              m_tile = fmaxf(m_tile, s);
+              const float s = __uint_as_float(r[i]) * args.scale;
+              r[i] = __float_as_uint(((keepw >> i) & 1u) ? s : (((validw >> i) & 1u) ? -1e9f : -INFINITY));
             }
+            m_tile = fmaxf(m_tile, row_max32(r));
           } else {
             m_tile = fmaxf(m_tile, row_max32(r) * args.scale);
           }
@@ -356,14 +368,13 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           tmem_ld_wait();
           float p[32];
           if (tile_mask) {
+            const uint32_t validw = prefix_bits(L - (k0 + c * 32));
+            const uint32_t keepw = keep_word(k0 + c * 32, validw);
+            const float x_masked = -1e9f * kLog2e - m_l2;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int kidx = k0 + c * 32 + i;
-              float s = __uint_as_float(r[i]) * args.scale;
-              if (kmask && kidx < L && __ldg(kmask + kidx) < 0.5f) s = -1e9f;
-              if (args.causal && kidx > qi) s = -1e9f;
-              if (kidx >= L) s = -INFINITY;
-              p[i] = fast_exp2(s * kLog2e - m_l2);
+              const float x = fmaf(__uint_as_float(r[i]), sl2, -m_l2);
+              p[i] = fast_exp2(((keepw >> i) & 1u) ? x : (((validw >> i) & 1u) ? x_masked : -INFINITY));
             }
           } else {
 #pragma unroll
@@ -507,6 +518,7 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   uint64_t* bar_o = bars + 4;      // O complete
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  uint32_t* s_keep = reinterpret_cast<uint32_t*>(tmem_holder + 2);   // [4] key-mask bit words of this sentence
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -529,7 +541,7 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + ATTN_TILE;
 
-  const int n_s = (L + 15) & ~15;                      // score columns computed
+  const int n_s = (L + 31) & ~31;                      // score columns computed (N = 16 mod 32 runs the MMA much slower)
   const int nchunks = (L + 31) >> 5;                   // 32-key chunks with a valid key
   const int ksteps = (L + UMMA_K - 1) / UMMA_K;        // k-steps of P V that cover valid keys
 
@@ -591,6 +603,16 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float sl2 = args.scale * 1.4426950408889634f;   // scores enter exp2 as s * scale * log2(e)
     const float* kmask = args.key_mask ? args.key_mask + static_cast<long long>(b) * args.S : nullptr;
+    if (kmask && t < 4) {
+      // the key mask is the same for every head and query of the sentence: 4 bit words, built once
+      uint32_t w = 0;
+      for (int j = 0; j < 32; ++j) {
+        const int kidx = t * 32 + j;
+        if (kidx < L && __ldg(kmask + kidx) >= 0.5f) w |= 1u << j;
+      }
+      s_keep[t] = w;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // softmax warps only (warp 4 is busy issuing)
     int i = 0;
     for (int h = h_begin; h < h_end; ++h, ++i) {
       const uint32_t ph = i & 1;
@@ -598,7 +620,8 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       tc_fence_after();
       float l_sum = 0.f;
       if (warp_active) {
-        // pass 1: row maximum (scale > 0 is folded in afterwards; masked keys count as -1e9 after scaling)
+        // pass 1: row maximum (scale > 0 is folded in afterwards). Per 32-key chunk two bit words say which columns
+        // exist (validw: key < L) and which also pass the key mask (keepw); a full, unmasked chunk takes the plain path.
         float m_raw = -INFINITY;
         bool any_masked = false;
 #pragma unroll 1
@@ -606,24 +629,21 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           uint32_t r[32];
           tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
           tmem_ld_wait();
-          const int kbase = c * 32;
-          if (kmask || kbase + 32 > L) {
+          const uint32_t validw = prefix_bits(L - c * 32);
+          const uint32_t keepw = kmask ? s_keep[c] : validw;
+          if (keepw != 0xffffffffu) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int kidx = kbase + j;
-              float s = __uint_as_float(r[j]);
-              if (kidx >= L) s = -INFINITY;
-              else if (kmask && __ldg(kmask + kidx) < 0.5f) { s = -INFINITY; any_masked = true; }
-              m_raw = fmaxf(m_raw, s);
-            }
-          } else {
-            m_raw = fmaxf(m_raw, row_max32(r));
+            for (int j = 0; j < 32; ++j)
+              if (!((keepw >> j) & 1u)) r[j] = 0xff800000u;   // -inf: absent or masked keys do not set the maximum
+            any_masked = any_masked || (validw & ~keepw) != 0u;
           }
+          m_raw = fmaxf(m_raw, row_max32(r));
         }
         // masked keys carry the score -1e9 (the reference adds (mask-1)*1e9): they only matter when every key is masked
         float m_sc = m_raw * args.scale;
         if (any_masked) m_sc = fmaxf(m_sc, -1e9f);
         const float m_l2 = m_sc * 1.4426950408889634f;
+        const float x_masked = -1e9f * 1.4426950408889634f - m_l2;
         // pass 2: p = exp(s - m), row sum, P written over S
 #pragma unroll 1
         for (int c = 0; c < nchunks; ++c) {
@@ -631,14 +651,13 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
           tmem_ld_wait();
           float p[32];
-          const int kbase = c * 32;
-          if (kmask || kbase + 32 > L) {
+          const uint32_t validw = prefix_bits(L - c * 32);
+          const uint32_t keepw = kmask ? s_keep[c] : validw;
+          if (keepw != 0xffffffffu) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int kidx = kbase + j;
               float x = fmaf(__uint_as_float(r[j]), sl2, -m_l2);
-              if (kidx >= L) x = -INFINITY;
-              else if (kmask && __ldg(kmask + kidx) < 0.5f) x = -1e9f * 1.4426950408889634f - m_l2;
+              x = ((keepw >> j) & 1u) ? x : (((validw >> j) & 1u) ? x_masked : -INFINITY);
               p[j] = fast_exp2(x);
             }
           } else {
