@@ -52,9 +52,9 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, 
     default library; load it by pointing the GRILLY_B200_LIB environment variable at it."""
     global BUILD, LIB
     if suffix:
-        BUILD = PKG / ("_build" + suffix)
+        BUILD = PKG / "_build" / ("variant" + suffix)
         LIB = PKG / "lib" / f"libgrilly_b200{suffix}.so"
-    BUILD.mkdir(exist_ok=True)
+    BUILD.mkdir(parents=True, exist_ok=True)
     LIB.parent.mkdir(exist_ok=True)
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.glob("*.h"))
     stamp = BUILD / "stamp"

@@ -1,6 +1,7 @@
 // Host launcher for the tcgen05 GEMM: picks the N tile, builds (or reuses) the
 // TMA descriptors and launches one persistent CTA per SM.
 #include "gemm.cuh"
+#include "gemm_pair.cuh"
 #include "internal.h"
 #include <cstdlib>
 
@@ -56,6 +57,68 @@ static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& a
   return GRILLY_OK;
 }
 
+// CTA-pair variant (gemm_pair.cuh): weights [N][K] and tokens [M][K], both K-major; tiles of 256 features x 256 tokens.
+template <bool kBf16>
+static int launch_pair(grilly_ctx* ctx, const void* x, const void* w, GemmArgs& args) {
+  using Cfg = GemmPairCfg;
+  constexpr int ELT = kBf16 ? 2 : 4;
+  constexpr int BK = 128 / ELT;
+  const int dtype = kBf16 ? TM_BF16 : TM_F32;
+  CUtensorMap tw, tx;
+  int rc;
+  if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tw))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, x, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tx))) return rc;
+  args.num_m_tiles = (args.N + Cfg::TILE - 1) / Cfg::TILE;
+  args.num_n_tiles = (args.M + Cfg::TILE - 1) / Cfg::TILE;
+  args.num_k_blocks = (args.K + BK - 1) / BK;
+  args.err = ctx->err_dev;
+  auto kern = gemm_tcgen05_pair_kernel<kBf16>;
+  const void* key = reinterpret_cast<const void*>(kern);
+  if (!ctx->smem_attr_done.count(key)) {
+    GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    ctx->smem_attr_done.insert(key);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = ctx->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  auto found = ctx->max_clusters.find(key);
+  if (found == ctx->max_clusters.end()) {
+    int n = 0;
+    cfg.gridDim = dim3(2 * (ctx->num_sms / 2), 1, 1);
+    GB_CUDA_CHECK(ctx, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    if (n <= 0) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "gemm: no CTA pair fits on this GPU");
+    found = ctx->max_clusters.emplace(key, n).first;
+  }
+  const int tiles = args.num_m_tiles * args.num_n_tiles;
+  const int pairs = tiles < found->second ? tiles : found->second;
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  const double out_cols = args.swiglu_pairs ? args.N / 2.0 : args.N;
+  const double bytes = static_cast<double>(ELT) * (static_cast<double>(args.M) * args.K + static_cast<double>(args.N) * args.K) +
+                       (args.bias ? 4.0 * args.N : 0.0) + static_cast<double>(args.M) * out_cols * (args.out_bf16 ? 2.0 : 4.0) +
+                       (args.residual ? 4.0 * args.M * out_cols : 0.0);
+  const int pi = prof_begin(ctx, PROF_GEMM, 2.0 * args.M * static_cast<double>(args.N) * args.K, bytes);
+  GB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, kern, tw, tx, args));
+  prof_end(ctx, pi);
+  ctx->launches++;
+  return GRILLY_OK;
+}
+
+// A pair tile covers 256 features: worth it when the GEMM is large enough to be bound by operand traffic and the
+// last feature block is not mostly padding (384 features would waste a quarter of the MMAs).
+static bool pick_pair(int M, int N, bool b_mn_major) {
+  if (b_mn_major || M < 1024 || N < 256) return false;
+  const int padded = (N + 255) / 256 * 256;
+  return padded * 8 <= N * 9;
+}
+
 // One tcgen05.mma takes about the same time for any N up to 256, so a tile costs the same whatever its width:
 // take the widest tile that is not mostly padding. The swapped orientation (weights as the 128-row operand,
 // tokens as the MMA's N) is used for `linear` whenever the output is wide enough to fill 128 feature rows.
@@ -90,12 +153,15 @@ int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, cons
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: operands must be 16-byte aligned");
   if (args.swiglu_pairs && (args.N & 1)) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: SwiGLU pairs need an even N");
-  bool swap = pick_swap(args.N, b_mn_major);
-  if (const char* env = getenv("GRILLY_GEMM_SWAP")) swap = !b_mn_major && atoi(env) != 0;  // tuning/debug override
   if (force_bn <= 0) {
-    // tuning/debug override of the tile width (64, 128, 192 or 256)
+    // tuning/debug override of the tile width (64, 128, 192 or 256); a forced width also rules out the pair kernel
     if (const char* env = getenv("GRILLY_GEMM_BN")) force_bn = atoi(env);
   }
+  bool pair = pick_pair(args.M, args.N, b_mn_major);
+  if (const char* env = getenv("GRILLY_GEMM_PAIR")) pair = !b_mn_major && atoi(env) != 0;  // tuning/debug override
+  if (pair && force_bn <= 0) return bf16 ? launch_pair<true>(ctx, a, b, args) : launch_pair<false>(ctx, a, b, args);
+  bool swap = pick_swap(args.N, b_mn_major);
+  if (const char* env = getenv("GRILLY_GEMM_SWAP")) swap = !b_mn_major && atoi(env) != 0;  // tuning/debug override
   const int bn = force_bn > 0 ? force_bn : pick_bn(swap ? args.M : args.N);
   if (bf16) {
     if (b_mn_major) return dispatch_bn<true, true, false>(ctx, bn, a, b, args);

@@ -53,6 +53,7 @@ struct grilly_ctx {
   uint64_t tmap_hits = 0, tmap_misses = 0;
   uint64_t launches = 0;
   std::unordered_set<const void*> smem_attr_done;  // kernels whose dynamic-smem limit is already raised
+  std::unordered_map<const void*, int> max_clusters;  // CTA-pair kernels: co-resident clusters of 2 on this GPU
   // optional per-kernel-class timing (CUDA events on the launching stream), see grilly_profile_begin/end
   struct ProfRec { int cls; cudaEvent_t a, b; double flops, bytes; };
   cudaEvent_t timer_a = nullptr, timer_b = nullptr;  // grilly_timer_start / grilly_timer_stop

@@ -65,6 +65,24 @@ def test_every_n_tile(backend, bn, monkeypatch):
     assert O.rel_l2(backend.fnn.fused_linear_relu(x, w), O.fused_linear_relu(x, w)) < TOL_TF32
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 520, 40), (1000, 384, 96), (2049, 1536, 384), (256, 256, 8)])
+def test_cta_pair_kernel(backend, backend_bf16, M, N, K, monkeypatch):
+    """The cta_group::2 kernel (two CTAs share one MMA, 256 x 256 tiles) on ragged shapes it would not be picked
+    for by default: partial token tiles, a feature count that leaves the second CTA of a pair without rows."""
+    monkeypatch.setenv("GRILLY_GEMM_PAIR", "1")
+    rng = np.random.default_rng(M + N + K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    assert O.rel_l2(backend.fnn.linear(x, w, b), O.linear(x, w, b)) < TOL_TF32
+    assert O.rel_l2(backend.fnn.fused_linear_gelu(x, w, b), O.fused_linear_gelu(x, w, b)) < TOL_TF32
+    assert O.rel_l2(backend_bf16.fnn.fused_linear_silu(x, w), O.fused_linear_silu(x, w)) < TOL_BF16
+    # the same launch through the single-CTA kernel gives the same numbers bit for bit (same MMA order per output)
+    y_pair = backend.fnn.linear(x, w, b)
+    monkeypatch.setenv("GRILLY_GEMM_PAIR", "0")
+    assert np.array_equal(y_pair, backend.fnn.linear(x, w, b))
+
+
 def test_linear_is_deterministic_and_weight_cache_is_used(backend):
     rng = np.random.default_rng(5)
     x = rng.standard_normal((256, 384)).astype(np.float32)
