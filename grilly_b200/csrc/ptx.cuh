@@ -246,7 +246,7 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // 2-D tiled load into THIS CTA's shared memory whose bytes are counted on a barrier that may live in the pair's
-// other CTA (`bar_cluster_addr` from map_to_cta). No multicast: each CTA fetches its own halves.
+// other CTA (`bar_cluster_addr` from map_to_cta). Every CTA fetches its own halves; nothing is broadcast.
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
