@@ -107,8 +107,8 @@ int grilly_init(int device, grilly_ctx** out) {
     uint64_t thresh = UINT64_MAX;
     ok = cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &thresh) == cudaSuccess;
   }
-  ok = ok && cudaMalloc(&ctx->err_dev, sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMemset(ctx->err_dev, 0, sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&ctx->err_dev, 2 * sizeof(int)) == cudaSuccess;  // [0] status word, [1] attention work counter
+  ok = ok && cudaMemset(ctx->err_dev, 0, 2 * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMallocHost(&ctx->err_host, sizeof(int)) == cudaSuccess;
   if (!ok) {
     cudaGetLastError();

@@ -1,5 +1,7 @@
 // Host launcher for the tcgen05 flash-attention kernel.
+#include <algorithm>
 #include "attention.cuh"
+#include "attention_short.cuh"
 #include "internal.h"
 #include <cstdlib>
 
@@ -58,17 +60,23 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
     GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     ctx->smem_attr_done.insert(reinterpret_cast<const void*>(kern));
   }
-  // one CTA per sequence walking all heads, split into head groups only while the grid is too small to fill the GPU
+  // a unit is one sequence with all its heads, split into head groups while there are fewer than about six units per
+  // slot (sequences differ in length, so a slot's last unit decides how long the tail of the launch is)
   int hpc = args.H;
-  while (hpc > 1 && static_cast<long long>(args.B) * ((args.H + hpc - 1) / hpc) < 4LL * ctx->num_sms) hpc = (hpc + 1) / 2;
-  if (const char* env = getenv("GRILLY_ATTN_HPC")) hpc = atoi(env) > 0 ? atoi(env) : hpc;  // heads per CTA, for tuning runs
-  hpc = (hpc + Cfg::HPR - 1) / Cfg::HPR * Cfg::HPR;   // heads that share a loaded row chunk stay in one CTA
-  dim3 grid(args.B, (args.H + hpc - 1) / hpc, 1);
+  while (hpc > 1 && static_cast<long long>(args.B) * ((args.H + hpc - 1) / hpc) < 6LL * Cfg::NSLOT * ctx->num_sms) hpc = (hpc + 1) / 2;
+  if (const char* env = getenv("GRILLY_ATTN_HPC")) hpc = atoi(env) > 0 ? atoi(env) : hpc;  // heads per unit, for tuning runs
+  hpc = (hpc + Cfg::HPR - 1) / Cfg::HPR * Cfg::HPR;   // heads that share a loaded row chunk stay in one unit
+  const int head_groups = (args.H + hpc - 1) / hpc;
+  const long long units = static_cast<long long>(args.B) * head_groups;
+  if (units > 2147483647LL) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: too many (sequence, head group) units");
+  const int ctas = static_cast<int>(std::min<long long>(ctx->num_sms, (units + Cfg::NSLOT - 1) / Cfg::NSLOT));
   double flops = ctx->attn_flops_hint >= 0.0 ? ctx->attn_flops_hint : 4.0 * args.B * args.H * static_cast<double>(args.S) * args.S * D;
   ctx->attn_flops_hint = -1.0;
   const double bytes = static_cast<double>(total_rows) * args.H * D * (3.0 * ELT + (args.out_bf16 ? 2.0 : 4.0));
+  int* counter = ctx->err_dev + 1;                     // the slots of all CTAs take their units from this counter
+  GB_CUDA_CHECK(ctx, cudaMemsetAsync(counter, 0, sizeof(int), ctx->stream));
   const int pi = prof_begin(ctx, PROF_ATTN, flops, bytes);
-  kern<<<grid, ATTN_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tq, tk, tv, args, hpc);
+  kern<<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tq, tk, tv, args, hpc, head_groups, static_cast<int>(units), counter);
   prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());

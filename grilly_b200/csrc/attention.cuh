@@ -459,281 +459,3 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 }
 
 }  // namespace gb
-
-// ---------------------------------------------------------------------------------------------------------
-// Short-sequence variant (every sequence fits one 128-key tile, no RoPE, no causal mask): the MiniLM encoder
-// case. One CTA owns one sequence and walks a range of its heads, so TMEM allocation, barrier set-up and the
-// tensor-map fetch are paid once per sequence instead of once per (sequence, head); Q/K/V of the next head are
-// in flight (double-buffered shared memory) while the current head is in its softmax. With a single key tile
-// there is no running-max rescale: row max, exp, row sum, P V, divide.
-namespace gb {
-
-template <int D, bool kBf16>
-struct AttnShortCfg {
-  static constexpr int ELT = kBf16 ? 2 : 4;
-  static constexpr int ROW_BYTES = D * ELT;                       // bytes of one head in a token row
-  static_assert(ROW_BYTES == 64 || ROW_BYTES == 128 || ROW_BYTES == 256, "head_dim*elt must be 64, 128 or 256 bytes");
-  // A 64-byte head (head_dim 32 in bf16) is loaded together with its neighbour: the 128-byte swizzled row then
-  // holds two heads side by side and each head's MMAs start 0 or 64 bytes into the row.
-  static constexpr int HPR = ROW_BYTES < 128 ? 128 / ROW_BYTES : 1;   // heads per loaded row chunk
-  static constexpr int NCH = ROW_BYTES <= 128 ? 1 : ROW_BYTES / 128;
-  static constexpr int HEAD_BYTES = 3 * NCH * ATTN_CHUNK_BYTES;   // Q, K, V tiles of one head (or head pair)
-  static constexpr int SMEM_BYTES = 2 * HEAD_BYTES + 1024 + 128;
-  static constexpr int TMEM_COLS = 256;                           // S/P at [0,128), O at [128,128+D)
-};
-
-template <int D, bool kBf16>
-__global__ void __launch_bounds__(ATTN_THREADS)
-flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                        const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args, int heads_per_cta) {
-  using Cfg = AttnShortCfg<D, kBf16>;
-  constexpr int ELT = Cfg::ELT;
-  constexpr int NCH = Cfg::NCH;
-  constexpr int HPR = Cfg::HPR;
-  constexpr int CHE = 128 / ELT;
-  constexpr int UMMA_K = 32 / ELT;
-  constexpr int TILE_BYTES = NCH * ATTN_CHUNK_BYTES;
-  constexpr uint32_t IDESC_S = make_idesc(kBf16, 128, ATTN_TILE, false, false);
-  constexpr uint32_t IDESC_O = make_idesc(kBf16, 128, D, false, true);
-
-  const int b = blockIdx.x;
-  const int h_begin = blockIdx.y * heads_per_cta;
-  const int h_end = min(args.H, h_begin + heads_per_cta);
-  int row0, L;
-  if (args.cu_seqlens) {
-    row0 = args.cu_seqlens[b];
-    L = args.cu_seqlens[b + 1] - row0;
-  } else {
-    row0 = b * args.S;
-    L = args.S;
-  }
-  if (L <= 0 || h_begin >= h_end) return;   // uniform for the CTA; nothing allocated yet
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * Cfg::HEAD_BYTES);
-  uint64_t* bar_load = bars + 0;   // [2] Q, K, V of a head landed in buffer 0 / 1
-  uint64_t* bar_s = bars + 2;      // S complete
-  uint64_t* bar_p = bars + 3;      // P written (one arrive per softmax warp)
-  uint64_t* bar_o = bars + 4;      // O complete
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 5);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  uint32_t* s_keep = reinterpret_cast<uint32_t*>(tmem_holder + 2);   // [4] key-mask bit words of this sentence
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    mbar_init(&bar_load[0], 1); mbar_init(&bar_load[1], 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
-    *abort_flag = 0;
-    fence_mbar_init();
-    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
-  }
-  if (warp == 4) {
-    tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + ATTN_TILE;
-
-  const int n_s = (L + 31) & ~31;                      // score columns computed (N = 16 mod 32 runs the MMA much slower)
-  const int nchunks = (L + 31) >> 5;                   // 32-key chunks with a valid key
-  const int ksteps = (L + UMMA_K - 1) / UMMA_K;        // k-steps of P V that cover valid keys
-
-#define ATTN_FAIL()                                         \
-  do {                                                      \
-    if (!*abort_flag) atomicCAS(args.err, 0, ERR_WAIT_ATTN); \
-    *abort_flag = 1;                                        \
-  } while (0)
-
-  if (warp == 4) {
-    if (lane == 0) {
-      // -------------------------------------------------------- TMA + MMA issuer
-      const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
-      // one load brings the Q, K, V tiles of HPR neighbouring heads (h_begin is a multiple of HPR)
-      auto load_group = [&](int h, int buf) {
-        uint8_t* base = smem + buf * Cfg::HEAD_BYTES;
-        mbar_expect_tx(&bar_load[buf], Cfg::HEAD_BYTES);
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          tma_load_2d(base + c * ATTN_CHUNK_BYTES, &tmap_q, &bar_load[buf], h * D + c * CHE, row0);
-          tma_load_2d(base + TILE_BYTES + c * ATTN_CHUNK_BYTES, &tmap_k, &bar_load[buf], h * D + c * CHE, row0);
-          tma_load_2d(base + 2 * TILE_BYTES + c * ATTN_CHUNK_BYTES, &tmap_v, &bar_load[buf], h * D + c * CHE, row0);
-        }
-      };
-      load_group(h_begin, 0);
-      int i = 0, gi = -1, buf = 0;
-      for (int h = h_begin; h < h_end; ++h, ++i) {
-        const uint32_t ph = i & 1;
-        const int u = (h - h_begin) % HPR;            // position of this head inside its loaded group
-        if (u == 0) {
-          ++gi;
-          buf = gi & 1;
-          // the other buffer was last read by the P V MMA of the previous head, whose completion was awaited below
-          if (h + HPR < h_end) load_group(h + HPR, buf ^ 1);
-          if (!mbar_wait(&bar_load[buf], (gi >> 1) & 1, abort_flag)) { ATTN_FAIL(); break; }
-        }
-        tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + buf * Cfg::HEAD_BYTES) + u * Cfg::ROW_BYTES, sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < D / UMMA_K; ++ks) {
-          const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
-          umma_ss<kBf16>(tmem_s, make_smem_desc_sw128(sQ + chunk * ATTN_CHUNK_BYTES + off, 16, 1024),
-                         make_smem_desc_sw128(sK + chunk * ATTN_CHUNK_BYTES + off, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
-        }
-        umma_commit(bar_s);
-        if (!mbar_wait(bar_p, ph, abort_flag)) { ATTN_FAIL(); break; }
-        tc_fence_after();
-        for (int ks = 0; ks < ksteps; ++ks)
-          umma_ts<kBf16>(tmem_o, tmem_s + ks * 8, make_smem_desc_mn<kBf16>(sV + ks * (UMMA_K * 128), ATTN_CHUNK_BYTES), IDESC_O,
-                         ks != 0 ? 1u : 0u);
-        umma_commit(bar_o);
-        if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
-      }
-    }
-  } else {
-    // ---------------------------------------------------------- softmax / output threads (one query row each)
-    const int t = threadIdx.x;
-    const bool warp_active = warp * 32 < L;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    const float sl2 = args.scale * 1.4426950408889634f;   // scores enter exp2 as s * scale * log2(e)
-    const float* kmask = args.key_mask ? args.key_mask + static_cast<long long>(b) * args.S : nullptr;
-    if (kmask && t < 4) {
-      // the key mask is the same for every head and query of the sentence: 4 bit words, built once
-      uint32_t w = 0;
-      for (int j = 0; j < 32; ++j) {
-        const int kidx = t * 32 + j;
-        if (kidx < L && __ldg(kmask + kidx) >= 0.5f) w |= 1u << j;
-      }
-      s_keep[t] = w;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // softmax warps only (warp 4 is busy issuing)
-    int i = 0;
-    for (int h = h_begin; h < h_end; ++h, ++i) {
-      const uint32_t ph = i & 1;
-      if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
-      tc_fence_after();
-      float l_sum = 0.f;
-      if (warp_active) {
-        // pass 1: row maximum (scale > 0 is folded in afterwards). Per 32-key chunk two bit words say which columns
-        // exist (validw: key < L) and which also pass the key mask (keepw); a full, unmasked chunk takes the plain path.
-        float m_raw = -INFINITY;
-        bool any_masked = false;
-#pragma unroll 1
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          const uint32_t validw = prefix_bits(L - c * 32);
-          const uint32_t keepw = kmask ? s_keep[c] : validw;
-          if (keepw != 0xffffffffu) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (!((keepw >> j) & 1u)) r[j] = 0xff800000u;   // -inf: absent or masked keys do not set the maximum
-            any_masked = any_masked || (validw & ~keepw) != 0u;
-          }
-          m_raw = fmaxf(m_raw, row_max32(r));
-        }
-        // masked keys carry the score -1e9 (the reference adds (mask-1)*1e9): they only matter when every key is masked
-        float m_sc = m_raw * args.scale;
-        if (any_masked) m_sc = fmaxf(m_sc, -1e9f);
-        const float m_l2 = m_sc * 1.4426950408889634f;
-        const float x_masked = -1e9f * 1.4426950408889634f - m_l2;
-        // pass 2: p = exp(s - m), row sum, P written over S
-#pragma unroll 1
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          float p[32];
-          const uint32_t validw = prefix_bits(L - c * 32);
-          const uint32_t keepw = kmask ? s_keep[c] : validw;
-          if (keepw != 0xffffffffu) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = fmaf(__uint_as_float(r[j]), sl2, -m_l2);
-              x = ((keepw >> j) & 1u) ? x : (((validw >> j) & 1u) ? x_masked : -INFINITY);
-              p[j] = fast_exp2(x);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) p[j] = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_l2));
-          }
-          if constexpr (kBf16) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(p[2 * j], p[2 * j + 1]);
-            l_sum += row_sum32(p);
-            tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
-          } else {
-            uint32_t pk[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              p[j] = round_to_tf32(p[j]);
-              pk[j] = __float_as_uint(p[j]);
-            }
-            l_sum += row_sum32(p);
-            tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
-          }
-        }
-        tmem_st_wait();
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p);
-
-      if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
-      tc_fence_after();
-      if (warp_active) {
-        const float inv = 1.f / l_sum;
-        const long long orow = static_cast<long long>(row0 + t) * args.ld_out + h * D;
-        const bool row_ok = t < L;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          if (row_ok) {
-            if (args.out_bf16) {
-              __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + orow + c * 32;
-#pragma unroll
-              for (int j = 0; j < 32; j += 2)
-                *reinterpret_cast<uint32_t*>(op + j) = pack_bf16x2(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
-            } else {
-              float* op = reinterpret_cast<float*>(args.out) + orow + c * 32;
-              const bool v4 = (args.ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 q = make_float4(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv,
-                                       __uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
-                if (args.round_tf32) {
-                  q.x = round_to_tf32(q.x); q.y = round_to_tf32(q.y); q.z = round_to_tf32(q.z); q.w = round_to_tf32(q.w);
-                }
-                if (v4) *reinterpret_cast<float4*>(op + j) = q;
-                else { op[j] = q.x; op[j + 1] = q.y; op[j + 2] = q.z; op[j + 3] = q.w; }
-              }
-            }
-          }
-          __syncwarp();
-        }
-      }
-      tc_fence_before();   // O and P of this head are consumed before the next head's MMAs may overwrite them
-    }
-  }
-#undef ATTN_FAIL
-
-  if (*abort_flag) {
-    for (int k = 0; k < 100; ++k) __nanosleep(10000);
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (warp == 4) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-}
-
-}  // namespace gb
