@@ -32,7 +32,7 @@ sys.path.insert(0, str(ROOT))
 
 CFG = dict(num_layers=6, hidden=384, heads=12, ffn=1536, vocab=30522, max_pos=512, batch=1024, seq=128)
 WORKLOAD = "minilm_l6_h384_encoder_forward_b1024_s128_per_gpu"
-NCU_GEMM_TRAFFIC_RATIO = 84.5 / 143.9  # dram bytes (read + write) per algorithmic byte, from the ncu capture
+NCU_GEMM_TRAFFIC_RATIO = 405.7 / 461.9  # dram bytes (read + write) per algorithmic byte, from the full-size ncu capture
 
 
 def make_batch(rank: int):
@@ -277,9 +277,10 @@ def main():
         ms_per_step = total_ms / args.steps
         value = world * B / (ms_per_step * 1e-3)
         e2e_value = world * B / (total_e2e_ms / args.steps * 1e-3)
-        # DRAM traffic per launch: the ncu capture of this kernel on the FFN1 shape at 18 432 rows
-        # (profiles/gemm_tcgen05_linear_gelu_18432x1536x384.md) moved 84.5 MB for 143.9 MB of algorithmic bytes;
-        # that ratio is scaled by the algorithmic bytes of this run's average launch
+        # DRAM traffic per launch: the ncu capture of the pair kernel on this run's QKV launch (74 884 x 1152 x 384,
+        # profiles/gemm_tcgen05_encoder_shapes_knockout.md) moved 116.9 + 288.8 MB for 461.9 MB of algorithmic
+        # bytes (the tail of the output is still in L2 when the kernel ends); that ratio is scaled by the
+        # algorithmic bytes of this run's average GEMM launch
         traffic = NCU_GEMM_TRAFFIC_RATIO * g["bytes"] / max(g["launches"], 1) if g["launches"] else None
         line = {
             "metric": "encoder_sentences_per_sec", "value": value, "unit": "sentences/s", "n_gpus": world,
@@ -293,7 +294,7 @@ def main():
                     "d2h_bytes_per_step": int(out_host.nbytes)},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all encoder GEMMs)", "achieved": gemm_tflops,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel + gemm_tcgen05_kernel (all encoder GEMMs)", "achieved": gemm_tflops,
                          "peak": peak_tf32, "unit": "TFLOP/s", "frac": (gemm_tflops / peak_tf32) if gemm_tflops else None,
                          "traffic": traffic, "peak_basis": peak_note,
                          "launches": g["launches"], "avg_launch_ms": g["ms"] / max(g["launches"], 1),

@@ -11,6 +11,7 @@ enum : int { ELT_GELU = 1, ELT_SILU = 2, ELT_RELU = 3, ELT_ADD = 4, ELT_SWIGLU =
 struct GemmArgs {
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_k_blocks;
+  int tile_group;         // fast-dimension blocks per group of the tile order (see tile_coords)
   const float* bias;      // [N] (pre-activation) or null
   const float* residual;  // [M][ld_res] fp32, added after the activation, or null
   long long ld_res;

@@ -7,6 +7,12 @@
 
 namespace gb {
 
+static int env_int(const char* name, int fallback) {   // tuning override, must be positive
+  const char* v = getenv(name);
+  const int x = v ? atoi(v) : 0;
+  return x > 0 ? x : fallback;
+}
+
 template <int BN, bool kBf16, bool kBMn, bool kSwap>
 static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& args) {
   using Cfg = GemmCfg<BN>;
@@ -37,6 +43,9 @@ static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& a
     args.num_n_tiles = (args.N + BN - 1) / BN;
   }
   args.num_k_blocks = (args.K + BK - 1) / BK;
+  // co-running tiles (one per SM) load group*fast_rows + (SMs/group)*slow_rows operand rows per k-block: smallest
+  // near group = sqrt(SMs * slow_rows / fast_rows)
+  args.tile_group = env_int("GRILLY_GEMM_GROUP", kSwap ? 16 : 8);
   args.err = ctx->err_dev;
   auto kern = gemm_tcgen05_kernel<BN, kBf16, kBMn, kSwap>;
   if (!ctx->smem_attr_done.count(reinterpret_cast<const void*>(kern))) {
@@ -71,6 +80,7 @@ static int launch_pair(grilly_ctx* ctx, const void* x, const void* w, GemmArgs& 
   args.num_m_tiles = (args.N + Cfg::TILE - 1) / Cfg::TILE;
   args.num_n_tiles = (args.M + Cfg::TILE - 1) / Cfg::TILE;
   args.num_k_blocks = (args.K + BK - 1) / BK;
+  args.tile_group = env_int("GRILLY_GEMM_GROUP", 8);
   args.err = ctx->err_dev;
   auto kern = gemm_tcgen05_pair_kernel<kBf16>;
   const void* key = reinterpret_cast<const void*>(kern);

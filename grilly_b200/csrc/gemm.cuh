@@ -368,6 +368,20 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
   }
 }
 
+// Tile order of the persistent loops. Tiles that run at the same time should share operand rows, and the set of
+// co-running tiles (one per SM) should be roughly square in loaded rows, or a large problem re-reads one operand
+// from DRAM once per row of tiles. `fast` blocks are walked in groups of `group`: inside a group the fast index
+// varies first, then the slow one; with group >= num_fast this is plain fast-major order.
+__device__ __forceinline__ void tile_coords(int tile, int num_fast, int num_slow, int group, int& fast, int& slow) {
+  const int per_group = group * num_slow;
+  const int g = tile / per_group;
+  const int first = g * group;
+  const int gsz = min(num_fast - first, group);
+  const int r = tile - g * per_group;
+  slow = r / gsz;
+  fast = first + (r - slow * gsz);
+}
+
 template <int BN>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -450,8 +464,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         // un-swapped: column blocks fastest (neighbouring CTAs share the A rows); swapped: the weight blocks
         // (128-row operand) fastest, so neighbouring CTAs share one block of tokens
-        const int m_blk = kSwap ? tile % args.num_m_tiles : tile / args.num_n_tiles;
-        const int n_blk = kSwap ? tile / args.num_m_tiles : tile % args.num_n_tiles;
+        int m_blk, n_blk;
+        if constexpr (kSwap) tile_coords(tile, args.num_m_tiles, args.num_n_tiles, args.tile_group, m_blk, n_blk);
+        else tile_coords(tile, args.num_n_tiles, args.num_m_tiles, args.tile_group, n_blk, m_blk);
         for (int kb = 0; kb < args.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             if (!*abort_flag) atomicCAS(args.err, 0, ERR_WAIT_EMPTY);
@@ -546,8 +561,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     f.res_vec_ok = args.residual && (args.ld_res % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
     f.bias_vec_ok = args.bias && ((reinterpret_cast<uintptr_t>(args.bias) & 15) == 0);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int m_blk = kSwap ? tile % args.num_m_tiles : tile / args.num_n_tiles;
-      const int n_blk = kSwap ? tile / args.num_m_tiles : tile % args.num_n_tiles;
+      int m_blk, n_blk;
+      if constexpr (kSwap) tile_coords(tile, args.num_m_tiles, args.num_n_tiles, args.tile_group, m_blk, n_blk);
+      else tile_coords(tile, args.num_n_tiles, args.num_m_tiles, args.tile_group, n_blk, m_blk);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) {

@@ -94,8 +94,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       int issued = 0;
 #endif
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int m_blk = tile % args.num_m_tiles;             // feature blocks fastest: neighbours share the tokens
-        const int n_blk = tile / args.num_m_tiles;
+        int m_blk, n_blk;                                      // feature blocks fastest: neighbours share the tokens
+        tile_coords(tile, args.num_m_tiles, args.num_n_tiles, args.tile_group, m_blk, n_blk);
         const int w_row = m_blk * Cfg::TILE + static_cast<int>(rank) * 128;
         const int x_row = n_blk * Cfg::TILE + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < args.num_k_blocks; ++kb) {
@@ -169,8 +169,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     const uint32_t leader_tempty0 = map_to_cta(&tmem_empty[0], 0);
     int it = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
-      const int m_blk = tile % args.num_m_tiles;
-      const int n_blk = tile / args.num_m_tiles;
+      int m_blk, n_blk;
+      tile_coords(tile, args.num_m_tiles, args.num_n_tiles, args.tile_group, m_blk, n_blk);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) { fail(ERR_WAIT_TMEM_FULL); break; }
