@@ -19,6 +19,7 @@ ACT_NONE, ACT_GELU, ACT_SILU, ACT_RELU = 0, 1, 2, 3
 NORM_LAYER, NORM_RMS = 0, 1
 ELT_GELU, ELT_SILU, ELT_RELU, ELT_ADD, ELT_SWIGLU = 1, 2, 3, 4, 5
 ROPE_NONE, ROPE_INTERLEAVED, ROPE_ROTATE_HALF = 0, 1, 2
+DIST_L2, DIST_COSINE, DIST_DOT = 1, 2, 3
 FLAG_OUT_BF16, FLAG_ROUND_TF32, FLAG_SWIGLU_PAIRS = 1, 2, 4
 
 
@@ -82,6 +83,8 @@ SIGNATURES = {
     "grilly_encoder_keep_hidden": [_vp, _i],
     "grilly_encoder_last_hidden": [_vp, _vp, _ll, C.POINTER(_ll)],
     "grilly_encoder_destroy": [_vp],
+    "grilly_faiss_distances": [_vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "grilly_faiss_topk": [_vp, _vp, _i, _i, _i, _vp, _vp],
     "grilly_gemm_pick_tile": [_i, _i, _i],
     "grilly_plan_chunks": [_vp, _i, _i, _vp, _vp, C.POINTER(_ll)],
 }

@@ -472,6 +472,54 @@ class Learning(_Namespace):
         return out.numpy()
 
 
+class Faiss(_Namespace):
+    """backend/faiss.py ``VulkanFAISS``: pairwise distances and exact top-k selection."""
+
+    _TYPES = {"l2": L.DIST_L2, "cosine": L.DIST_COSINE, "dot": L.DIST_DOT}
+
+    def compute_distances(self, queries, database, distance_type="cosine"):
+        """(num_queries, num_database) distances: 'l2' sqrt(sum (q-d)^2), 'cosine' 1 - q.d/(|q||d| + 1e-8), 'dot'
+        -(q.d); an unknown name means cosine, as in the reference (backend/faiss.py:25-104, faiss-distance.glsl:29-83).
+        The dot products run on the tensor cores over tf32 hi/lo splits, so they carry fp32 accuracy. A NumPy
+        database is cached on the device like a weight (``backend.invalidate(database)`` after an in-place change)."""
+        if not isinstance(queries, DeviceTensor):
+            queries = np.asarray(queries, dtype=np.float32)
+            if queries.ndim == 1:
+                queries = queries.reshape(1, -1)
+        if len(queries.shape) != 2 or len(database.shape) != 2:
+            raise ValueError("queries must be (num_queries, dim) or (dim,), database (num_database, dim)")
+        nq, dim = (int(s) for s in queries.shape)
+        ndb, dim_db = (int(s) for s in database.shape)
+        if dim != dim_db:
+            raise ValueError(f"dimension mismatch: queries have {dim}, database has {dim_db}")
+        qd, host = self._act_in(queries, mma_operand=False)
+        dd = self.dev.weight(database, "f32", round_tf32=False, tag="faiss-db")
+        out = self.dev.empty((nq, ndb))
+        code = self._TYPES.get(distance_type, L.DIST_COSINE)
+        self.dev.check(self.lib.grilly_faiss_distances(self.ctx, _p(qd), _p(dd), _p(out), nq, ndb, dim, code))
+        return self._out(out, host)
+
+    def topk(self, distances, k):
+        """(indices uint32, distances fp32), each (num_queries, k): the k smallest entries of every row in ascending
+        order, ties by ascending index (backend/faiss.py:106-195). k is clipped to the row length as in the
+        reference; k above 1024 is not supported on the device."""
+        if not isinstance(distances, DeviceTensor):
+            distances = np.asarray(distances, dtype=np.float32)
+            if distances.ndim == 1:
+                distances = distances.reshape(1, -1)
+        if len(distances.shape) != 2:
+            raise ValueError("distances must be (num_queries, num_database)")
+        nq, ndb = (int(s) for s in distances.shape)
+        k = min(int(k), ndb)
+        if k <= 0:
+            raise ValueError("k must be positive")
+        dd, _ = self._act_in(distances, mma_operand=False)
+        idx = self.dev.empty((nq, k), "i32")
+        val = self.dev.empty((nq, k))
+        self.dev.check(self.lib.grilly_faiss_topk(self.ctx, _p(dd), nq, ndb, k, _p(idx), _p(val)))
+        return idx.numpy().view(np.uint32), val.numpy()
+
+
 class _PoolView:
     """``backend.fnn.buffer_pool.get_stats()`` (tutorials/06_transformer_components.py:142-145)."""
 
@@ -499,6 +547,7 @@ class Compute:
         self.attention = Attention(self)
         self.pooling = Pooling(self)
         self.learning = Learning(self)
+        self.faiss = Faiss(self)
         self._alias()
 
     def _alias(self):
@@ -512,6 +561,8 @@ class Compute:
         self.apply_rope = self.attention.apply_rope
         self.mean_pool = self.pooling.mean_pool
         self.embedding_lookup = self.learning.embedding_lookup
+        self.faiss_compute_distances = self.faiss.compute_distances   # backend/compute.py:143-150
+        self.faiss_topk = self.faiss.topk
 
     def set_architecture(self, architecture: str):
         """backend/compute.py:70-128. There are no per-architecture kernels here: causal masking is a flag."""

@@ -6,6 +6,7 @@ namespace gb {
 enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU = 3 };
 enum : int { ROPE_NONE = 0, ROPE_INTERLEAVED = 1, ROPE_ROTATE_HALF = 2 };
 enum : int { NORM_LAYER = 0, NORM_RMS = 1 };
+enum : int { DIST_NONE = 0, DIST_L2 = 1, DIST_COSINE = 2, DIST_DOT = 3 };
 enum : int { ELT_GELU = 1, ELT_SILU = 2, ELT_RELU = 3, ELT_ADD = 4, ELT_SWIGLU = 5 };
 
 struct GemmArgs {
@@ -27,6 +28,11 @@ struct GemmArgs {
   const float* row_mean;  // null for RMSNorm (no mean term)
   const float* row_rstd;  // null when no normalisation is folded in
   const float* col_sum;
+  // Distance epilogue (applied to the raw dot product before everything else): row_vec[r] = |a_r|^2, col_vec[c] = |b_c|^2
+  //   DIST_L2: sqrt(max(|a|^2 + |b|^2 - 2 acc, 0));  DIST_COSINE: 1 - acc / (|a| |b| + 1e-8);  DIST_DOT: -acc
+  int dist_mode;
+  const float* row_vec;
+  const float* col_vec;
   int* err;               // device status word
 };
 

@@ -1,0 +1,220 @@
+// Vector search on top of the GEMM: pairwise distances (reference backend/faiss.py:25-104, shader
+// faiss-distance.glsl:29-83) and top-k selection per query (backend/faiss.py:106-195, shader faiss-topk.glsl).
+//
+// Distances are one tcgen05 GEMM over split operands plus a distance epilogue. A single tf32 pass is 5e-4 off per
+// dot product, which reorders near neighbours, so every vector x is written as hi + lo (hi = x rounded to tf32,
+// lo = (x - hi) rounded to tf32) and the GEMM runs over K' = 3 dim with rows [hi | lo | hi] for the queries and
+// [hi | hi | lo] for the database: hi.hi + lo.hi + hi.lo in one fp32 accumulator, i.e. the fp32 dot product up to
+// the dropped lo.lo term (2^-22 relative). The squared norms the L2 and cosine forms need are taken from the
+// unsplit fp32 values by the same kernel that writes the split rows.
+//
+// Top-k is exact: a radix select over order-preserving 32-bit keys finds the k-th smallest distance of a row in four
+// histogram passes, one more pass collects everything below it and, in index order, as many ties as are still
+// needed, and a bitonic sort in shared memory puts the k results in ascending (distance, index) order.
+#include "gemm.cuh"  // round_to_tf32, GemmArgs
+#include "internal.h"
+#include <mutex>
+
+namespace gb {
+
+// One warp per row: out[row] = [hi | lo | hi] (query_side) or [hi | hi | lo], each part dim_pad wide (zero padded),
+// norm2[row] = sum x^2 in fp32.
+__global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ x, float* __restrict__ out,
+                                                         float* __restrict__ norm2, long long rows, int dim, int dim_pad,
+                                                         int query_side) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* xp = x + row * dim;
+  float* op = out + row * 3LL * dim_pad;
+  float s = 0.f;
+  for (int d = lane; d < dim_pad; d += 32) {
+    const float v = d < dim ? __ldg(xp + d) : 0.f;
+    const float hi = round_to_tf32(v);
+    const float lo = round_to_tf32(v - hi);
+    s = fmaf(v, v, s);
+    op[d] = hi;
+    op[dim_pad + d] = query_side ? lo : hi;
+    op[2 * dim_pad + d] = query_side ? hi : lo;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) norm2[row] = s;
+}
+
+// float -> uint32 whose unsigned order is the float order (-0 < +0, NaNs at the ends)
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+constexpr int TOPK_THREADS = 256;
+constexpr int TOPK_MAX_K = 1024;
+
+// One CTA per query row.
+__global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const float* __restrict__ dist, long long ld, int ndb, int k,
+                                                                 uint32_t* __restrict__ idx_out, float* __restrict__ val_out) {
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t s_prefix, s_need, s_count, s_ties;
+  __shared__ uint32_t warp_tot[TOPK_THREADS / 32];
+  __shared__ uint32_t cand_key[TOPK_MAX_K];
+  __shared__ uint32_t cand_idx[TOPK_MAX_K];
+  const float* row = dist + static_cast<long long>(blockIdx.x) * ld;
+  const int t = threadIdx.x;
+
+  // ---- radix select: after the loop s_prefix is the key of the k-th smallest element and s_need (>= 1) says how
+  // many elements equal to it belong to the result
+  if (t == 0) { s_prefix = 0; s_need = static_cast<uint32_t>(k); }
+  __syncthreads();
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    hist[t] = 0;                                    // TOPK_THREADS == 256 bins
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+    for (int i = t; i < ndb; i += TOPK_THREADS) {
+      const uint32_t key = order_key(__ldg(row + i));
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (t == 0) {
+      uint32_t need = s_need, bin = 0;
+      for (; bin < 255u; ++bin) {
+        if (hist[bin] >= need) break;
+        need -= hist[bin];
+      }
+      s_prefix = prefix | (bin << shift);
+      s_need = need;
+    }
+    __syncthreads();
+  }
+  const uint32_t kth = s_prefix;
+  const uint32_t need_ties = s_need;
+
+  // ---- collect: everything below the k-th key in any order, ties in index order until need_ties are taken
+  if (t == 0) { s_count = 0; s_ties = 0; }
+  __syncthreads();
+  const int lane = t & 31, warp = t >> 5;
+  for (int base = 0; base < ndb; base += TOPK_THREADS) {
+    const int i = base + t;
+    const uint32_t key = i < ndb ? order_key(__ldg(row + i)) : 0xffffffffu;
+    const bool below = i < ndb && key < kth;
+    const bool tie = i < ndb && key == kth;
+    if (below) {
+      const uint32_t slot = atomicAdd(&s_count, 1u);
+      cand_key[slot] = key;
+      cand_idx[slot] = static_cast<uint32_t>(i);
+    }
+    if (__syncthreads_or(tie)) {
+      // rank of each tie inside this block of 256 consecutive indices
+      const uint32_t bal = __ballot_sync(0xffffffffu, tie);
+      if (lane == 0) warp_tot[warp] = __popc(bal);
+      __syncthreads();
+      uint32_t before = s_ties;
+      for (int w = 0; w < warp; ++w) before += warp_tot[w];
+      const uint32_t rank = before + __popc(bal & ((1u << lane) - 1u));
+      if (tie && rank < need_ties) {
+        const uint32_t slot = atomicAdd(&s_count, 1u);
+        cand_key[slot] = key;
+        cand_idx[slot] = static_cast<uint32_t>(i);
+      }
+      __syncthreads();
+      if (t == 0) {
+        uint32_t tot = 0;
+        for (int w = 0; w < TOPK_THREADS / 32; ++w) tot += warp_tot[w];
+        s_ties += tot;
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+
+  // ---- sort the k candidates by (key, index): bitonic network over the next power of two, padded with maxima
+  int n2 = 1;
+  while (n2 < k) n2 <<= 1;
+  for (int i = k + t; i < n2; i += TOPK_THREADS) { cand_key[i] = 0xffffffffu; cand_idx[i] = 0xffffffffu; }
+  __syncthreads();
+  for (int size = 2; size <= n2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = t; i < n2; i += TOPK_THREADS) {
+        const int j = i ^ stride;
+        if (j > i) {
+          const bool up = (i & size) == 0;
+          const uint32_t ki = cand_key[i], kj = cand_key[j], ii = cand_idx[i], ij = cand_idx[j];
+          const bool gt = ki > kj || (ki == kj && ii > ij);
+          if (gt == up) { cand_key[i] = kj; cand_key[j] = ki; cand_idx[i] = ij; cand_idx[j] = ii; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = t; i < k; i += TOPK_THREADS) {
+    const uint32_t id = cand_idx[i];
+    idx_out[static_cast<long long>(blockIdx.x) * k + i] = id;
+    val_out[static_cast<long long>(blockIdx.x) * k + i] = __ldg(row + id);
+  }
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+extern "C" {
+
+int grilly_faiss_distances(grilly_ctx* ctx, const float* queries, const float* database, float* out, int num_queries,
+                           int num_database, int dim, int distance_type) {
+  if (!ctx) return GRILLY_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (cudaSetDevice(ctx->device) != cudaSuccess) return set_error(ctx, GRILLY_ERR_CUDA, "cudaSetDevice failed");
+  if (!queries || !database || !out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_distances: null operand");
+  if (num_queries <= 0 || num_database <= 0 || dim <= 0)
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_distances: sizes must be positive");
+  if (distance_type < GRILLY_DIST_L2 || distance_type > GRILLY_DIST_DOT)
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_distances: distance_type must be L2, COSINE or DOT");
+  const int dim_pad = (dim + 3) & ~3;                       // 16-byte rows for the TMA descriptors
+  const long long kq = 3LL * dim_pad;
+  if (kq > 2147483647LL) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "faiss_distances: dim too large");
+  float *qs = nullptr, *ds = nullptr, *qn = nullptr, *dn = nullptr;
+  const size_t q_bytes = static_cast<size_t>(num_queries) * kq * sizeof(float);
+  const size_t d_bytes = static_cast<size_t>(num_database) * kq * sizeof(float);
+  cudaError_t e = cudaMallocAsync(&qs, q_bytes, ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&ds, d_bytes, ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&qn, static_cast<size_t>(num_queries) * sizeof(float), ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&dn, static_cast<size_t>(num_database) * sizeof(float), ctx->stream);
+  int rc = GRILLY_OK;
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    rc = set_error(ctx, GRILLY_ERR_OOM, "faiss_distances: no memory for the split operands (3 x the size of queries + database)");
+  } else {
+    split_rows_kernel<<<(num_queries + 7) / 8, 256, 0, ctx->stream>>>(queries, qs, qn, num_queries, dim, dim_pad, 1);
+    split_rows_kernel<<<(num_database + 7) / 8, 256, 0, ctx->stream>>>(database, ds, dn, num_database, dim, dim_pad, 0);
+    ctx->launches += 2;
+    GemmArgs a{};
+    a.M = num_queries; a.N = num_database; a.K = static_cast<int>(kq);
+    a.out = out; a.ld_out = num_database;
+    a.dist_mode = distance_type;                            // GRILLY_DIST_* == gb::DIST_*
+    a.row_vec = qn; a.col_vec = dn;
+    rc = launch_gemm(ctx, false, false, qs, ds, a, 0);
+  }
+  if (qs) cudaFreeAsync(qs, ctx->stream);
+  if (ds) cudaFreeAsync(ds, ctx->stream);
+  if (qn) cudaFreeAsync(qn, ctx->stream);
+  if (dn) cudaFreeAsync(dn, ctx->stream);
+  return rc;
+}
+
+int grilly_faiss_topk(grilly_ctx* ctx, const float* distances, int num_queries, int num_database, int k,
+                      unsigned int* indices_out, float* distances_out) {
+  if (!ctx) return GRILLY_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (cudaSetDevice(ctx->device) != cudaSuccess) return set_error(ctx, GRILLY_ERR_CUDA, "cudaSetDevice failed");
+  if (!distances || !indices_out || !distances_out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_topk: null operand");
+  if (num_queries <= 0 || num_database <= 0 || k <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_topk: sizes must be positive");
+  if (k > num_database) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_topk: k exceeds the number of database vectors");
+  if (k > TOPK_MAX_K) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "faiss_topk: k is limited to 1024");
+  topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(distances, num_database, num_database, k, indices_out, distances_out);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+
+}  // extern "C"

@@ -54,6 +54,13 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+// Distance epilogue: the accumulator is a dot product, a2 and b2 are the squared norms of the two vectors.
+__device__ __forceinline__ float dist_from_dot(int mode, float acc, float a2, float b2) {
+  if (mode == DIST_L2) return sqrtf(fmaxf(a2 + b2 - 2.f * acc, 0.f));
+  if (mode == DIST_COSINE) return 1.f - acc / (sqrtf(a2) * sqrtf(b2) + 1e-8f);
+  return -acc;
+}
+
 struct EpiFlags {
   bool vec_ok, vec8_ok, res_vec_ok, bias_vec_ok;
 };
@@ -65,6 +72,12 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (args.dist_mode) {
+    const float a2 = args.row_vec ? __ldg(args.row_vec + row) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < args.N) v[j] = dist_from_dot(args.dist_mode, v[j], a2, args.col_vec ? __ldg(args.col_vec + col0 + j) : 0.f);
+  }
   if (col0 + 32 <= args.N) {
     // ---------------- fast path: the whole 32-column chunk is inside the matrix
     if (args.row_rstd) {
@@ -260,7 +273,8 @@ __device__ __forceinline__ void epilogue_swapped_fast(const GemmArgs& args, cons
 __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, const uint32_t (&r)[32], int f, int t0) {
   const bool f_ok = f < args.N;
   const bool full = t0 + 32 <= args.M;
-  if (full && f_ok && !args.out_bf16 && !args.row_rstd && !args.swiglu_pairs && !(args.residual && args.residual_bf16)) {
+  if (full && f_ok && !args.out_bf16 && !args.row_rstd && !args.swiglu_pairs && !args.dist_mode &&
+      !(args.residual && args.residual_bf16)) {
     const float b = args.bias ? __ldg(args.bias + f) : 0.f;
     if (args.residual) {
       switch (args.act) {
@@ -280,6 +294,12 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (args.dist_mode) {
+    const float b2 = (args.col_vec && f_ok) ? __ldg(args.col_vec + f) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || t0 + j < args.M) v[j] = dist_from_dot(args.dist_mode, v[j], args.row_vec ? __ldg(args.row_vec + t0 + j) : 0.f, b2);
+  }
   if (args.row_rstd) {
     const float cs = (args.row_mean && f_ok) ? __ldg(args.col_sum + f) : 0.f;
 #pragma unroll

@@ -38,6 +38,7 @@ enum { GRILLY_ACT_NONE = 0, GRILLY_ACT_GELU = 1, GRILLY_ACT_SILU = 2, GRILLY_ACT
 enum { GRILLY_NORM_LAYER = 0, GRILLY_NORM_RMS = 1 };
 enum { GRILLY_ELT_GELU = 1, GRILLY_ELT_SILU = 2, GRILLY_ELT_RELU = 3, GRILLY_ELT_ADD = 4, GRILLY_ELT_SWIGLU = 5 };
 enum { GRILLY_ROPE_NONE = 0, GRILLY_ROPE_INTERLEAVED = 1, GRILLY_ROPE_ROTATE_HALF = 2 };
+enum { GRILLY_DIST_L2 = 1, GRILLY_DIST_COSINE = 2, GRILLY_DIST_DOT = 3 };  /* faiss-distance.glsl:25 (there 0, 1, 2) */
 
 /* flags for the GEMM family, attention and the norms */
 enum {
@@ -222,6 +223,22 @@ int grilly_encoder_keep_hidden(grilly_encoder* enc, int on);
 /* final hidden states of the last forward (packed rows, fp32 [total_tokens][hidden]) for parity checks */
 int grilly_encoder_last_hidden(grilly_encoder* enc, float* out_host, long long max_rows, long long* rows);
 int grilly_encoder_destroy(grilly_encoder* enc);
+
+/* ---- vector search over the embeddings ---------------------------------------------------------------------- */
+/* Replaces VulkanFAISS.compute_distances (backend/faiss.py:25-104; shader faiss-distance.glsl:29-83):
+ * out[q][d] for queries fp32 [num_queries][dim] and database fp32 [num_database][dim], all device pointers.
+ *   GRILLY_DIST_L2     sqrt(sum (q - d)^2), evaluated as sqrt(max(|q|^2 + |d|^2 - 2 q.d, 0))
+ *   GRILLY_DIST_COSINE 1 - q.d / (|q| |d| + 1e-8)
+ *   GRILLY_DIST_DOT    -(q.d)
+ * The dot products come from one tensor-core GEMM over tf32 hi/lo splits of both operands (fp32-level accuracy);
+ * scratch of 3 x the operand bytes is taken from the context's pool for the duration of the call. Asynchronous. */
+int grilly_faiss_distances(grilly_ctx* ctx, const float* queries, const float* database, float* out, int num_queries,
+                           int num_database, int dim, int distance_type);
+/* Replaces VulkanFAISS.topk (backend/faiss.py:120-195; shader faiss-topk.glsl): for each of num_queries rows of
+ * distances fp32 [num_queries][num_database], the k smallest values in ascending order (equal values by ascending
+ * index) and their column indices. Exact selection; 1 <= k <= min(num_database, 1024). Asynchronous. */
+int grilly_faiss_topk(grilly_ctx* ctx, const float* distances, int num_queries, int num_database, int k,
+                      unsigned int* indices_out, float* distances_out);
 
 /* ---- host-side planning helpers (no GPU needed; exposed so the host logic can be tested on CPU) ------------- */
 /* N-tile (64/128/192/256) the GEMM launcher picks for an M x N output on a GPU with num_sms SMs. */

@@ -285,6 +285,35 @@ def encoder_forward(ids, mask, w, num_heads, embed_eps=1e-12, layer_eps=1e-5, re
     return (out, x) if return_hidden else out
 
 
+# --------------------------------------------------------------------------- vector search
+def faiss_distances(queries, database, distance_type="cosine"):
+    """Pairwise distances as the shader states them (shaders/faiss-distance.glsl:29-83; the reference has no CPU
+    branch for this op): 'l2' sqrt(sum (q-d)^2), 'cosine' 1 - q.d / (sqrt(q.q) sqrt(d.d) + 1e-8), 'dot' -(q.d);
+    any other name is treated as cosine (backend/faiss.py:44-45)."""
+    q = np.asarray(queries, np.float64)
+    if q.ndim == 1:
+        q = q.reshape(1, -1)
+    d = np.asarray(database, np.float64)
+    if distance_type == "l2":
+        out = np.sqrt(((q[:, None, :] - d[None, :, :]) ** 2).sum(-1))
+    elif distance_type == "dot":
+        out = -(q @ d.T)
+    else:
+        out = 1.0 - (q @ d.T) / (np.sqrt((q * q).sum(-1))[:, None] * np.sqrt((d * d).sum(-1))[None, :] + 1e-8)
+    return out.astype(np.float32)
+
+
+def faiss_topk(distances, k):
+    """k smallest entries per row, ascending (backend/faiss.py:106-118). The reference leaves the order of equal
+    values to argpartition/argsort; here equal values come by ascending index, which is one of the orders it allows."""
+    dist = np.asarray(distances, np.float32)
+    if dist.ndim == 1:
+        dist = dist.reshape(1, -1)
+    k = min(int(k), dist.shape[1])
+    idx = np.argsort(dist, axis=1, kind="stable")[:, :k]
+    return idx.astype(np.uint32), np.take_along_axis(dist, idx, axis=1).astype(np.float32)
+
+
 # --------------------------------------------------------------------------- checkers
 def rel_l2(a, b):
     """||a - b||_2 / ||b||_2 in float64."""

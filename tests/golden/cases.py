@@ -58,3 +58,15 @@ def encoder_layer_cfg2():
     lens = np.array([24, 9, 16])
     mask = (np.arange(S)[None, :] < lens[:, None]).astype(f32)
     return dict(lw=lw, x=x, mask=mask, num_heads=12)
+
+
+def faiss_search():
+    """Vector search: 10 queries and 1000 database vectors of dimension 256 ~ N(0,1) (the sizes of the reference's
+    end-to-end test), a distance matrix for top-k with exact ties in it, seed 42."""
+    rng = np.random.default_rng(42)
+    queries = rng.standard_normal((10, 256)).astype(f32)
+    database = rng.standard_normal((1000, 256)).astype(f32)
+    dist = rng.standard_normal((10, 1000)).astype(f32)
+    dist[3, 100:140] = dist[3].min() - 1.0      # forty equal smallest values: more ties than k
+    dist[5, ::7] = np.round(dist[5, ::7], 1)    # scattered exact ties
+    return dict(queries=queries, database=database, dist=dist, k=20)

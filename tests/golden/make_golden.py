@@ -1,8 +1,9 @@
-"""Generates tests/golden/hotpath_golden.npz by running the REFERENCE's own CPU code paths.
+"""Generates tests/golden/hotpath_golden.npz and faiss_golden.npz by running the REFERENCE's own CPU code paths.
 
 Run where the reference source tree is available:
 
-    python tests/golden/make_golden.py /path/to/grilly-source
+    python tests/golden/make_golden.py /path/to/grilly-source            # both files
+    python tests/golden/make_golden.py /path/to/grilly-source --faiss-only
 
 The reference is imported as the package ``grilly`` through a temporary symlink (its tree is not copied),
 Vulkan is absent so every op takes its numba/NumPy branch. Inputs come from the seeded generators in
@@ -22,6 +23,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parent))
 import cases  # noqa: E402
 
 OUT = Path(__file__).resolve().parent / "hotpath_golden.npz"
+OUT_FAISS = Path(__file__).resolve().parent / "faiss_golden.npz"
 
 
 def import_reference(src: str):
@@ -114,5 +116,23 @@ def main(src: str) -> None:
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 
 
+def main_faiss(src: str) -> None:
+    """Top-k through the reference's own CPU selection (backend/faiss.py:106-118; ``topk`` takes it when there is no
+    Vulkan device). ``compute_distances`` has no CPU branch in the reference, so no distance matrix is stored."""
+    import_reference(src)
+    from grilly.backend.faiss import VulkanFAISS
+    c = cases.faiss_search()
+    idx, val = VulkanFAISS(None, None).topk(c["dist"], c["k"])
+    g = {"topk_idx": np.asarray(idx, np.uint32), "topk_val": np.asarray(val, np.float32)}
+    np.savez_compressed(OUT_FAISS, **g)
+    print(f"wrote {OUT_FAISS} ({OUT_FAISS.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    src = args[0] if args else "/root/reference"
+    if "--faiss-only" in sys.argv:
+        main_faiss(src)
+    else:
+        main(src)
+        main_faiss(src)
