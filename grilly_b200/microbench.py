@@ -4,6 +4,7 @@
     gemm       C = A B, row-major                    --m --n --k --precision
     attention  flash_attention2 on packed sentences  --b --s --h --d (lengths uniform in [16, s]) --causal --rope
     layernorm  y = LayerNorm(x)                      --m --n
+    faiss      cosine distances (--m queries, --n database vectors, --k dim) and top-k (--topk) of the result
 
 Inputs are seeded synthetic data already resident on the GPU; the op is launched ``--warmup`` times, then ``--reps``
 launches are timed with CUDA events on the launching stream and the average is printed with the algorithmic
@@ -75,7 +76,7 @@ def _nsplit(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["linear", "gemm", "attention", "layernorm"])
+    ap.add_argument("op", choices=["linear", "gemm", "attention", "layernorm", "faiss"])
     ap.add_argument("--m", "--dim-m", dest="m", type=int, default=18432)
     ap.add_argument("--n", "--dim-n", dest="n", type=int, default=1536)
     ap.add_argument("--k", "--dim-k", dest="k", type=int, default=384)
@@ -89,6 +90,7 @@ def main(argv=None):
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--rope", action="store_true")
     ap.add_argument("--full-length", action="store_true", help="attention: every sentence has length s")
+    ap.add_argument("--topk", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--device", type=int, default=0)
@@ -138,6 +140,19 @@ def main(argv=None):
                 None, 1.0 / math.sqrt(a.d), int(a.causal), rope, 10000.0, 1.0, prec, 0))
             flops = 4.0 * a.h * a.d * float((lens.astype(np.float64) ** 2).sum()) * (0.5 if a.causal else 1.0)
             nbytes = T * F * (3.0 * elt + 4.0)
+        elif a.op == "faiss":
+            q = dev.upload(rng.standard_normal((a.m, a.k)).astype(np.float32))
+            db = dev.upload(rng.standard_normal((a.n, a.k)).astype(np.float32))
+            dist = dev.empty((a.m, a.n))
+            idx = dev.empty((a.m, a.topk), "i32")
+            val = dev.empty((a.m, a.topk))
+            fn = lambda: dev.check(lib.grilly_faiss_distances(ctx, q.ptr, db.ptr, dist.ptr, a.m, a.n, a.k, L.DIST_COSINE))  # noqa: E731
+            ms = _time(dev, fn, a.warmup, a.reps)
+            print(f"faiss distances {a.m} x {a.n} x {a.k}: {ms * 1e3:.1f} us/launch  {2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s "
+                  f"(fp32 dot products; the split GEMM does 3x that)  {4.0 * (a.m * a.k + a.n * a.k + a.m * a.n) / ms / 1e6:.1f} GB/s (algorithmic)")
+            fn = lambda: dev.check(lib.grilly_faiss_topk(ctx, dist.ptr, a.m, a.n, a.topk, idx.ptr, val.ptr))  # noqa: E731
+            flops = 0.0
+            nbytes = 4.0 * a.m * a.n                       # every distance read once
         else:
             x = dev.upload(rng.standard_normal((a.m, a.n)).astype(np.float32))
             g = dev.upload(np.ones(a.n, np.float32))
