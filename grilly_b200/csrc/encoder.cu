@@ -397,6 +397,10 @@ int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* 
   if (!ids_host || !out_host || B <= 0 || S <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_forward: bad arguments");
   int rc = ensure_io(e, B, S);
   if (rc) return rc;
+  // the ids go on their way first: the copy runs while the host reads the mask
+  const size_t n_ids = static_cast<size_t>(B) * S;
+  std::memcpy(e->ids_pin, ids_host, n_ids * sizeof(int));
+  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->ids_dev, e->ids_pin, n_ids * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
   // valid lengths from the mask; the packed path needs every mask row to be a prefix of ones
   std::vector<int> lengths(B);
   bool holes = false;
@@ -411,9 +415,6 @@ int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* 
     }
     lengths[b] = len;
   }
-  const size_t n_ids = static_cast<size_t>(B) * S;
-  std::memcpy(e->ids_pin, ids_host, n_ids * sizeof(int));
-  GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->ids_dev, e->ids_pin, n_ids * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
   if (holes) {
     GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->mask_dev, mask_host, n_ids * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
     rc = forward_padded_nolock(e, e->ids_dev, e->mask_dev, B, S, e->out_dev);

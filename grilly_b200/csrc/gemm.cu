@@ -66,23 +66,32 @@ static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& a
   return GRILLY_OK;
 }
 
-// CTA-pair variant (gemm_pair.cuh): weights [N][K] and tokens [M][K], both K-major; tiles of 256 features x 256 tokens.
-template <bool kBf16>
+// CTA-pair variant (gemm_pair.cuh), tiles of 256 x 256. kBMn = false: `linear`, x = tokens [M][K], w = weights [N][K],
+// both K-major. kBMn = true: `gemm_mnk`, x = A [M][K], w = B [K][N] row-major.
+template <bool kBf16, bool kBMn>
 static int launch_pair(grilly_ctx* ctx, const void* x, const void* w, GemmArgs& args) {
   using Cfg = GemmPairCfg;
   constexpr int ELT = kBf16 ? 2 : 4;
   constexpr int BK = 128 / ELT;
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
-  CUtensorMap tw, tx;
+  CUtensorMap tw, tx;   // tw: the MMA's M operand, tx: its N operand
   int rc;
-  if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tw))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, x, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tx))) return rc;
-  args.num_m_tiles = (args.N + Cfg::TILE - 1) / Cfg::TILE;
-  args.num_n_tiles = (args.M + Cfg::TILE - 1) / Cfg::TILE;
+  if (kBMn) {
+    if ((rc = get_tmap_2d(ctx, dtype, x, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tw))) return rc;
+    if ((rc = get_tmap_2d(ctx, dtype, w, args.N, args.K, static_cast<uint64_t>(args.N) * ELT, 128 / ELT, BK, &tx,
+                          kBf16 ? TM_SW128 : TM_SW128_ATOM32))) return rc;
+    args.num_m_tiles = (args.M + Cfg::TILE - 1) / Cfg::TILE;
+    args.num_n_tiles = (args.N + Cfg::TILE - 1) / Cfg::TILE;
+  } else {
+    if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tw))) return rc;
+    if ((rc = get_tmap_2d(ctx, dtype, x, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &tx))) return rc;
+    args.num_m_tiles = (args.N + Cfg::TILE - 1) / Cfg::TILE;
+    args.num_n_tiles = (args.M + Cfg::TILE - 1) / Cfg::TILE;
+  }
   args.num_k_blocks = (args.K + BK - 1) / BK;
   args.tile_group = env_int("GRILLY_GEMM_GROUP", 8);
   args.err = ctx->err_dev;
-  auto kern = gemm_tcgen05_pair_kernel<kBf16>;
+  auto kern = gemm_tcgen05_pair_kernel<kBf16, kBMn>;
   const void* key = reinterpret_cast<const void*>(kern);
   if (!ctx->smem_attr_done.count(key)) {
     GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -124,9 +133,11 @@ static int launch_pair(grilly_ctx* ctx, const void* x, const void* w, GemmArgs& 
 // A pair tile covers 256 features: worth it when the GEMM is large enough to be bound by operand traffic and the
 // last feature block is not mostly padding (384 features would waste a quarter of the MMAs).
 static bool pick_pair(int M, int N, bool b_mn_major) {
-  if (b_mn_major || M < 1024 || N < 256) return false;
+  if (M < 1024 || N < 256) return false;
   const int padded = (N + 255) / 256 * 256;
-  return padded * 8 <= N * 9;
+  if (padded * 8 > N * 9) return false;
+  // gemm_mnk tiles the rows of C in 256s as well
+  return !b_mn_major || ((M + 255) / 256 * 256) * 8 <= M * 9;
 }
 
 // One tcgen05.mma takes about the same time for any N up to 256, so a tile costs the same whatever its width:
@@ -168,8 +179,11 @@ int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, cons
     if (const char* env = getenv("GRILLY_GEMM_BN")) force_bn = atoi(env);
   }
   bool pair = pick_pair(args.M, args.N, b_mn_major);
-  if (const char* env = getenv("GRILLY_GEMM_PAIR")) pair = !b_mn_major && atoi(env) != 0;  // tuning/debug override
-  if (pair && force_bn <= 0) return bf16 ? launch_pair<true>(ctx, a, b, args) : launch_pair<false>(ctx, a, b, args);
+  if (const char* env = getenv("GRILLY_GEMM_PAIR")) pair = atoi(env) != 0;  // tuning/debug override
+  if (pair && force_bn <= 0) {
+    if (b_mn_major) return bf16 ? launch_pair<true, true>(ctx, a, b, args) : launch_pair<false, true>(ctx, a, b, args);
+    return bf16 ? launch_pair<true, false>(ctx, a, b, args) : launch_pair<false, false>(ctx, a, b, args);
+  }
   bool swap = pick_swap(args.N, b_mn_major);
   if (const char* env = getenv("GRILLY_GEMM_SWAP")) swap = !b_mn_major && atoi(env) != 0;  // tuning/debug override
   const int bn = force_bn > 0 ? force_bn : pick_bn(swap ? args.M : args.N);

@@ -25,7 +25,12 @@ struct GemmPairCfg {
   static constexpr int TILE = 256;                             // features and tokens per pair tile
 };
 
-template <bool kBf16>
+// kBMn = false: `linear` (tmap_w = weights [N][K], the MMA's M operand; tmap_x = tokens [M][K], the MMA's N operand;
+// accumulator lanes are features, the swapped epilogue writes y[token][feature]).
+// kBMn = true: `gemm_mnk` (tmap_w = A [M][K], the MMA's M operand; tmap_x = B [K][N] row-major, consumed in place as
+// an MN-major N operand in 128-byte-wide column chunks; accumulator lanes are rows of C, the plain epilogue writes
+// C[row][col]). num_m_tiles / num_n_tiles count 256-blocks of the MMA's M / N operand in both cases.
+template <bool kBf16, bool kBMn>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                          const GemmArgs args) {
@@ -33,8 +38,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
   constexpr int STAGES = Cfg::STAGES;
   constexpr int ELT = kBf16 ? 2 : 4;
   constexpr int BK = 128 / ELT;
+  constexpr int CH = 128 / ELT;                                // columns per 128-byte chunk of an MN-major operand
+  constexpr int UMMA_K = 32 / ELT;
   constexpr int KSTEPS = 4;                                    // 32-byte k-steps per 128-byte stage row
-  constexpr uint32_t IDESC = make_idesc(kBf16, 256, 256, false, false);
+  constexpr uint32_t IDESC = make_idesc(kBf16, 256, 256, false, kBMn);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -110,7 +117,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);   // both CTAs' bytes land on this barrier
           const uint32_t bar = map_to_cta(&full_bar[stage], 0);
           tma_load_2d_pair(sw, &tmap_w, bar, kb * BK, w_row);
-          tma_load_2d_pair(sx, &tmap_x, bar, kb * BK, x_row);
+          if constexpr (kBMn) {
+#pragma unroll
+            for (int c = 0; c < 128 / CH; ++c)                 // this CTA's 128 columns, one chunk of CH columns at a time
+              tma_load_2d_pair(sx + c * (BK * 128), &tmap_x, bar, x_row + c * CH, kb * BK);
+          } else {
+            tma_load_2d_pair(sx, &tmap_x, bar, kb * BK, x_row);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -124,7 +137,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
       const uint64_t a_desc0 = make_smem_desc_sw128(smem_base, 16, 1024);
-      const uint64_t b_desc0 = make_smem_desc_sw128(smem_base + Cfg::HALF_BYTES, 16, 1024);
+      constexpr uint32_t B_KSTEP_BYTES = kBMn ? UMMA_K * 128 : 32;   // advance of the N operand per 32-byte k-step
+      const uint64_t b_desc0 = kBMn ? make_smem_desc_mn<kBf16>(smem_base + Cfg::HALF_BYTES, BK * 128)
+                                    : make_smem_desc_sw128(smem_base + Cfg::HALF_BYTES, 16, 1024);
       const uint32_t a_desc_lo = static_cast<uint32_t>(a_desc0), a_desc_hi = static_cast<uint32_t>(a_desc0 >> 32);
       const uint32_t b_desc_lo = static_cast<uint32_t>(b_desc0), b_desc_hi = static_cast<uint32_t>(b_desc0 >> 32);
       const uint32_t peer_empty0 = map_to_cta(&empty_bar[0], 1), own_empty0 = map_to_cta(&empty_bar[0], 0);
@@ -144,7 +159,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
           for (int ks = 0; ks < KSTEPS; ++ks) {
             const uint64_t adesc = (static_cast<uint64_t>(a_desc_hi) << 32) | (a_lo + ks * 2);
-            const uint64_t bdesc = (static_cast<uint64_t>(b_desc_hi) << 32) | (b_lo + ks * 2);
+            const uint64_t bdesc = (static_cast<uint64_t>(b_desc_hi) << 32) | (b_lo + ks * (B_KSTEP_BYTES >> 4));
             umma_ss_pair<kBf16>(d_tmem, adesc, bdesc, IDESC, (kb | ks) != 0 ? 1u : 0u);
           }
 #endif
@@ -168,6 +183,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     const int group = (warp - 2) >> 2;
     const uint32_t leader_tempty0 = map_to_cta(&tmem_empty[0], 0);
     int it = 0;
+    EpiFlags f;
+    const bool out_al16 = (reinterpret_cast<uintptr_t>(args.out) & 15) == 0;
+    f.vec_ok = !args.out_bf16 && (args.ld_out % 4 == 0) && out_al16;
+    f.vec8_ok = args.out_bf16 && (args.ld_out % 8 == 0) && out_al16;
+    f.res_vec_ok = args.residual && (args.ld_res % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
+    f.bias_vec_ok = args.bias && ((reinterpret_cast<uintptr_t>(args.bias) & 15) == 0);
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
       int m_blk, n_blk;
       tile_coords(tile, args.num_m_tiles, args.num_n_tiles, args.tile_group, m_blk, n_blk);
@@ -193,7 +214,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         if (c < NCHUNK && tok0 < 0) epilogue_chunk_swapped(args, cur, feat, tok0);  // timing experiment: drain only
         continue;
 #endif
-        if (c < NCHUNK && tok0 < args.M) epilogue_chunk_swapped(args, cur, feat, tok0);
+        if constexpr (kBMn) {
+          // feat is the row of C, tok0 the first of 32 columns
+          if (c < NCHUNK && feat < args.M && tok0 < args.N) epilogue_chunk(args, f, cur, feat, tok0, 0.f, 1.f);
+        } else {
+          if (c < NCHUNK && tok0 < args.M) epilogue_chunk_swapped(args, cur, feat, tok0);
+        }
       }
       tc_fence_before();
       __syncwarp();
