@@ -28,11 +28,6 @@ struct GemmArgs {
   const float* row_mean;  // null for RMSNorm (no mean term)
   const float* row_rstd;  // null when no normalisation is folded in
   const float* col_sum;
-  // Distance epilogue (applied to the raw dot product before everything else): row_vec[r] = |a_r|^2, col_vec[c] = |b_c|^2
-  //   DIST_L2: sqrt(max(|a|^2 + |b|^2 - 2 acc, 0));  DIST_COSINE: 1 - acc / (|a| |b| + 1e-8);  DIST_DOT: -acc
-  int dist_mode;
-  const float* row_vec;
-  const float* col_vec;
   int* err;               // device status word
 };
 

@@ -429,9 +429,20 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const long long orow = static_cast<long long>(row0 + qi) * args.ld_out + h * D;
       if (args.out_bf16) {
         __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + orow;
+        const bool v8 = (args.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0) && (D % 8 == 0);
 #pragma unroll
-        for (int d = 0; d < D; d += 2)
-          *reinterpret_cast<__nv_bfloat162*>(op + d) = __floats2bfloat162_rn(o_acc[d] * inv, o_acc[d + 1] * inv);
+        for (int d = 0; d < D; d += 8) {
+          uint4 q;   // eight bf16 per 16-byte store
+          q.x = pack_bf16x2(o_acc[d] * inv, o_acc[d + 1] * inv);
+          q.y = pack_bf16x2(o_acc[d + 2] * inv, o_acc[d + 3] * inv);
+          q.z = pack_bf16x2(o_acc[d + 4] * inv, o_acc[d + 5] * inv);
+          q.w = pack_bf16x2(o_acc[d + 6] * inv, o_acc[d + 7] * inv);
+          if (v8) *reinterpret_cast<uint4*>(op + d) = q;
+          else {
+            uint32_t* o32 = reinterpret_cast<uint32_t*>(op + d);
+            o32[0] = q.x; o32[1] = q.y; o32[2] = q.z; o32[3] = q.w;
+          }
+        }
       } else {
         float* op = reinterpret_cast<float*>(args.out) + orow;
         const bool v4 = (args.ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);

@@ -291,9 +291,20 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (row_ok) {
               if (args.out_bf16) {
                 __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + orow + c * 32;
+                const bool v8 = (args.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);
 #pragma unroll
-                for (int j = 0; j < 32; j += 2)
-                  *reinterpret_cast<uint32_t*>(op + j) = pack_bf16x2(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 q;   // eight bf16 per 16-byte store
+                  q.x = pack_bf16x2(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+                  q.y = pack_bf16x2(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
+                  q.z = pack_bf16x2(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
+                  q.w = pack_bf16x2(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
+                  if (v8) *reinterpret_cast<uint4*>(op + j) = q;
+                  else {
+                    uint32_t* o32 = reinterpret_cast<uint32_t*>(op + j);   // head offsets are even: 4-byte aligned
+                    o32[0] = q.x; o32[1] = q.y; o32[2] = q.z; o32[3] = q.w;
+                  }
+                }
               } else {
                 float* op = reinterpret_cast<float*>(args.out) + orow + c * 32;
                 const bool v4 = (args.ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);

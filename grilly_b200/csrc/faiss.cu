@@ -1,7 +1,8 @@
 // Vector search on top of the GEMM: pairwise distances (reference backend/faiss.py:25-104, shader
 // faiss-distance.glsl:29-83) and top-k selection per query (backend/faiss.py:106-195, shader faiss-topk.glsl).
 //
-// Distances are one tcgen05 GEMM over split operands plus a distance epilogue. A single tf32 pass is 5e-4 off per
+// Distances are one tcgen05 GEMM over split operands plus one elementwise pass that turns dot products into distances
+// (kept out of the GEMM's epilogue: that code is shared with the encoder's launches and is register-critical). A single tf32 pass is 5e-4 off per
 // dot product, which reorders near neighbours, so every vector x is written as hi + lo (hi = x rounded to tf32,
 // lo = (x - hi) rounded to tf32) and the GEMM runs over K' = 3 dim with rows [hi | lo | hi] for the queries and
 // [hi | hi | lo] for the database: hi.hi + lo.hi + hi.lo in one fp32 accumulator, i.e. the fp32 dot product up to
@@ -13,6 +14,7 @@
 // needed, and a bitonic sort in shared memory puts the k results in ascending (distance, index) order.
 #include "gemm.cuh"  // round_to_tf32, GemmArgs
 #include "internal.h"
+#include <algorithm>
 #include <mutex>
 
 namespace gb {
@@ -40,6 +42,22 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if (lane == 0) norm2[row] = s;
+}
+
+// In place: out[q][d] holds q.d on entry; qn2 / dn2 are the squared norms.
+__global__ void __launch_bounds__(256) dot_to_distance_kernel(float* __restrict__ out, const float* __restrict__ qn2,
+                                                              const float* __restrict__ dn2, int nq, int ndb, int mode) {
+  const long long total = static_cast<long long>(nq) * ndb;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int q = static_cast<int>(i / ndb), d = static_cast<int>(i - static_cast<long long>(q) * ndb);
+    const float acc = out[i];
+    float r;
+    if (mode == DIST_L2) r = sqrtf(fmaxf(__ldg(qn2 + q) + __ldg(dn2 + d) - 2.f * acc, 0.f));
+    else if (mode == DIST_COSINE) r = 1.f - acc / (sqrtf(__ldg(qn2 + q)) * sqrtf(__ldg(dn2 + d)) + 1e-8f);
+    else r = -acc;
+    out[i] = r;
+  }
 }
 
 // float -> uint32 whose unsigned order is the float order (-0 < +0, NaNs at the ends)
@@ -191,9 +209,14 @@ int grilly_faiss_distances(grilly_ctx* ctx, const float* queries, const float* d
     GemmArgs a{};
     a.M = num_queries; a.N = num_database; a.K = static_cast<int>(kq);
     a.out = out; a.ld_out = num_database;
-    a.dist_mode = distance_type;                            // GRILLY_DIST_* == gb::DIST_*
-    a.row_vec = qn; a.col_vec = dn;
     rc = launch_gemm(ctx, false, false, qs, ds, a, 0);
+    if (!rc) {
+      const long long total = static_cast<long long>(num_queries) * num_database;
+      const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 8LL * ctx->num_sms));
+      dot_to_distance_kernel<<<blocks, 256, 0, ctx->stream>>>(out, qn, dn, num_queries, num_database, distance_type);  // GRILLY_DIST_* == gb::DIST_*
+      ctx->launches++;
+      if (cudaGetLastError() != cudaSuccess) rc = set_error(ctx, GRILLY_ERR_CUDA, "faiss_distances: launch failed");
+    }
   }
   if (qs) cudaFreeAsync(qs, ctx->stream);
   if (ds) cudaFreeAsync(ds, ctx->stream);

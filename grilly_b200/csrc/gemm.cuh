@@ -8,7 +8,7 @@
 //
 // One CTA per SM walks output tiles of 128 x BN. Warp 0 feeds a ring of shared
 // memory stages with TMA, warp 1 issues tcgen05.mma into one of two TMEM
-// accumulators, warps 2..9 drain the other accumulator (tcgen05.ld), apply the
+// accumulators, warps 2..17 drain the other accumulator (tcgen05.ld), apply the
 // fused epilogue and store. Element type is fp32 consumed as tf32
 // (kind::tf32) or bf16 (kind::f16); accumulation is always fp32.
 #pragma once
@@ -54,13 +54,6 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
-// Distance epilogue: the accumulator is a dot product, a2 and b2 are the squared norms of the two vectors.
-__device__ __forceinline__ float dist_from_dot(int mode, float acc, float a2, float b2) {
-  if (mode == DIST_L2) return sqrtf(fmaxf(a2 + b2 - 2.f * acc, 0.f));
-  if (mode == DIST_COSINE) return 1.f - acc / (sqrtf(a2) * sqrtf(b2) + 1e-8f);
-  return -acc;
-}
-
 struct EpiFlags {
   bool vec_ok, vec8_ok, res_vec_ok, bias_vec_ok;
 };
@@ -72,12 +65,6 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-  if (args.dist_mode) {
-    const float a2 = args.row_vec ? __ldg(args.row_vec + row) : 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < args.N) v[j] = dist_from_dot(args.dist_mode, v[j], a2, args.col_vec ? __ldg(args.col_vec + col0 + j) : 0.f);
-  }
   if (col0 + 32 <= args.N) {
     // ---------------- fast path: the whole 32-column chunk is inside the matrix
     if (args.row_rstd) {
@@ -273,8 +260,7 @@ __device__ __forceinline__ void epilogue_swapped_fast(const GemmArgs& args, cons
 __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, const uint32_t (&r)[32], int f, int t0) {
   const bool f_ok = f < args.N;
   const bool full = t0 + 32 <= args.M;
-  if (full && f_ok && !args.out_bf16 && !args.row_rstd && !args.swiglu_pairs && !args.dist_mode &&
-      !(args.residual && args.residual_bf16)) {
+  if (full && f_ok && !args.out_bf16 && !args.row_rstd && !args.swiglu_pairs && !(args.residual && args.residual_bf16)) {
     const float b = args.bias ? __ldg(args.bias + f) : 0.f;
     if (args.residual) {
       switch (args.act) {
@@ -294,12 +280,6 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-  if (args.dist_mode) {
-    const float b2 = (args.col_vec && f_ok) ? __ldg(args.col_vec + f) : 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (full || t0 + j < args.M) v[j] = dist_from_dot(args.dist_mode, v[j], args.row_vec ? __ldg(args.row_vec + t0 + j) : 0.f, b2);
-  }
   if (args.row_rstd) {
     const float cs = (args.row_mean && f_ok) ? __ldg(args.col_sum + f) : 0.f;
 #pragma unroll
@@ -392,14 +372,27 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
 // co-running tiles (one per SM) should be roughly square in loaded rows, or a large problem re-reads one operand
 // from DRAM once per row of tiles. `fast` blocks are walked in groups of `group`: inside a group the fast index
 // varies first, then the slow one; with group >= num_fast this is plain fast-major order.
-__device__ __forceinline__ void tile_coords(int tile, int num_fast, int num_slow, int group, int& fast, int& slow) {
+// Out of line on purpose: inlined, the compiler hoists the division set-up out of the persistent loops and keeps it
+// in registers next to the 64 accumulator registers of the epilogue, which then spills.
+static __device__ __noinline__ uint32_t tile_coords_packed(int tile, int num_fast, int num_slow, int group) {
   const int per_group = group * num_slow;
   const int g = tile / per_group;
   const int first = g * group;
   const int gsz = min(num_fast - first, group);
   const int r = tile - g * per_group;
-  slow = r / gsz;
-  fast = first + (r - slow * gsz);
+  const int slow = r / gsz;
+  const int fast = first + (r - slow * gsz);
+  return static_cast<uint32_t>(fast) | (static_cast<uint32_t>(slow) << 16);
+}
+__device__ __forceinline__ void tile_coords(int tile, int num_fast, int num_slow, int group, int& fast, int& slow) {
+  if (group >= num_fast) {   // one group: plain fast-major order (every launch of the encoder)
+    slow = tile / num_fast;
+    fast = tile - slow * num_fast;
+    return;
+  }
+  const uint32_t p = tile_coords_packed(tile, num_fast, num_slow, group);   // both counts are below 65536
+  fast = static_cast<int>(p & 0xffffu);
+  slow = static_cast<int>(p >> 16);
 }
 
 template <int BN>
@@ -600,17 +593,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (args.row_mean) mean = args.row_mean[row];
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#ifdef GEMM_NO_TMEM_PREFETCH
+      uint32_t ra[32];
+      __syncwarp();
+#else
       uint32_t ra[32], rb[32];
       __syncwarp();
       if (group < NCHUNK) tmem_ld_32x32(taddr_row + group * 32, ra);
+#endif
 #pragma unroll
       for (int i = 0; i < MAXIT; ++i) {
         const int c = group + i * G;           // warp-uniform
+#ifdef GEMM_NO_TMEM_PREFETCH
+        uint32_t (&cur)[32] = ra;
+        __syncwarp();
+        if (c < NCHUNK) { tmem_ld_32x32(taddr_row + c * 32, ra); tmem_ld_wait(); }
+#else
         uint32_t (&cur)[32] = (i & 1) ? rb : ra;
         uint32_t (&nxt)[32] = (i & 1) ? ra : rb;
         __syncwarp();                          // tcgen05.ld / wait are warp-collective: reconverge first
         if (c < NCHUNK) tmem_ld_wait();
         if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
+#endif
         const int col0 = n_blk * BN + c * 32;
 #ifdef GEMM_EXPERIMENT_NOEPI
         if (c < NCHUNK && col0 < 0) epilogue_chunk_swapped(args, cur, row, col0);  // timing experiment: drain only
