@@ -593,28 +593,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (args.row_mean) mean = args.row_mean[row];
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-#ifdef GEMM_NO_TMEM_PREFETCH
-      uint32_t ra[32];
-      __syncwarp();
-#else
       uint32_t ra[32], rb[32];
       __syncwarp();
       if (group < NCHUNK) tmem_ld_32x32(taddr_row + group * 32, ra);
-#endif
 #pragma unroll
       for (int i = 0; i < MAXIT; ++i) {
         const int c = group + i * G;           // warp-uniform
-#ifdef GEMM_NO_TMEM_PREFETCH
-        uint32_t (&cur)[32] = ra;
-        __syncwarp();
-        if (c < NCHUNK) { tmem_ld_32x32(taddr_row + c * 32, ra); tmem_ld_wait(); }
-#else
         uint32_t (&cur)[32] = (i & 1) ? rb : ra;
         uint32_t (&nxt)[32] = (i & 1) ? ra : rb;
         __syncwarp();                          // tcgen05.ld / wait are warp-collective: reconverge first
         if (c < NCHUNK) tmem_ld_wait();
         if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
-#endif
         const int col0 = n_blk * BN + c * 32;
 #ifdef GEMM_EXPERIMENT_NOEPI
         if (c < NCHUNK && col0 < 0) epilogue_chunk_swapped(args, cur, row, col0);  // timing experiment: drain only

@@ -198,28 +198,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       tc_fence_after();
       const int feat = m_blk * Cfg::TILE + static_cast<int>(rank) * 128 + quad * 32 + lane;
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * Cfg::TILE;
-#ifdef GEMM_NO_TMEM_PREFETCH
-      uint32_t ra[32];
-      __syncwarp();
-#else
       uint32_t ra[32], rb[32];
       __syncwarp();
       if (group < NCHUNK) tmem_ld_32x32(taddr_row + group * 32, ra);
-#endif
 #pragma unroll
       for (int i = 0; i < MAXIT; ++i) {
         const int c = group + i * G;
-#ifdef GEMM_NO_TMEM_PREFETCH
-        uint32_t (&cur)[32] = ra;
-        __syncwarp();
-        if (c < NCHUNK) { tmem_ld_32x32(taddr_row + c * 32, ra); tmem_ld_wait(); }
-#else
         uint32_t (&cur)[32] = (i & 1) ? rb : ra;
         uint32_t (&nxt)[32] = (i & 1) ? ra : rb;
         __syncwarp();
         if (c < NCHUNK) tmem_ld_wait();
         if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
-#endif
         const int tok0 = n_blk * Cfg::TILE + c * 32;
 #ifdef GEMM_EXPERIMENT_NOEPI
         if (c < NCHUNK && tok0 < 0) epilogue_chunk_swapped(args, cur, feat, tok0);  // timing experiment: drain only
