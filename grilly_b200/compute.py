@@ -124,6 +124,14 @@ class FNN(_Namespace):
     def fused_swiglu(self, x, w_gate, w_up, b_gate=None, b_up=None):
         """(x Wg^T + bg) * silu(x Wu^T + bu) as ONE GEMM over row-interleaved [g0,u0,g1,u1,...] weights with a
         pairwise epilogue: backend/_glu_append.py:47-60, fused-swiglu.glsl:48-79."""
+        return self._fused_glu(x, w_gate, w_up, b_gate, b_up, L.ACT_NONE, "swiglu")
+
+    def fused_geglu(self, x, w_gate, w_up, b_gate=None, b_up=None):
+        """(x Wg^T + bg) * gelu(x Wu^T + bu), tanh GELU, same single GEMM: backend/_glu_append.py:224-262,
+        fused-geglu.glsl:53-84."""
+        return self._fused_glu(x, w_gate, w_up, b_gate, b_up, L.ACT_GELU, "geglu")
+
+    def _fused_glu(self, x, w_gate, w_up, b_gate, b_up, act, name):
         if tuple(w_gate.shape) != tuple(w_up.shape):
             raise ValueError("gate and up weights must have the same shape")
         n = int(w_gate.shape[0])
@@ -139,8 +147,8 @@ class FNN(_Namespace):
         if b_gate is not None and b_up is not None:
             bias = np.empty(2 * n, dtype=np.float32)
             bias[0::2], bias[1::2] = np.asarray(b_gate, np.float32), np.asarray(b_up, np.float32)
-        tag = f"|swiglu{np.asarray(w_up).__array_interface__['data'][0]}"
-        return self._linear(x, w_gate, bias, L.ACT_NONE, flags=L.FLAG_SWIGLU_PAIRS, w_tag=tag, w_transform=interleave,
+        tag = f"|{name}{np.asarray(w_up).__array_interface__['data'][0]}"
+        return self._linear(x, w_gate, bias, act, flags=L.FLAG_SWIGLU_PAIRS, w_tag=tag, w_transform=interleave,
                             n_out=n)
 
     def fused_layernorm_linear(self, x, gamma, beta, weights, bias=None, eps=1e-5, mode="layer"):
@@ -205,6 +213,23 @@ class FNN(_Namespace):
     gemm_mnk = gemm
 
     # ---- normalisation ----------------------------------------------------------------------
+    def linear_backward(self, grad_output, x, weights, bias=None):
+        """(grad_input, grad_weight, grad_bias) of y = x W^T + b as three products on the tensor cores, the way the
+        reference's GEMM branch does it (backend/fnn.py:1501-1573): grad_output @ W, grad_output^T @ x, and the
+        column sums of grad_output as ones(1, rows) @ grad_output. grad_bias is None when there is no bias."""
+        go = np.asarray(grad_output, dtype=np.float32)
+        xs = np.asarray(x, dtype=np.float32)
+        w = np.asarray(weights, dtype=np.float32)
+        if go.ndim not in (2, 3) or xs.ndim != go.ndim or go.shape[:-1] != xs.shape[:-1]:
+            raise ValueError("grad_output (.., out) and x (.., in) must be 2-D or 3-D with the same leading shape")
+        if w.shape != (go.shape[-1], xs.shape[-1]):
+            raise ValueError(f"weights must have shape {(go.shape[-1], xs.shape[-1])}")
+        go2, x2 = go.reshape(-1, go.shape[-1]), xs.reshape(-1, xs.shape[-1])
+        grad_input = self.gemm(go2, w).reshape(xs.shape)
+        grad_weight = self.gemm(np.ascontiguousarray(go2.T), x2)
+        grad_bias = self.gemm(np.ones((1, go2.shape[0]), np.float32), go2).reshape(-1) if bias is not None else None
+        return grad_input, grad_weight, grad_bias
+
     def _norm(self, x, gamma, beta, eps, mode, residual=None):
         x_shape = tuple(x.shape)
         F = int(x_shape[-1])

@@ -54,6 +54,11 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+// gate * act(up) of the pair epilogue: SiLU (SwiGLU) unless the launch asks for GELU (GeGLU)
+__device__ __forceinline__ float glu_pair(float gate, float up, int act) {
+  return gate * (act == ACT_GELU_TANH ? act_gelu_tanh(up) : act_silu(up));
+}
+
 struct EpiFlags {
   bool vec_ok, vec8_ok, res_vec_ok, bias_vec_ok;
 };
@@ -92,7 +97,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
       float o[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        o[j] = v[2 * j] * act_silu(v[2 * j + 1]);
+        o[j] = glu_pair(v[2 * j], v[2 * j + 1], args.act);
         if (args.round_tf32) o[j] = round_to_tf32(o[j]);
       }
       const long long idx = static_cast<long long>(row) * args.ld_out + (col0 >> 1);
@@ -196,7 +201,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
     for (int j = 0; j < 32; j += 2) {
       const int col = col0 + j;
       if (col + 1 < args.N) {
-        float o = v[j] * act_silu(v[j + 1]);
+        float o = glu_pair(v[j], v[j + 1], args.act);
         if (args.round_tf32) o = round_to_tf32(o);
         const long long idx = static_cast<long long>(row) * args.ld_out + (col >> 1);
         if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(o);
@@ -303,7 +308,7 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
     for (int j = 0; j < 32; ++j) {
       const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
       if (writer && (full || t0 + j < args.M)) {
-        float o = v[j] * act_silu(up);
+        float o = glu_pair(v[j], up, args.act);
         if (args.round_tf32) o = round_to_tf32(o);
         const long long idx = static_cast<long long>(t0 + j) * args.ld_out + (f >> 1);
         if (args.out_bf16) reinterpret_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16(o);

@@ -44,7 +44,8 @@ enum { GRILLY_DIST_L2 = 1, GRILLY_DIST_COSINE = 2, GRILLY_DIST_DOT = 3 };  /* fa
 enum {
   GRILLY_FLAG_OUT_BF16 = 1,     /* store the result as bf16 instead of fp32 */
   GRILLY_FLAG_ROUND_TF32 = 2,   /* round fp32 results to the nearest tf32 value (they feed a tf32 GEMM next) */
-  GRILLY_FLAG_SWIGLU_PAIRS = 4  /* weight rows interleaved (gate_j, up_j): y[:, j] = gate_j * silu(up_j), N/2 columns out */
+  GRILLY_FLAG_SWIGLU_PAIRS = 4  /* weight rows interleaved (gate_j, up_j): y[:, j] = gate_j * silu(up_j), N/2 columns out;
+                                   with act = GRILLY_ACT_GELU the gate is gate_j * gelu(up_j) (GeGLU) */
 };
 
 /* ---- context, replaces VulkanCore (backend/core.py:14-439) ------------------------------- */
@@ -102,7 +103,8 @@ int grilly_cast_bf16_to_f32(grilly_ctx* ctx, const void* x_dev, float* y_dev, lo
 /* y[M,N] = act(x[M,K] * W[N,K]^T + bias) (+ residual).  W is (out, in) row-major.
  * VulkanFNN.linear backend/fnn.py:1394-1496 (shader fnn-linear.glsl:33-58);
  * fused_linear_gelu/relu/silu backend/fnn.py:2022-2303 (fused-linear-{gelu,relu,silu}.glsl);
- * GRILLY_FLAG_SWIGLU_PAIRS: fused-swiglu.glsl:48-79, backend/_glu_append.py:47-60.
+ * GRILLY_FLAG_SWIGLU_PAIRS: fused-swiglu.glsl:48-79, backend/_glu_append.py:47-60; with GRILLY_ACT_GELU
+ * fused-geglu.glsl:53-84, backend/_glu_append.py:224-262.
  * x and W are fp32 (precision TF32) or bf16 (precision BF16); bias and residual are fp32. */
 int grilly_linear(grilly_ctx* ctx, const void* x_dev, const void* w_dev, const float* bias_dev,
                   const float* residual_dev, void* y_dev, int M, int N, int K, int act, int precision, int flags);

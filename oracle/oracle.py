@@ -128,6 +128,22 @@ def fused_swiglu(x, w_gate, w_up, b_gate=None, b_up=None):
     return (g * (u / (1.0 + np.exp(-u)))).astype(F32)
 
 
+def fused_geglu(x, w_gate, w_up, b_gate=None, b_up=None):
+    """(x Wg^T + bg) * gelu_tanh(x Wu^T + bu): backend/_glu_append.py:224-262 (CPU branch :256-267)."""
+    g = linear(x, w_gate, b_gate).astype(np.float64)
+    u = linear(x, w_up, b_up).astype(np.float64)
+    return (g * (0.5 * u * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (u + 0.044715 * u ** 3))))).astype(F32)
+
+
+def linear_backward(grad_output, x, weights, bias=None):
+    """(grad_input, grad_weight, grad_bias) of y = x W^T + b: backend/fnn.py:1501-1587 (grad_output @ W,
+    grad_output^T @ x, column sums; grad_bias is None without a bias)."""
+    go = np.asarray(grad_output, np.float64)
+    go2, x2 = go.reshape(-1, go.shape[-1]), np.asarray(x, np.float64).reshape(-1, np.shape(x)[-1])
+    gi = (go2 @ np.asarray(weights, np.float64)).reshape(go.shape[:-1] + (np.shape(weights)[1],))
+    return gi.astype(F32), (go2.T @ x2).astype(F32), (go2.sum(0).astype(F32) if bias is not None else None)
+
+
 def residual(a, b):
     """a + b: fnn-residual.glsl:25-34."""
     return (np.asarray(a, dtype=F32) + np.asarray(b, dtype=F32)).astype(F32)

@@ -70,3 +70,10 @@ def faiss_search():
     dist[3, 100:140] = dist[3].min() - 1.0      # forty equal smallest values: more ties than k
     dist[5, ::7] = np.round(dist[5, ::7], 1)    # scattered exact ties
     return dict(queries=queries, database=database, dist=dist, k=20)
+
+
+def linear_backward():
+    """Gradients of a (3, 40, 96) -> 160 linear layer, seed 11 (3-D input as the encoder passes it)."""
+    rng = np.random.default_rng(11)
+    return dict(grad_out=rng.standard_normal((3, 40, 160)).astype(f32), x=rng.standard_normal((3, 40, 96)).astype(f32),
+                w=(rng.standard_normal((160, 96)) / 10).astype(f32), bias=np.zeros(160, f32))

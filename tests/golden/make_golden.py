@@ -1,9 +1,9 @@
-"""Generates tests/golden/hotpath_golden.npz and faiss_golden.npz by running the REFERENCE's own CPU code paths.
+"""Generates tests/golden/hotpath_golden.npz and extras_golden.npz by running the REFERENCE's own CPU code paths.
 
 Run where the reference source tree is available:
 
     python tests/golden/make_golden.py /path/to/grilly-source            # both files
-    python tests/golden/make_golden.py /path/to/grilly-source --faiss-only
+    python tests/golden/make_golden.py /path/to/grilly-source --extras-only
 
 The reference is imported as the package ``grilly`` through a temporary symlink (its tree is not copied),
 Vulkan is absent so every op takes its numba/NumPy branch. Inputs come from the seeded generators in
@@ -23,7 +23,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parent))
 import cases  # noqa: E402
 
 OUT = Path(__file__).resolve().parent / "hotpath_golden.npz"
-OUT_FAISS = Path(__file__).resolve().parent / "faiss_golden.npz"
+OUT_EXTRAS = Path(__file__).resolve().parent / "extras_golden.npz"
 
 
 def import_reference(src: str):
@@ -116,7 +116,7 @@ def main(src: str) -> None:
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 
 
-def main_faiss(src: str) -> None:
+def main_extras(src: str) -> None:
     """Top-k through the reference's own CPU selection (backend/faiss.py:106-118; ``topk`` takes it when there is no
     Vulkan device). ``compute_distances`` has no CPU branch in the reference, so no distance matrix is stored."""
     import_reference(src)
@@ -124,15 +124,20 @@ def main_faiss(src: str) -> None:
     c = cases.faiss_search()
     idx, val = VulkanFAISS(None, None).topk(c["dist"], c["k"])
     g = {"topk_idx": np.asarray(idx, np.uint32), "topk_val": np.asarray(val, np.float32)}
-    np.savez_compressed(OUT_FAISS, **g)
-    print(f"wrote {OUT_FAISS} ({OUT_FAISS.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
+    # linear_backward through the reference's CPU branch (backend/fnn.py:1575-1587; no shaders registered)
+    from grilly.backend.fnn import VulkanFNN
+    b = cases.linear_backward()
+    gi, gw, gb = VulkanFNN(None, None, {}).linear_backward(b["grad_out"], b["x"], b["w"], b["bias"])
+    g.update(lb_grad_input=np.asarray(gi, np.float32), lb_grad_weight=np.asarray(gw, np.float32), lb_grad_bias=np.asarray(gb, np.float32))
+    np.savez_compressed(OUT_EXTRAS, **g)
+    print(f"wrote {OUT_EXTRAS} ({OUT_EXTRAS.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 
 
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     src = args[0] if args else "/root/reference"
-    if "--faiss-only" in sys.argv:
-        main_faiss(src)
+    if "--extras-only" in sys.argv:
+        main_extras(src)
     else:
         main(src)
-        main_faiss(src)
+        main_extras(src)

@@ -58,7 +58,7 @@ def test_identical_vectors_and_unknown_type(backend):
 
 
 def test_topk_against_reference_outputs(backend):
-    ref = dict(np.load(ROOT / "tests" / "golden" / "faiss_golden.npz"))
+    ref = dict(np.load(ROOT / "tests" / "golden" / "extras_golden.npz"))
     c = cases.faiss_search()
     idx, val = backend.faiss_topk(c["dist"], c["k"])
     assert idx.shape == (10, 20) and idx.dtype == np.uint32 and val.dtype == np.float32

@@ -147,6 +147,45 @@ def test_fused_swiglu(backend):
     assert O.rel_l2(backend.fnn.fused_swiglu(x, wg, wu, bg, bu), O.fused_swiglu(x, wg, wu, bg, bu)) < TOL_TF32
 
 
+@pytest.mark.parametrize("rows", [200, 2048])
+def test_fused_geglu(backend, backend_bf16, rows):
+    """gate * gelu(up) through the same pair epilogue (fused-geglu.glsl:53-84, backend/_glu_append.py:224-262);
+    2048 rows take the CTA-pair kernel, 200 the single-CTA one."""
+    rng = np.random.default_rng(19)
+    x = rng.standard_normal((rows, 256)).astype(np.float32)
+    wg, wu = ((rng.standard_normal((384, 256)) / 16).astype(np.float32) for _ in range(2))
+    bg, bu = rng.standard_normal(384).astype(np.float32), rng.standard_normal(384).astype(np.float32)
+    out = backend.fnn.fused_geglu(x, wg, wu)
+    assert out.shape == (rows, 384)
+    assert O.rel_l2(out, O.fused_geglu(x, wg, wu)) < TOL_TF32
+    assert O.rel_l2(backend.fnn.fused_geglu(x, wg, wu, bg, bu), O.fused_geglu(x, wg, wu, bg, bu)) < TOL_TF32
+    assert O.rel_l2(backend_bf16.fnn.fused_geglu(x, wg, wu, bg, bu), O.fused_geglu(x, wg, wu, bg, bu)) < TOL_BF16
+    # the SiLU gate is a different function: the two entry points must not be mixed up
+    assert O.rel_l2(out, O.fused_swiglu(x, wg, wu)) > 0.05
+
+
+def test_linear_backward(backend):
+    """The three products of the backward pass (backend/fnn.py:1501-1573) against the reference's CPU outputs."""
+    from pathlib import Path
+    ref = dict(np.load(Path(__file__).resolve().parent / "golden" / "extras_golden.npz"))
+    c = cases.linear_backward()
+    gi, gw, gb = backend.fnn.linear_backward(c["grad_out"], c["x"], c["w"], c["bias"])
+    assert gi.shape == (3, 40, 96) and gw.shape == (160, 96) and gb.shape == (160,)
+    assert O.rel_l2(gi, ref["lb_grad_input"]) < TOL_TF32
+    assert O.rel_l2(gw, ref["lb_grad_weight"]) < TOL_TF32
+    assert O.rel_l2(gb, ref["lb_grad_bias"]) < TOL_TF32
+    assert backend.fnn.linear_backward(c["grad_out"], c["x"], c["w"])[2] is None
+    # a training-sized case (4096 tokens, 384 -> 1536) against the oracle
+    rng = np.random.default_rng(12)
+    go, x = rng.standard_normal((4096, 1536)).astype(np.float32), rng.standard_normal((4096, 384)).astype(np.float32)
+    w = (rng.standard_normal((1536, 384)) / 20).astype(np.float32)
+    got, want = backend.fnn.linear_backward(go, x, w, np.zeros(1536, np.float32)), O.linear_backward(go, x, w, np.zeros(1536))
+    for a, b in zip(got, want):
+        assert O.rel_l2(a, b) < TOL_TF32
+    with pytest.raises(ValueError):
+        backend.fnn.linear_backward(go, x[:-1], w)
+
+
 def test_gemm_mnk_golden_and_sweep(backend, golden):
     r = cases.rowops()
     assert O.rel_l2(backend.fnn.gemm(r["gemm_a"], r["gemm_b"]), golden["gemm_c"]) < TOL_TF32
