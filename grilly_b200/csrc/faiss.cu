@@ -9,8 +9,8 @@
 // the dropped lo.lo term (2^-22 relative). The squared norms the L2 and cosine forms need are taken from the
 // unsplit fp32 values by the same kernel that writes the split rows.
 //
-// Top-k is exact: a radix select over order-preserving 32-bit keys finds the k-th smallest distance of a row in four
-// histogram passes, one more pass collects everything below it and, in index order, as many ties as are still
+// Top-k is exact: a radix select over order-preserving 32-bit keys finds the k-th smallest distance of a row (or of a
+// segment of a long row, when there are few rows) in four histogram passes, one more pass collects everything below it and, in index order, as many ties as are still
 // needed, and a bitonic sort in shared memory puts the k results in ascending (distance, index) order.
 #include "gemm.cuh"  // round_to_tf32, GemmArgs
 #include "internal.h"
@@ -69,15 +69,23 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 constexpr int TOPK_THREADS = 256;
 constexpr int TOPK_MAX_K = 1024;
 
-// One CTA per query row.
-__global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const float* __restrict__ dist, long long ld, int ndb, int k,
+// One CTA per (row, segment): the k smallest of vals[row][seg_begin .. seg_end) in ascending (value, position) order.
+// With segs > 1 a row is cut into equal parts and the k winners of each part are written side by side
+// (out row = row * segs + seg) for a second launch to merge; src_idx, when given, maps positions of that second
+// launch back to column indices of the original row. Every segment must hold at least k elements.
+__global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const float* __restrict__ vals, long long ld, int len, int segs,
+                                                                 int k, const uint32_t* __restrict__ src_idx,
                                                                  uint32_t* __restrict__ idx_out, float* __restrict__ val_out) {
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need, s_count, s_ties;
   __shared__ uint32_t warp_tot[TOPK_THREADS / 32];
   __shared__ uint32_t cand_key[TOPK_MAX_K];
   __shared__ uint32_t cand_idx[TOPK_MAX_K];
-  const float* row = dist + static_cast<long long>(blockIdx.x) * ld;
+  const int row_id = blockIdx.x / segs, seg = blockIdx.x - row_id * segs;
+  const int seg_begin = static_cast<int>(static_cast<long long>(len) * seg / segs);
+  const int ndb = static_cast<int>(static_cast<long long>(len) * (seg + 1) / segs) - seg_begin;   // elements of this segment
+  const float* row = vals + static_cast<long long>(row_id) * ld + seg_begin;
+  const uint32_t* src = src_idx ? src_idx + static_cast<long long>(row_id) * ld + seg_begin : nullptr;
   const int t = threadIdx.x;
 
   // ---- radix select: after the loop s_prefix is the key of the k-th smallest element and s_need (>= 1) says how
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const float* __
   }
   for (int i = t; i < k; i += TOPK_THREADS) {
     const uint32_t id = cand_idx[i];
-    idx_out[static_cast<long long>(blockIdx.x) * k + i] = id;
+    idx_out[static_cast<long long>(blockIdx.x) * k + i] = src ? __ldg(src + id) : static_cast<uint32_t>(seg_begin) + id;
     val_out[static_cast<long long>(blockIdx.x) * k + i] = __ldg(row + id);
   }
 }
@@ -234,9 +242,38 @@ int grilly_faiss_topk(grilly_ctx* ctx, const float* distances, int num_queries, 
   if (num_queries <= 0 || num_database <= 0 || k <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_topk: sizes must be positive");
   if (k > num_database) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_topk: k exceeds the number of database vectors");
   if (k > TOPK_MAX_K) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "faiss_topk: k is limited to 1024");
-  topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(distances, num_database, num_database, k, indices_out, distances_out);
-  ctx->launches++;
-  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  // Few long rows: cut each row into segments so that the whole GPU works on them, then merge the segments' winners.
+  int segs = 1;
+  if (num_queries < 2 * ctx->num_sms && num_database >= 65536) {
+    const int want = (4 * ctx->num_sms + num_queries - 1) / num_queries;
+    const int most = num_database / std::max(k, 8192);                     // every segment keeps at least k elements
+    segs = std::max(1, std::min(want, most));
+  }
+  if (segs == 1) {
+    topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(distances, num_database, num_database, 1, k, nullptr,
+                                                                    indices_out, distances_out);
+    ctx->launches++;
+    GB_CUDA_CHECK(ctx, cudaGetLastError());
+    return GRILLY_OK;
+  }
+  const size_t cand = static_cast<size_t>(num_queries) * segs * k;
+  uint32_t* cidx = nullptr;
+  float* cval = nullptr;
+  GB_CUDA_CHECK(ctx, cudaMallocAsync(&cidx, cand * sizeof(uint32_t), ctx->stream));
+  cudaError_t e = cudaMallocAsync(&cval, cand * sizeof(float), ctx->stream);
+  if (e != cudaSuccess) {
+    cudaFreeAsync(cidx, ctx->stream);
+    cudaGetLastError();
+    return set_error(ctx, GRILLY_ERR_OOM, "faiss_topk: no memory for the per-segment candidates");
+  }
+  topk_rows_kernel<<<num_queries * segs, TOPK_THREADS, 0, ctx->stream>>>(distances, num_database, num_database, segs, k, nullptr, cidx, cval);
+  topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(cval, static_cast<long long>(segs) * k, segs * k, 1, k, cidx,
+                                                                  indices_out, distances_out);
+  ctx->launches += 2;
+  e = cudaGetLastError();
+  cudaFreeAsync(cidx, ctx->stream);
+  cudaFreeAsync(cval, ctx->stream);
+  if (e != cudaSuccess) return set_error(ctx, GRILLY_ERR_CUDA, std::string("faiss_topk: ") + cudaGetErrorString(e));
   return GRILLY_OK;
 }
 

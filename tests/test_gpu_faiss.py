@@ -68,12 +68,15 @@ def test_topk_against_reference_outputs(backend):
     assert np.array_equal(idx[3], np.arange(100, 120, dtype=np.uint32))
 
 
-@pytest.mark.parametrize("nq,ndb,k", [(1, 1, 1), (10, 1000, 20), (7, 257, 257), (3, 5000, 1024), (64, 100000, 10), (2, 33, 500)])
+@pytest.mark.parametrize("nq,ndb,k", [(1, 1, 1), (10, 1000, 20), (7, 257, 257), (3, 5000, 1024), (64, 100000, 10), (2, 33, 500),
+                                       (4, 300000, 50), (1, 1000000, 1024)])
 def test_topk_sizes(backend, nq, ndb, k):
     rng = np.random.default_rng(ndb + k)
     dist = rng.standard_normal((nq, ndb)).astype(np.float32)
     dist[0, : min(ndb, 9)] = -np.inf                                # infinities and signed zeros order like floats
     dist[-1, ndb // 2] = np.float32(-0.0)
+    if ndb >= 100000:
+        dist[-1, ::1000] = -10.0                                     # equal minima spread over the segments of a long row
     idx, val = backend.faiss.topk(dist, k)
     o_idx, o_val = O.faiss_topk(dist, k)
     assert idx.shape == (nq, min(k, ndb))
