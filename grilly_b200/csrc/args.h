@@ -60,6 +60,7 @@ struct NormArgs {
   int mode;               // NORM_LAYER: gamma (x-mean) rstd + beta (biased variance); NORM_RMS: x / sqrt(mean(x^2)+eps) gamma
   int out_bf16;
   int round_tf32;
+  int reverse;            // walk the rows from the last to the first (the rows a producer wrote last are still in L2)
 };
 
 struct EmbedArgs {

@@ -14,6 +14,7 @@
 // layers, reusing one set of activation buffers, so a chunk's activations stay
 // in the 126 MB L2 between producer and consumer kernels.
 #include "internal.h"
+#include <cstdlib>
 #include "args.h"
 #include <algorithm>
 #include <cmath>
@@ -130,6 +131,7 @@ static int enc_norm(grilly_encoder* e, const float* x, const float* g, const flo
   n.mode = NORM_LAYER;
   n.out_bf16 = (e->bf16 && !out_fp32) ? 1 : 0;
   n.round_tf32 = e->bf16 ? 0 : 1;
+  n.reverse = 1;   // the GEMM before it wrote the last rows last: start where L2 still holds them (about 4 % of this kernel)
   return launch_norm(e->ctx, n);
 }
 

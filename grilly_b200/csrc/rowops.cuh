@@ -28,8 +28,9 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const NormArgs a) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = a.F >> 2;
-  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < a.rows;
-       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+  for (long long it = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); it < a.rows;
+       it += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const long long row = a.reverse ? a.rows - 1 - it : it;
     const float4* xp = reinterpret_cast<const float4*>(a.x + row * a.F);
     const float4* rp = a.residual ? reinterpret_cast<const float4*>(a.residual + row * a.F) : nullptr;
     float4 v[VPL];
