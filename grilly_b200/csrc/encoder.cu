@@ -409,11 +409,14 @@ int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* 
   for (int b = 0; b < B && !holes; ++b) {
     int len = S;
     if (mask_host) {
+      // branch-free counts (the compiler vectorises them): the row is a prefix of ones exactly when its first
+      // `count` entries are all ones
       const float* m = mask_host + static_cast<size_t>(b) * S;
-      len = 0;
-      while (len < S && m[len] > 0.5f) ++len;
-      for (int s = len; s < S; ++s)
-        if (m[s] > 0.5f) { holes = true; break; }
+      int count = 0, head = 0;
+      for (int s = 0; s < S; ++s) count += m[s] > 0.5f ? 1 : 0;
+      for (int s = 0; s < count; ++s) head += m[s] > 0.5f ? 1 : 0;
+      holes = head != count;
+      len = count;
     }
     lengths[b] = len;
   }
