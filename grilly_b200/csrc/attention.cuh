@@ -37,8 +37,13 @@ struct AttnCfg {
   static constexpr int Q_BYTES = NCH * ATTN_CHUNK_BYTES;
   static constexpr int SMEM_BYTES = 3 * Q_BYTES + 1024 + 128;
   // TMEM columns: S (fp32 scores, overwritten in place by P in the MMA operand precision) at [0,128),
-  // O_j at [128, 128 + D). Two CTAs of 256 columns fit the SM's 512.
-  static constexpr int TMEM_COLS = 256;
+  // O_j at [128, 128 + D): 256 columns, two CTAs per SM. With bf16 and head_dim <= 64 the packed P fills only
+  // columns [0,64) of the score region, so O_j goes to [64, 64 + D) of the same region: 128 columns, and three or
+  // four CTAs share an SM (the kernel is bound by the latency of its per-tile chain, so more chains in flight pay).
+  static constexpr bool SHARE_O = kBf16 && D <= 64;
+  static constexpr int TMEM_COLS = SHARE_O ? 128 : 256;
+  static constexpr int O_COL = SHARE_O ? 64 : ATTN_TILE;
+  static constexpr int MIN_CTAS = SHARE_O ? 3 : 1;   // four would cap registers at 96 and spill (measured slower)
 };
 
 // low n bits set (n <= 0 -> none, n >= 32 -> all)
@@ -149,7 +154,7 @@ __device__ __forceinline__ void rope_row_inplace(uint8_t* tile, int r, int pos, 
 }
 
 template <int D, bool kBf16>
-__global__ void __launch_bounds__(ATTN_THREADS)
+__global__ void __launch_bounds__(ATTN_THREADS, AttnCfg<D, kBf16>::MIN_CTAS)
 flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
   using Cfg = AttnCfg<D, kBf16>;
@@ -160,7 +165,9 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   constexpr uint32_t IDESC_S = make_idesc(kBf16, 128, ATTN_TILE, false, false);  // Q (K-major) x K (K-major)
   constexpr uint32_t IDESC_O = make_idesc(kBf16, 128, D, false, true);           // P (TMEM)    x V (MN-major)
 
-  const int qtile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // causal launches start with the last query tiles: those walk the most key tiles, and the launch should end on short CTAs
+  const int qtile = args.causal ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
   int row0, L;
   if (args.cu_seqlens) {
     row0 = args.cu_seqlens[b];
@@ -189,7 +196,8 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   uint64_t* bar_o = bars + 5;     // O_j = P V complete in TMEM
   uint64_t* bar_rq = bars + 6;    // Q rotated (RoPE)
   uint64_t* bar_rk = bars + 7;    // K rotated (RoPE)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* bar_or = bars + 8;    // O_j read out of TMEM (only when it shares columns with the next S): one arrive per warp
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -199,7 +207,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
     mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
-    mbar_init(bar_rq, 4); mbar_init(bar_rk, 4);
+    mbar_init(bar_rq, 4); mbar_init(bar_rk, 4); mbar_init(bar_or, 4);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -213,7 +221,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + ATTN_TILE;
+  const uint32_t tmem_o = tmem_base + Cfg::O_COL;
 
 #define ATTN_FAIL()                                         \
   do {                                                      \
@@ -243,6 +251,10 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const int n_s = (kv_len + 31) & ~31;                             // score columns computed (multiples of 32: N = 16 mod 32 is slow)
         const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
         if (!mbar_wait(rope ? bar_rk : bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
+        if constexpr (Cfg::SHARE_O) {
+          // the scores of this step overwrite the columns that hold O of the previous step: wait until it has been read
+          if (j > 0 && !mbar_wait(bar_or, (j - 1) & 1, abort_flag)) { ATTN_FAIL(); break; }
+        }
         tc_fence_after();
         // S = Q K_j^T : D/UMMA_K k-steps of 32 B, walking the 128-B chunks
 #pragma unroll
@@ -422,6 +434,10 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         }
       }
       tc_fence_before();
+      if constexpr (Cfg::SHARE_O) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_or);
+      }
     }
 
     if (ok && qi < L && !*abort_flag) {
