@@ -4,7 +4,7 @@
 // string of dependent steps separated by tensor-core completion latencies, so one unit at a time leaves the SM
 // mostly waiting. TMEM (512 columns, allocated in powers of two) would let only two independent CTAs of
 // 128 + D columns share an SM; instead ONE persistent CTA per SM allocates all 512 columns and runs NSLOT
-// independent "slots" (three for head_dim 32), each with its own 160 threads (four softmax warps + one issuing
+// independent "slots" (three for head_dim 32 in tf32, four in bf16), each with its own 160 threads (four softmax warps + one issuing
 // warp), shared-memory tiles, barriers and TMEM columns. A slot takes the next unit from a global counter, so
 // long and short sequences balance out. With a single key tile there is no running-max rescale: row max, exp,
 // row sum, P V, divide.
@@ -23,13 +23,17 @@ struct AttnShortCfg {
   static constexpr int HPR = ROW_BYTES < 128 ? 128 / ROW_BYTES : 1;   // heads per loaded row chunk
   static constexpr int NCH = ROW_BYTES <= 128 ? 1 : ROW_BYTES / 128;
   static constexpr int TILE_BYTES = NCH * ATTN_CHUNK_BYTES;       // one of Q, K, V
-  static constexpr int SLOT_COLS = ATTN_TILE + D;                 // S/P at [0,128), O at [128,128+D) of the slot
-  static constexpr int NSLOT = 3 * SLOT_COLS <= 512 ? 3 : 2;
+  // TMEM columns of a slot: S/P at [0,128), O at [128,128+D). With bf16 and head_dim <= 64 the packed P fills only
+  // [0,64) of the score columns, so O goes to [64,64+D) of the same region, a slot is 128 columns and four fit.
+  static constexpr bool SHARE_O = kBf16 && D <= 64;
+  static constexpr int SLOT_COLS = SHARE_O ? ATTN_TILE : ATTN_TILE + D;
+  static constexpr int O_COL = SHARE_O ? 64 : ATTN_TILE;
+  static constexpr int NSLOT = SHARE_O ? 4 : (3 * SLOT_COLS <= 512 ? 3 : 2);
   static_assert(NSLOT * SLOT_COLS <= 512, "slots must fit TMEM");
   static constexpr int SLOT_THREADS = 160;
   static constexpr int THREADS = NSLOT * SLOT_THREADS;
   static constexpr int SLOT_SMEM = 3 * TILE_BYTES;                // Q, K, V of one head (or head pair)
-  static constexpr int CTRL_BYTES = 64;                           // per slot: 5 barriers, unit, key-mask words
+  static constexpr int CTRL_BYTES = 96;                           // per slot: 6 barriers, unit, key-mask words
   static constexpr int SMEM_BYTES = NSLOT * SLOT_SMEM + 1024 + NSLOT * CTRL_BYTES + 64;
   static constexpr int TMEM_COLS = 512;
 };
@@ -67,13 +71,15 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   uint64_t* bar_s = bar_qk + 2;                             // S complete
   uint64_t* bar_p = bar_qk + 3;                             // P written (one arrive per softmax warp)
   uint64_t* bar_o = bar_qk + 4;                             // O complete
-  volatile int* slot_unit = reinterpret_cast<volatile int*>(ctrl + 40);
-  uint32_t* s_keep = reinterpret_cast<uint32_t*>(ctrl + 48);   // [4] key-mask bit words of the slot's sequence
+  uint64_t* bar_or = bar_qk + 5;                            // O read out of TMEM (only when it shares columns with the next S)
+  volatile int* slot_unit = reinterpret_cast<volatile int*>(ctrl + 48);
+  uint32_t* s_keep = reinterpret_cast<uint32_t*>(ctrl + 64);   // [4] key-mask bit words of the slot's sequence
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + Cfg::NSLOT * (Cfg::SLOT_SMEM + Cfg::CTRL_BYTES));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   if (t == 0) {
     mbar_init(bar_qk, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
+    mbar_init(bar_or, 4);
     if (slot == 0) {
       *abort_flag = 0;
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
@@ -89,7 +95,7 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_s = tmem_base + slot * Cfg::SLOT_COLS;
-  const uint32_t tmem_o = tmem_s + ATTN_TILE;
+  const uint32_t tmem_o = tmem_s + Cfg::O_COL;
 
 #define ATTN_FAIL()                                         \
   do {                                                      \
@@ -155,6 +161,10 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           const int u = (h - h_begin) % HPR;                 // position of this head inside its loaded group
           const bool group_ends = u == HPR - 1 || h + 1 == h_end;
           if (u == 0 && !mbar_wait(bar_qk, groups_done & 1u, abort_flag)) { ATTN_FAIL(); break; }
+          if constexpr (Cfg::SHARE_O) {
+            // these scores overwrite the columns that hold O of the slot's previous head: wait until it has been read
+            if (heads_done > 0 && !mbar_wait(bar_or, (heads_done - 1) & 1u, abort_flag)) { ATTN_FAIL(); break; }
+          }
           tc_fence_after();
           const uint32_t sQ = smem_u32(tiles) + u * Cfg::ROW_BYTES, sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
 #pragma unroll
@@ -324,6 +334,10 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           }
         }
         tc_fence_before();   // O and P of this head are consumed before the next head's MMAs may overwrite them
+        if constexpr (Cfg::SHARE_O) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_or);
+        }
         ++heads_done;
       }
     }
