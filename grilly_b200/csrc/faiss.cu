@@ -1,17 +1,18 @@
 // Vector search on top of the GEMM: pairwise distances (reference backend/faiss.py:25-104, shader
 // faiss-distance.glsl:29-83) and top-k selection per query (backend/faiss.py:106-195, shader faiss-topk.glsl).
 //
-// Distances are one tcgen05 GEMM over split operands plus one elementwise pass that turns dot products into distances
-// (kept out of the GEMM's epilogue: that code is shared with the encoder's launches and is register-critical). A single tf32 pass is 5e-4 off per
-// dot product, which reorders near neighbours, so every vector x is written as hi + lo (hi = x rounded to tf32,
-// lo = (x - hi) rounded to tf32) and the GEMM runs over K' = 3 dim with rows [hi | lo | hi] for the queries and
-// [hi | hi | lo] for the database: hi.hi + lo.hi + hi.lo in one fp32 accumulator, i.e. the fp32 dot product up to
-// the dropped lo.lo term (2^-22 relative). The squared norms the L2 and cosine forms need are taken from the
-// unsplit fp32 values by the same kernel that writes the split rows.
+// Distances are one tcgen05 GEMM over split operands plus one elementwise pass that turns dot products into
+// distances (kept out of the GEMM's epilogue: that code is shared with the encoder's launches and is
+// register-critical). A single tf32 pass is 5e-4 off per dot product, which reorders near neighbours, so every
+// vector x is written as hi + lo (hi = x rounded to tf32, lo = (x - hi) rounded to tf32) and the GEMM runs over
+// K' = 3 dim with rows [hi | lo | hi] for the queries and [hi | hi | lo] for the database: hi.hi + lo.hi + hi.lo in
+// one fp32 accumulator, i.e. the fp32 dot product up to the dropped lo.lo term (2^-22 relative). The squared norms
+// the L2 and cosine forms need are taken from the unsplit fp32 values by the kernel that writes the split rows.
 //
-// Top-k is exact: a radix select over order-preserving 32-bit keys finds the k-th smallest distance of a row (or of a
-// segment of a long row, when there are few rows) in four histogram passes, one more pass collects everything below it and, in index order, as many ties as are still
-// needed, and a bitonic sort in shared memory puts the k results in ascending (distance, index) order.
+// Top-k is exact: a radix select over order-preserving 32-bit keys finds the k-th smallest distance of a row (or of
+// a segment of a long row, when there are few rows) in four histogram passes, one more pass collects everything
+// below it and, in index order, as many ties as are still needed, and a bitonic sort in shared memory puts the k
+// results in ascending (distance, index) order.
 #include "gemm.cuh"  // round_to_tf32, GemmArgs
 #include "internal.h"
 #include <algorithm>
