@@ -419,18 +419,15 @@ int grilly_flash_attention(grilly_ctx* ctx, const void* q, const void* k, const 
   }
   const bool bf16 = precision == GRILLY_PREC_BF16;
   if (rope_style != GRILLY_ROPE_NONE && S > 2 * 128) {
-    // Long sequences: every 128-query CTA would rotate all of its key tiles again. Rotate Q and K once into
-    // pool scratch instead and run the kernel without RoPE (short sequences keep the rotation on the tile load).
+    // Long sequences: every 128-query CTA would rotate all of its key tiles again. Rotate K once into pool scratch
+    // instead; Q is still rotated in shared memory by the CTA that loads it (once per tile either way).
     const size_t bytes = static_cast<size_t>(total_rows) * H * D * (bf16 ? 2 : 4);
-    void *qr = nullptr, *kr = nullptr;
-    GB_CUDA_CHECK(ctx, cudaMallocAsync(&qr, bytes, ctx->stream));
+    void* kr = nullptr;
     cudaError_t e2 = cudaMallocAsync(&kr, bytes, ctx->stream);
-    if (e2 != cudaSuccess) { cudaFreeAsync(qr, ctx->stream); cudaGetLastError(); return set_error(ctx, GRILLY_ERR_OOM, "flash_attention: no memory for the rotated Q/K copies"); }
-    rc = launch_rope_rows(ctx, bf16, q, qr, total_rows, ld_qkv, H, D, S, cu_seqlens, B, a.rope_cos, a.rope_sin, rope_style);
-    if (!rc) rc = launch_rope_rows(ctx, bf16, k, kr, total_rows, ld_qkv, H, D, S, cu_seqlens, B, a.rope_cos, a.rope_sin, rope_style);
-    a.rope_style = ROPE_NONE;
-    if (!rc) rc = launch_attention(ctx, bf16, qr, kr, v, static_cast<long long>(H) * D, static_cast<long long>(H) * D, ld_qkv, total_rows, a);
-    cudaFreeAsync(qr, ctx->stream);
+    if (e2 != cudaSuccess) { cudaGetLastError(); return set_error(ctx, GRILLY_ERR_OOM, "flash_attention: no memory for the rotated K copy"); }
+    rc = launch_rope_rows(ctx, bf16, k, kr, total_rows, ld_qkv, H, D, S, cu_seqlens, B, a.rope_cos, a.rope_sin, rope_style);
+    a.rope_k_done = 1;
+    if (!rc) rc = launch_attention(ctx, bf16, q, kr, v, ld_qkv, static_cast<long long>(H) * D, ld_qkv, total_rows, a);
     cudaFreeAsync(kr, ctx->stream);
     return rc;
   }

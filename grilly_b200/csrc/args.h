@@ -44,6 +44,7 @@ struct AttnArgs {
   int rope_style;
   const float* rope_cos;   // [S][D/2] tables (position-major), or null
   const float* rope_sin;
+  int rope_k_done;         // K is already rotated (pre-pass): the kernel rotates Q only
   int* err;
 };
 

@@ -203,6 +203,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const bool rope = args.rope_style != ROPE_NONE;
+  const bool rope_k = rope && !args.rope_k_done;   // K may have been rotated by a pre-pass (long sequences)
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
@@ -250,7 +251,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const int kv_len = min(ATTN_TILE, L - j * ATTN_TILE);           // valid keys of this step
         const int n_s = (kv_len + 31) & ~31;                             // score columns computed (multiples of 32: N = 16 mod 32 is slow)
         const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
-        if (!mbar_wait(rope ? bar_rk : bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
+        if (!mbar_wait(rope_k ? bar_rk : bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
         if constexpr (Cfg::SHARE_O) {
           // the scores of this step overwrite the columns that hold O of the previous step: wait until it has been read
           if (j > 0 && !mbar_wait(bar_or, (j - 1) & 1, abort_flag)) { ATTN_FAIL(); break; }
@@ -320,7 +321,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const int k0 = j * ATTN_TILE;
       const int kv_len = min(ATTN_TILE, L - k0);
       const int nchunks = (kv_len + 31) >> 5;      // 32-key chunks that hold at least one valid key
-      if (rope) {
+      if (rope_k) {
         if (!mbar_wait(bar_k, ph, abort_flag)) { ATTN_FAIL(); break; }
         rope_row_inplace<D, kBf16>(sK, t, min(k0 + t, args.S - 1), args);
         fence_proxy_async_smem();
