@@ -83,6 +83,7 @@ SIGNATURES = {
     "grilly_encoder_keep_hidden": [_vp, _i],
     "grilly_encoder_last_hidden": [_vp, _vp, _ll, C.POINTER(_ll)],
     "grilly_encoder_destroy": [_vp],
+    "grilly_gemm_mnk_multi": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _i],
     "grilly_faiss_distances": [_vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "grilly_faiss_topk": [_vp, _vp, _i, _i, _i, _vp, _vp],
     "grilly_gemm_pick_tile": [_i, _i, _i],

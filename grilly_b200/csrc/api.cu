@@ -391,6 +391,22 @@ int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void*
   return launch_gemm(ctx, precision == GRILLY_PREC_BF16, true, a_dev, b_dev, a, 0);
 }
 
+int grilly_gemm_mnk_multi(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* const* c_ptrs, int num_outputs, int M,
+                          int K, int N, long long ld_c, int precision) {
+  CTX_GUARD(ctx);
+  int rc = check_prec(ctx, precision);
+  if (rc) return rc;
+  if (!a_dev || !b_dev || !c_ptrs || num_outputs < 1 || num_outputs > 8)
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm_mnk_multi: null operand or destination count outside [1, 8]");
+  for (int i = 0; i < num_outputs; ++i)
+    if (!c_ptrs[i]) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm_mnk_multi: null destination");
+  if (ld_c < N) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm_mnk_multi: ld_c is smaller than N");
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K;
+  a.out = c_ptrs[0]; a.ld_out = ld_c;
+  return launch_gemm_multi(ctx, precision == GRILLY_PREC_BF16, a_dev, b_dev, a, c_ptrs + 1, num_outputs - 1);
+}
+
 int grilly_flash_attention(grilly_ctx* ctx, const void* q, const void* k, const void* v, void* out, int B, int S, int H,
                            int D, long long ld_qkv, long long ld_out, const int* cu_seqlens, long long total_rows,
                            const float* key_mask, float scale, int causal, int rope_style, float rope_base,

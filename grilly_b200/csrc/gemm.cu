@@ -195,4 +195,22 @@ int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, cons
   return swap ? dispatch_bn<false, false, true>(ctx, bn, a, b, args) : dispatch_bn<false, false, false>(ctx, bn, a, b, args);
 }
 
+// gemm_mnk whose fp32 result goes to args.out and to n_extra further matrices of the same pitch (device pointers,
+// possibly peer-mapped). The list is placed in constant memory in stream order around the launch.
+int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, GemmArgs& args, void* const* extra, int n_extra) {
+  if (n_extra < 0 || n_extra > 7) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm_mnk_multi: at most 8 destinations");
+  if (n_extra > 0 && (args.N % 32 != 0 || args.out_bf16))
+    return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "gemm_mnk_multi: fp32 output and N a multiple of 32 are required");
+  GemmExtraOut h{};
+  h.n = n_extra;
+  for (int i = 0; i < n_extra; ++i) h.p[i] = extra[i];
+  if (n_extra > 0) GB_CUDA_CHECK(ctx, cudaMemcpyToSymbolAsync(g_gemm_extra_out, &h, sizeof(h), 0, cudaMemcpyHostToDevice, ctx->stream));
+  const int rc = launch_gemm(ctx, bf16, true, a, b, args, 0);
+  if (n_extra > 0) {
+    h = GemmExtraOut{};
+    GB_CUDA_CHECK(ctx, cudaMemcpyToSymbolAsync(g_gemm_extra_out, &h, sizeof(h), 0, cudaMemcpyHostToDevice, ctx->stream));
+  }
+  return rc;
+}
+
 }  // namespace gb

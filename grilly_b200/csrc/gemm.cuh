@@ -54,6 +54,16 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+// Further destinations of a gemm_mnk result (fp32, same pitch as the first output), e.g. the C matrices of the other
+// GPUs of a column-split product. They travel in constant memory, not in GemmArgs: the `linear` kernels are compiled
+// at their register limit and a larger argument struct alone made them spill. Set by the launcher in the stream
+// before the launch and cleared after it; n = 0 for every other launch.
+struct GemmExtraOut {
+  int n;
+  void* p[7];
+};
+static __constant__ GemmExtraOut g_gemm_extra_out;
+
 // gate * act(up) of the pair epilogue: SiLU (SwiGLU) unless the launch asks for GELU (GeGLU)
 __device__ __forceinline__ float glu_pair(float gate, float up, int act) {
   return gate * (act == ACT_GELU_TANH ? act_gelu_tanh(up) : act_silu(up));
@@ -180,6 +190,18 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) op[j] = v[j];
+      }
+      // plain stores of the same block to the further destinations, which may be peer-mapped memory
+      for (int e = 0; e < g_gemm_extra_out.n; ++e) {
+        void* const base = g_gemm_extra_out.p[e];
+        float* xp = reinterpret_cast<float*>(base) + static_cast<long long>(row) * args.ld_out + col0;
+        if (vec_ok && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(xp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) xp[j] = v[j];
+        }
       }
     }
     return;

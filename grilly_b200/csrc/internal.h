@@ -95,6 +95,7 @@ struct PoolArgs;
 
 // gemm.cu
 int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, const void* b, GemmArgs& args, int force_bn);
+int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, GemmArgs& args, void* const* extra, int n_extra);
 // attention.cu
 int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
                      long long ld_v, long long total_rows, AttnArgs& args);

@@ -7,7 +7,10 @@ two partitionings the path admits:
   (:func:`shard_range`, :func:`encode_sharded`);
 * one large ``gemm`` (backend/fnn.py:104-166) is split by columns of B: rank r multiplies A by its column block and
   the blocks of C are exchanged with one all-gather per slab of rows (:func:`gemm_nsplit`). The all-gather of a slab
-  runs on NCCL's stream while the next slab's GEMM runs on the compute stream.
+  runs on NCCL's stream while the next slab's GEMM runs on the compute stream;
+* the same split with the exchange inside the GEMM kernel (:func:`gemm_nsplit_fused`): C lives in symmetric memory,
+  every rank's epilogue stores its column block straight into every rank's C (plain stores to peer-mapped memory,
+  tile by tile under the main loop), and one barrier ends the step. No staging buffer, no un-permute pass.
 
 The collective layer is injected (``group``, any initialised ``torch.distributed`` backend) and so is the local
 multiply, which lets the partitioning and re-assembly logic be tested on CPU ranks over gloo; the default local
@@ -142,3 +145,65 @@ def gemm_nsplit(A, B, local=None, backend=None, group=None, slabs: int = 4, retu
         w.wait()
         out3[r0:r1].copy_(staged.view(world, r1 - r0, n_loc).permute(1, 0, 2))   # (g, rows, N/g) -> rows x N
     return out if return_tensor else local.to_numpy(out)
+
+
+class FusedNsplit:
+    """C = A @ B with B split by columns and every rank's epilogue writing its block into all ranks' C.
+
+    Set-up (once per shape): a symmetric (M, N) fp32 buffer and the peers' addresses of it. ``run()`` is then one
+    kernel launch per rank plus a barrier. Operands are uploaded by ``prepare``; A is replicated, rank r keeps
+    columns [r N/g, (r+1) N/g) of B.
+    """
+
+    def __init__(self, backend, M: int, N: int, K: int, group=None):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer mappings are all the kernel needs
+        import torch
+        import torch.distributed._symmetric_memory as symm_mem
+
+        dist = _dist()
+        self.torch, self.dist, self.group = torch, dist, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one destination per rank in the kernel's list)")
+        if N % (self.world * 32):
+            raise ValueError(f"N = {N} must be a multiple of 32 x world size ({self.world})")
+        self.backend, self.dev = backend, backend.device
+        self.M, self.N, self.K, self.n_loc = M, N, K, N // self.world
+        self.device = torch.device("cuda", self.dev.index)
+        self.dev.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        self.c = symm_mem.empty((M, N), dtype=torch.float32, device=self.device)
+        self.handle = symm_mem.rendezvous(self.c, group if group is not None else dist.group.WORLD)
+        # destination i = C of rank (rank + i) % world at this rank's column offset; the own copy first
+        col_bytes = self.rank * self.n_loc * 4
+        order = [(self.rank + i) % self.world for i in range(self.world)]
+        import ctypes as C
+        self._ptrs = (C.c_void_p * self.world)(*[int(self.handle.buffer_ptrs[r]) + col_bytes for r in order])
+
+    def prepare(self, A: np.ndarray, B_cols: np.ndarray):
+        bf16 = self.backend.precision == "bf16"
+        self.a = self.backend.to_device(np.ascontiguousarray(A, dtype=np.float32))
+        self.b = self.backend.to_device(np.ascontiguousarray(B_cols, dtype=np.float32))
+        self.prec = 1 if bf16 else 0
+
+    def run(self):
+        """One step: every rank's C holds the full product when this returns (device-side: after the barrier)."""
+        import ctypes as C
+
+        rc = self.dev.lib.grilly_gemm_mnk_multi(self.dev.ctx, C.c_void_p(self.a.ptr), C.c_void_p(self.b.ptr), self._ptrs,
+                                                self.world, self.M, self.K, self.n_loc, C.c_longlong(self.N), self.prec)
+        self.dev.check(rc)
+        self.handle.barrier()        # all ranks' stores have landed before anyone reads C
+        return self.c
+
+
+def gemm_nsplit_fused(A, B, backend, group=None, return_tensor: bool = False):
+    """C = A @ B, column-split with the exchange fused into the GEMM epilogue (see :class:`FusedNsplit`)."""
+    A, B = np.asarray(A), np.asarray(B)
+    if A.ndim != 2 or B.ndim != 2 or A.shape[1] != B.shape[0]:
+        raise AssertionError(f"K mismatch: {A.shape} @ {B.shape}")
+    op = FusedNsplit(backend, A.shape[0], B.shape[1], A.shape[1], group)
+    op.prepare(A, B[:, op.rank * op.n_loc:(op.rank + 1) * op.n_loc])
+    c = op.run()
+    return c if return_tensor else c.cpu().numpy()

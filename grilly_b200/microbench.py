@@ -50,17 +50,24 @@ def _nsplit(a):
     rng = np.random.default_rng(4)
     A = rng.standard_normal((a.m, a.k)).astype(np.float32)
     B = rng.standard_normal((a.k, a.n)).astype(np.float32)
-    local = CudaLocalGemm(backend)
     n_loc = a.n // world
-    local.prepare(A, B[:, dist.get_rank() * n_loc:(dist.get_rank() + 1) * n_loc])
+    if a.fused:
+        from .dist import FusedNsplit
+        op = FusedNsplit(backend, a.m, a.n, a.k)
+        op.prepare(A, B[:, dist.get_rank() * n_loc:(dist.get_rank() + 1) * n_loc])
+        step = op.run
+    else:
+        local = CudaLocalGemm(backend)
+        local.prepare(A, B[:, dist.get_rank() * n_loc:(dist.get_rank() + 1) * n_loc])
+        step = lambda: gemm_nsplit(A, B, local=local, return_tensor=True, prepared=True)  # noqa: E731
     for _ in range(a.warmup):
-        gemm_nsplit(A, B, local=local, return_tensor=True, prepared=True)
+        step()
     torch.cuda.synchronize()
     dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(a.reps):
-        gemm_nsplit(A, B, local=local, return_tensor=True, prepared=True)
+        step()
     e1.record()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) / a.reps], device="cuda", dtype=torch.float64)
@@ -68,8 +75,9 @@ def _nsplit(a):
     if dist.get_rank() == 0:
         ms = t.item()
         sent = (world - 1) / world * a.m * a.n * 4.0
+        how = "epilogue stores to peers" if a.fused else "all-gather"
         print(f"gemm n-split x{world} {a.m}x{a.n}x{a.k} {a.precision}: {ms * 1e3:.1f} us (max over ranks)  "
-              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s aggregate  all-gather {sent / ms / 1e6:.1f} GB/s sent per GPU")
+              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s aggregate  {how} {sent / ms / 1e6:.1f} GB/s sent per GPU")
     backend.cleanup()
     dist.destroy_process_group()
 
@@ -94,6 +102,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--fused", action="store_true", help="with --nsplit: exchange C inside the GEMM epilogue (peer stores)")
     ap.add_argument("--nsplit", action="store_true",
                     help="gemm: split B by columns over the ranks of a torch.distributed.run launch and all-gather C")
     a = ap.parse_args(argv)

@@ -226,6 +226,16 @@ int grilly_encoder_keep_hidden(grilly_encoder* enc, int on);
 int grilly_encoder_last_hidden(grilly_encoder* enc, float* out_host, long long max_rows, long long* rows);
 int grilly_encoder_destroy(grilly_encoder* enc);
 
+/* C = A B like grilly_gemm_mnk, with the fp32 result stored to num_outputs (1..8) matrices c_ptrs[i] (host array of
+ * device pointers), all with row pitch ld_c >= N elements; N must be a multiple of 32. The destinations may be
+ * peer-mapped memory of other GPUs (plain stores only): with each GPU computing one column block of a product and
+ * writing it into every GPU's C at its column offset, the exchange of a column-split GEMM happens inside the kernel,
+ * tile by tile, instead of in an all-gather after it. No counterpart in the reference, which has no multi-GPU code
+ * (CHANGELOG.md:75). One launch at a time per GPU uses this entry point (the destination list lives in constant
+ * memory of the library). Asynchronous. */
+int grilly_gemm_mnk_multi(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* const* c_ptrs, int num_outputs, int M,
+                          int K, int N, long long ld_c, int precision);
+
 /* ---- vector search over the embeddings ---------------------------------------------------------------------- */
 /* Replaces VulkanFAISS.compute_distances (backend/faiss.py:25-104; shader faiss-distance.glsl:29-83):
  * out[q][d] for queries fp32 [num_queries][dim] and database fp32 [num_database][dim], all device pointers.

@@ -1,5 +1,5 @@
-"""Two-GPU run of the sharded paths (skipped on a single-GPU box): the column-split GEMM with an NCCL all-gather and
-the batch-sharded encoder must reproduce the one-GPU results bit for bit. Ranks are child processes; NVLS is off."""
+"""Two-GPU run of the sharded paths (skipped on a single-GPU box): the column-split GEMM (with an NCCL all-gather, and with the
+exchange fused into the epilogue) and the batch-sharded encoder must reproduce the one-GPU results bit for bit. Ranks are child processes; NVLS is off."""
 import os
 import socket
 import sys
@@ -16,11 +16,12 @@ def _worker(rank, world, port, q):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"   # plain peer mappings only
     import torch
     import torch.distributed as dist
 
     import grilly_b200
-    from grilly_b200.dist import encode_sharded, gemm_nsplit
+    from grilly_b200.dist import encode_sharded, gemm_nsplit, gemm_nsplit_fused
 
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -30,6 +31,7 @@ def _worker(rank, world, port, q):
         A = rng.standard_normal((1000, 512)).astype(np.float32)
         B = rng.standard_normal((512, 1024)).astype(np.float32)
         C = gemm_nsplit(A, B, backend=backend, slabs=3)
+        Cf = gemm_nsplit_fused(A, B, backend)          # exchange inside the GEMM epilogue (stores to the peer's C)
         backend.device.set_stream(None)
         single = backend.fnn.gemm(A, B)
         ref = A.astype(np.float64) @ B.astype(np.float64)
@@ -42,7 +44,8 @@ def _worker(rank, world, port, q):
         sharded = encode_sharded(enc, ids, mask)
         whole = enc.encode_ids(ids, mask)
         enc.close()
-        q.put((rank, bool(np.array_equal(C, single)), rel < 2e-3, bool(np.array_equal(sharded, whole))))
+        q.put((rank, bool(np.array_equal(C, single)) and bool(np.array_equal(Cf, single)), rel < 2e-3,
+               bool(np.array_equal(sharded, whole))))
     finally:
         backend.cleanup()
         dist.destroy_process_group()

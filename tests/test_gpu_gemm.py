@@ -164,6 +164,29 @@ def test_fused_geglu(backend, backend_bf16, rows):
     assert O.rel_l2(out, O.fused_swiglu(x, wg, wu)) > 0.05
 
 
+def test_gemm_mnk_multi_destinations(backend, lib):
+    """One product stored to three matrices of a wider pitch at a column offset (the layout of a column-split
+    product: on several GPUs the destinations are peer-mapped, here they are local)."""
+    import ctypes as C
+    rng = np.random.default_rng(21)
+    M, K, N, ld, off = 300, 96, 128, 512, 256
+    A, B = rng.standard_normal((M, K)).astype(np.float32), rng.standard_normal((K, N)).astype(np.float32)
+    dev = backend.device
+    ad, bd = backend.to_device(A), backend.to_device(B)
+    outs = [dev.upload(np.full((M, ld), 7.0, np.float32)) for _ in range(3)]
+    ptrs = (C.c_void_p * 3)(*[o.ptr + off * 4 for o in outs])
+    dev.check(lib.grilly_gemm_mnk_multi(dev.ctx, C.c_void_p(ad.ptr), C.c_void_p(bd.ptr), ptrs, 3, M, K, N, C.c_longlong(ld), 0))
+    want = backend.fnn.gemm(A, B)
+    for o in outs:
+        got = o.numpy()
+        assert np.array_equal(got[:, off:off + N], want)                       # same kernel, same bits
+        assert np.all(got[:, :off] == 7.0) and np.all(got[:, off + N:] == 7.0)   # nothing else is touched
+    # a following plain gemm writes one destination only (the list is cleared after the launch)
+    again = backend.fnn.gemm(A, B)
+    assert np.array_equal(again, want) and np.all(outs[1].numpy()[:, :off] == 7.0)
+    assert lib.grilly_gemm_mnk_multi(dev.ctx, C.c_void_p(ad.ptr), C.c_void_p(bd.ptr), ptrs, 3, M, K, 100, C.c_longlong(ld), 0) != 0
+
+
 def test_linear_backward(backend):
     """The three products of the backward pass (backend/fnn.py:1501-1573) against the reference's CPU outputs."""
     from pathlib import Path
