@@ -69,6 +69,25 @@ def encode_sharded(encoder, input_ids, attention_mask=None, group=None, gather: 
     return np.concatenate(parts, axis=0) if parts else torch.empty(0).numpy()
 
 
+class _StreamBridge:
+    """Runs the library's launches on a torch stream of their own, ordered inside torch's current stream: the
+    launches wait for what the current stream has queued, and the current stream (hence NCCL and torch ops issued
+    after them) waits for the launches. Torch's default stream has the handle 0, which the library reads as "use
+    your own stream", so the current stream itself cannot be handed over."""
+
+    def __init__(self, dev, torch, device):
+        self.torch, self.device = torch, device
+        self.stream = torch.cuda.Stream(device=device)
+        dev.set_stream(self.stream.cuda_stream)
+
+    def __enter__(self):
+        self.stream.wait_stream(self.torch.cuda.current_stream(self.device))
+        return self
+
+    def __exit__(self, *exc):
+        self.torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+
 class CudaLocalGemm:
     """Local multiply through libgrilly_b200.so on torch-owned CUDA buffers (A and the column block of B are
     uploaded once and kept; C is written into a torch tensor so NCCL can send it without a copy)."""
@@ -80,8 +99,7 @@ class CudaLocalGemm:
         self.backend = backend
         self.dev = backend.device
         self.device = torch.device("cuda", self.dev.index)
-        # the library launches on torch's current stream so that torch and NCCL see its work in order
-        self.dev.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        self.bridge = _StreamBridge(self.dev, torch, self.device)   # torch and NCCL see the library's work in order
 
     def prepare(self, A: np.ndarray, B_cols: np.ndarray):
         bf16 = self.backend.precision == "bf16"
@@ -96,8 +114,9 @@ class CudaLocalGemm:
         """out[(r1-r0), n_loc] (torch, fp32, contiguous) = A[r0:r1] @ B_cols."""
         import ctypes as C
 
-        rc = self.dev.lib.grilly_gemm_mnk(self.dev.ctx, C.c_void_p(self.a.ptr + r0 * self.K * self.elt), C.c_void_p(self.b.ptr),
-                                          C.c_void_p(out.data_ptr()), r1 - r0, self.K, self.n_loc, self.prec, 0)
+        with self.bridge:
+            rc = self.dev.lib.grilly_gemm_mnk(self.dev.ctx, C.c_void_p(self.a.ptr + r0 * self.K * self.elt), C.c_void_p(self.b.ptr),
+                                              C.c_void_p(out.data_ptr()), r1 - r0, self.K, self.n_loc, self.prec, 0)
         self.dev.check(rc)
 
     def empty(self, *shape):
@@ -172,7 +191,7 @@ class FusedNsplit:
         self.backend, self.dev = backend, backend.device
         self.M, self.N, self.K, self.n_loc = M, N, K, N // self.world
         self.device = torch.device("cuda", self.dev.index)
-        self.dev.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        self.bridge = _StreamBridge(self.dev, torch, self.device)
         self.c = symm_mem.empty((M, N), dtype=torch.float32, device=self.device)
         self.handle = symm_mem.rendezvous(self.c, group if group is not None else dist.group.WORLD)
         # destination i = C of rank (rank + i) % world at this rank's column offset; the own copy first
@@ -187,23 +206,57 @@ class FusedNsplit:
         self.b = self.backend.to_device(np.ascontiguousarray(B_cols, dtype=np.float32))
         self.prec = 1 if bf16 else 0
 
+    def run_copy(self, slabs: int = 4):
+        """Same result with the exchange done by strided peer-to-peer copies instead of epilogue stores: the GEMM of
+        a row slab writes this rank's column block into its own C, then one copy per peer (on a side stream, rows of
+        N/g contiguous floats) puts the slab into the peer's C while the next slab's GEMM runs."""
+        import ctypes as C
+
+        torch = self.torch
+        if not hasattr(self, "_side"):
+            self._side = torch.cuda.Stream(device=self.device)
+            self._peers = {r: self.handle.get_buffer(r, (self.M, self.N), torch.float32) for r in range(self.world) if r != self.rank}
+        self.handle.barrier()
+        cur = torch.cuda.current_stream(self.device)
+        c0, c1 = self.rank * self.n_loc, (self.rank + 1) * self.n_loc
+        elt = 2 if self.prec else 4
+        for s in range(slabs):
+            r0, r1 = shard_range(self.M, s, slabs)
+            with self.bridge:
+                out = self.c.data_ptr() + (r0 * self.N + c0) * 4
+                ptr = (C.c_void_p * 1)(out)
+                rc = self.dev.lib.grilly_gemm_mnk_multi(self.dev.ctx, C.c_void_p(self.a.ptr + r0 * self.K * elt), C.c_void_p(self.b.ptr),
+                                                        ptr, 1, r1 - r0, self.K, self.n_loc, C.c_longlong(self.N), self.prec)
+            self.dev.check(rc)
+            self._side.wait_stream(cur)
+            with torch.cuda.stream(self._side):
+                for peer in self._peers.values():
+                    peer[r0:r1, c0:c1].copy_(self.c[r0:r1, c0:c1])
+        cur.wait_stream(self._side)
+        self.handle.barrier()
+        return self.c
+
     def run(self):
         """One step: every rank's C holds the full product when this returns (device-side: after the barrier)."""
         import ctypes as C
 
-        rc = self.dev.lib.grilly_gemm_mnk_multi(self.dev.ctx, C.c_void_p(self.a.ptr), C.c_void_p(self.b.ptr), self._ptrs,
-                                                self.world, self.M, self.K, self.n_loc, C.c_longlong(self.N), self.prec)
+        self.handle.barrier()        # nobody still reads the C of the previous step
+        with self.bridge:
+            rc = self.dev.lib.grilly_gemm_mnk_multi(self.dev.ctx, C.c_void_p(self.a.ptr), C.c_void_p(self.b.ptr), self._ptrs,
+                                                    self.world, self.M, self.K, self.n_loc, C.c_longlong(self.N), self.prec)
         self.dev.check(rc)
         self.handle.barrier()        # all ranks' stores have landed before anyone reads C
         return self.c
 
 
-def gemm_nsplit_fused(A, B, backend, group=None, return_tensor: bool = False):
-    """C = A @ B, column-split with the exchange fused into the GEMM epilogue (see :class:`FusedNsplit`)."""
+def gemm_nsplit_fused(A, B, backend, group=None, return_tensor: bool = False, exchange: str = "stores"):
+    """C = A @ B, column-split over symmetric memory (see :class:`FusedNsplit`): ``exchange="stores"`` writes every
+    tile to all ranks from the GEMM epilogue, ``"copies"`` moves row slabs with strided peer copies under the next
+    slab's GEMM (the faster of the two on two GPUs)."""
     A, B = np.asarray(A), np.asarray(B)
     if A.ndim != 2 or B.ndim != 2 or A.shape[1] != B.shape[0]:
         raise AssertionError(f"K mismatch: {A.shape} @ {B.shape}")
     op = FusedNsplit(backend, A.shape[0], B.shape[1], A.shape[1], group)
     op.prepare(A, B[:, op.rank * op.n_loc:(op.rank + 1) * op.n_loc])
-    c = op.run()
+    c = op.run_copy() if exchange == "copies" else op.run()
     return c if return_tensor else c.cpu().numpy()

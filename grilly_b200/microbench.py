@@ -55,7 +55,7 @@ def _nsplit(a):
         from .dist import FusedNsplit
         op = FusedNsplit(backend, a.m, a.n, a.k)
         op.prepare(A, B[:, dist.get_rank() * n_loc:(dist.get_rank() + 1) * n_loc])
-        step = op.run
+        step = op.run_copy if a.p2p_copy else op.run
     else:
         local = CudaLocalGemm(backend)
         local.prepare(A, B[:, dist.get_rank() * n_loc:(dist.get_rank() + 1) * n_loc])
@@ -75,7 +75,7 @@ def _nsplit(a):
     if dist.get_rank() == 0:
         ms = t.item()
         sent = (world - 1) / world * a.m * a.n * 4.0
-        how = "epilogue stores to peers" if a.fused else "all-gather"
+        how = ("peer copies" if a.p2p_copy else "epilogue stores to peers") if a.fused else "all-gather"
         print(f"gemm n-split x{world} {a.m}x{a.n}x{a.k} {a.precision}: {ms * 1e3:.1f} us (max over ranks)  "
               f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s aggregate  {how} {sent / ms / 1e6:.1f} GB/s sent per GPU")
     backend.cleanup()
@@ -102,6 +102,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--p2p-copy", action="store_true", help="with --nsplit --fused: exchange by strided peer copies per row slab")
     ap.add_argument("--fused", action="store_true", help="with --nsplit: exchange C inside the GEMM epilogue (peer stores)")
     ap.add_argument("--nsplit", action="store_true",
                     help="gemm: split B by columns over the ranks of a torch.distributed.run launch and all-gather C")

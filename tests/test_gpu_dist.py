@@ -21,7 +21,7 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
 
     import grilly_b200
-    from grilly_b200.dist import encode_sharded, gemm_nsplit, gemm_nsplit_fused
+    from grilly_b200.dist import FusedNsplit, encode_sharded, gemm_nsplit, gemm_nsplit_fused
 
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -32,6 +32,9 @@ def _worker(rank, world, port, q):
         B = rng.standard_normal((512, 1024)).astype(np.float32)
         C = gemm_nsplit(A, B, backend=backend, slabs=3)
         Cf = gemm_nsplit_fused(A, B, backend)          # exchange inside the GEMM epilogue (stores to the peer's C)
+        op = FusedNsplit(backend, 1000, 1024, 512)
+        op.prepare(A, B[:, rank * 512:(rank + 1) * 512])
+        Cc = op.run_copy(slabs=3).cpu().numpy()        # exchange by strided peer copies per row slab
         backend.device.set_stream(None)
         single = backend.fnn.gemm(A, B)
         ref = A.astype(np.float64) @ B.astype(np.float64)
@@ -44,7 +47,7 @@ def _worker(rank, world, port, q):
         sharded = encode_sharded(enc, ids, mask)
         whole = enc.encode_ids(ids, mask)
         enc.close()
-        q.put((rank, bool(np.array_equal(C, single)) and bool(np.array_equal(Cf, single)), rel < 2e-3,
+        q.put((rank, bool(np.array_equal(C, single)) and bool(np.array_equal(Cf, single)) and bool(np.array_equal(Cc, single)), rel < 2e-3,
                bool(np.array_equal(sharded, whole))))
     finally:
         backend.cleanup()
