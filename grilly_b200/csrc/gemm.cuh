@@ -73,6 +73,36 @@ struct EpiFlags {
   bool vec_ok, vec8_ok, res_vec_ok, bias_vec_ok;
 };
 
+// gemm_mnk with several destinations (g_gemm_extra_out.n > 0): the plain fp32 product goes to args.out and to every
+// further destination. A warp holds a 32 x 32 block with one row per lane; it is transposed inside the warp (five
+// exchange stages) so that every store instruction writes 32 consecutive columns of ONE row, a full 128-byte
+// line: stores to a peer GPU then leave as whole lines instead of 16-byte pieces of 32 different rows.
+// Called by all 32 lanes of the warp, whatever their row; row0 is the first row of the warp's block.
+__device__ __forceinline__ void epilogue_chunk_multi(const GemmArgs& args, const uint32_t (&r)[32], int row0, int col0, int lane) {
+  uint32_t v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = r[j];
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if ((j & s) == 0) {
+        const uint32_t send = upper ? v[j] : v[j + s];
+        const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, s);
+        if (upper) v[j] = recv; else v[j + s] = recv;
+      }
+    }
+  }
+  // now v[i] of lane l is element (row0 + i, col0 + l)
+  for (int d = 0; d <= g_gemm_extra_out.n; ++d) {
+    float* base = reinterpret_cast<float*>(d == 0 ? args.out : g_gemm_extra_out.p[d - 1]) + col0 + lane;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (row0 + i < args.M) base[static_cast<long long>(row0 + i) * args.ld_out] = __uint_as_float(v[i]);
+  }
+}
+
 // Applies the fused epilogue to 32 consecutive accumulator columns of one row and stores them.
 __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFlags& f, const uint32_t (&r)[32], int row,
                                                int col0, float mean, float rstd) {
@@ -190,18 +220,6 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& args, const EpiFl
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) op[j] = v[j];
-      }
-      // plain stores of the same block to the further destinations, which may be peer-mapped memory
-      for (int e = 0; e < g_gemm_extra_out.n; ++e) {
-        void* const base = g_gemm_extra_out.p[e];
-        float* xp = reinterpret_cast<float*>(base) + static_cast<long long>(row) * args.ld_out + col0;
-        if (vec_ok && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(xp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) xp[j] = v[j];
-        }
       }
     }
     return;
@@ -639,7 +657,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if constexpr (kSwap) {
           if (c < NCHUNK && col0 < args.M) epilogue_chunk_swapped(args, cur, row, col0);
         } else {
-          if (c < NCHUNK && row_ok && col0 < args.N) epilogue_chunk(args, f, cur, row, col0, mean, rstd);
+          if (g_gemm_extra_out.n > 0) {   // launcher guarantees fp32 output and N a multiple of 32
+            if (c < NCHUNK && col0 < args.N) epilogue_chunk_multi(args, cur, row - lane, col0, lane);
+          } else if (c < NCHUNK && row_ok && col0 < args.N) {
+            epilogue_chunk(args, f, cur, row, col0, mean, rstd);
+          }
         }
       }
       // this warp has finished reading the accumulator

@@ -216,7 +216,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #endif
         if constexpr (kBMn) {
           // feat is the row of C, tok0 the first of 32 columns
-          if (c < NCHUNK && feat < args.M && tok0 < args.N) epilogue_chunk(args, f, cur, feat, tok0, 0.f, 1.f);
+          if (g_gemm_extra_out.n > 0) {   // launcher guarantees fp32 output and N a multiple of 32
+            if (c < NCHUNK && tok0 < args.N) epilogue_chunk_multi(args, cur, feat - lane, tok0, lane);
+          } else if (c < NCHUNK && feat < args.M && tok0 < args.N) {
+            epilogue_chunk(args, f, cur, feat, tok0, 0.f, 1.f);
+          }
         } else {
           if (c < NCHUNK && tok0 < args.M) epilogue_chunk_swapped(args, cur, feat, tok0);
         }
