@@ -251,8 +251,8 @@ class FusedNsplit:
 
 def gemm_nsplit_fused(A, B, backend, group=None, return_tensor: bool = False, exchange: str = "stores"):
     """C = A @ B, column-split over symmetric memory (see :class:`FusedNsplit`): ``exchange="stores"`` writes every
-    tile to all ranks from the GEMM epilogue, ``"copies"`` moves row slabs with strided peer copies under the next
-    slab's GEMM (the faster of the two on two GPUs)."""
+    tile to all ranks from the GEMM epilogue (whole 128-byte lines), ``"copies"`` moves row slabs with strided peer
+    copies under the next slab's GEMM. On two GPUs the first is ahead at 8192^3, the second slightly at 16384^3."""
     A, B = np.asarray(A), np.asarray(B)
     if A.ndim != 2 or B.ndim != 2 or A.shape[1] != B.shape[0]:
         raise AssertionError(f"K mismatch: {A.shape} @ {B.shape}")
