@@ -129,7 +129,8 @@ def fused_swiglu(x, w_gate, w_up, b_gate=None, b_up=None):
 
 
 def fused_geglu(x, w_gate, w_up, b_gate=None, b_up=None):
-    """(x Wg^T + bg) * gelu_tanh(x Wu^T + bu): backend/_glu_append.py:224-262 (CPU branch :256-267)."""
+    """(x Wg^T + bg) * gelu_tanh(x Wu^T + bu): backend/_glu_append.py:224-262 (CPU branch :256-267). Parity unpinned:
+    that file is a fragment no class of the reference includes, so it cannot be run to generate outputs."""
     g = linear(x, w_gate, b_gate).astype(np.float64)
     u = linear(x, w_up, b_up).astype(np.float64)
     return (g * (0.5 * u * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (u + 0.044715 * u ** 3))))).astype(F32)
@@ -305,7 +306,8 @@ def encoder_forward(ids, mask, w, num_heads, embed_eps=1e-12, layer_eps=1e-5, re
 def faiss_distances(queries, database, distance_type="cosine"):
     """Pairwise distances as the shader states them (shaders/faiss-distance.glsl:29-83; the reference has no CPU
     branch for this op): 'l2' sqrt(sum (q-d)^2), 'cosine' 1 - q.d / (sqrt(q.q) sqrt(d.d) + 1e-8), 'dot' -(q.d);
-    any other name is treated as cosine (backend/faiss.py:44-45)."""
+    any other name is treated as cosine (backend/faiss.py:44-45). Parity unpinned: there is no reference CPU code to
+    generate outputs from; checked against the closed forms of the reference's tests (tests/test_gpu_operations.py:219-241)."""
     q = np.asarray(queries, np.float64)
     if q.ndim == 1:
         q = q.reshape(1, -1)
