@@ -122,7 +122,8 @@ def swiglu(x):
 
 
 def fused_swiglu(x, w_gate, w_up, b_gate=None, b_up=None):
-    """(x Wg^T + bg) * silu(x Wu^T + bu): backend/_glu_append.py:47-60, fused-swiglu.glsl:54-78."""
+    """(x Wg^T + bg) * silu(x Wu^T + bu): backend/_glu_append.py:47-60, fused-swiglu.glsl:54-78. Parity unpinned as a
+    fused op (the file is a fragment no class includes); its parts, linear and SiLU, are pinned by the golden file."""
     g = linear(x, w_gate, b_gate if (b_gate is not None and b_up is not None) else None).astype(np.float64)
     u = linear(x, w_up, b_up if (b_gate is not None and b_up is not None) else None).astype(np.float64)
     return (g * (u / (1.0 + np.exp(-u)))).astype(F32)
