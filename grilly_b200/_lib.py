@@ -14,7 +14,7 @@ LIB_PATH = PKG / "lib" / "libgrilly_b200.so"
 
 OK = 0
 ERR_INVALID_ARG, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
-PREC_TF32, PREC_BF16 = 0, 1
+PREC_TF32, PREC_BF16, PREC_TF32X3 = 0, 1, 2
 ACT_NONE, ACT_GELU, ACT_SILU, ACT_RELU = 0, 1, 2, 3
 NORM_LAYER, NORM_RMS = 0, 1
 ELT_GELU, ELT_SILU, ELT_RELU, ELT_ADD, ELT_SWIGLU = 1, 2, 3, 4, 5
@@ -43,6 +43,7 @@ SIGNATURES = {
     "grilly_last_error": [_vp],
     "grilly_set_stream": [_vp, _vp],
     "grilly_sync": [_vp],
+    "grilly_set_tuning": [_vp, C.c_char_p, _i],
     "grilly_launch_count": [_vp, C.POINTER(C.c_uint64)],
     "grilly_selftest_wait_timeout": [_vp, _i],
     "grilly_timer_start": [_vp],

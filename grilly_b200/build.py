@@ -18,7 +18,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 BUILD = PKG / "_build"
 LIB = PKG / "lib" / "libgrilly_b200.so"
-SOURCES = ["api.cu", "gemm.cu", "attention.cu", "rowops.cu", "encoder.cu", "noalloc.cu", "selftest.cu", "faiss.cu"]
+SOURCES = ["api.cu", "gemm.cu", "attention.cu", "rowops.cu", "encoder.cu", "noalloc.cu", "selftest.cu", "faiss.cu", "tf32x3.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -45,24 +45,17 @@ def _digest(paths) -> str:
 
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, extra_flags=(), suffix: str = "") -> Path:
-    """Compile every .cu for sm_100a and link the shared library. Returns its path.
-
-    ``extra_flags`` (e.g. ``["-DGEMM_EPI_WARPS=16"]``) with a ``suffix`` builds a tuning variant next to the
-    default library; load it by pointing the GRILLY_B200_LIB environment variable at it."""
-    global BUILD, LIB
-    if suffix:
-        BUILD = PKG / "_build" / ("variant" + suffix)
-        LIB = PKG / "lib" / f"libgrilly_b200{suffix}.so"
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile every .cu for sm_100a and link the shared library. Returns its path."""
     BUILD.mkdir(parents=True, exist_ok=True)
     LIB.parent.mkdir(exist_ok=True)
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.glob("*.h"))
     stamp = BUILD / "stamp"
-    digest = _digest(deps) + "|" + " ".join(extra_flags)
+    digest = _digest(deps)
     if not force and LIB.exists() and stamp.exists() and stamp.read_text() == digest:
         return LIB
     nvcc = _nvcc()
-    flags = list(NVCC_FLAGS) + list(extra_flags) + (["-Xptxas", "-v"] if ptxas_info else [])
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
 
     def compile_one(src: str) -> Path:
         obj = BUILD / (src + ".o")
@@ -85,7 +78,5 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, 
 
 
 if __name__ == "__main__":
-    extra = [a for a in sys.argv[1:] if a.startswith("-D")]
-    sfx = next((a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--suffix=")), "")
-    path = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv, extra_flags=extra, suffix=sfx)
+    path = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
     print(path)

@@ -12,12 +12,14 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+from collections import OrderedDict
 
 import numpy as np
 
 from . import _lib as L
 from .device import Device, DeviceTensor
 
+_PREC = {"tf32": L.PREC_TF32, "bf16": L.PREC_BF16, "tf32x3": L.PREC_TF32X3}
 _ACT = {None: L.ACT_NONE, "none": L.ACT_NONE, "gelu": L.ACT_GELU, "silu": L.ACT_SILU, "relu": L.ACT_RELU}
 
 
@@ -37,14 +39,24 @@ class _Namespace:
     def _bf16(self) -> bool:
         return self._b.precision == "bf16"
 
-    def _act_in(self, x, mma_operand: bool = True):
+    def _mode(self, precision=None) -> str:
+        """Precision of one GEMM-family call: the per-call override, else the backend's. 'tf32x3' exists for
+        linear / fused_linear_* / fused_qkv_projection / gemm only; everything else then runs in tf32."""
+        mode = precision if precision is not None else self._b.precision
+        if mode not in ("tf32", "bf16", "tf32x3"):
+            raise ValueError("precision must be 'tf32', 'bf16' or 'tf32x3'")
+        return mode
+
+    def _act_in(self, x, mma_operand: bool = True, mode: str | None = None):
         """Activation operand -> (DeviceTensor, was_host). GEMM/attention operands are staged in the
-        precision the tensor core consumes (bf16, or fp32 rounded to the nearest tf32 value)."""
+        precision the tensor core consumes (bf16, or fp32 rounded to the nearest tf32 value; raw fp32 for the
+        split products of 'tf32x3')."""
         if isinstance(x, DeviceTensor):
             return x, False
-        if mma_operand and self._bf16:
+        bf16 = self._bf16 if mode is None else mode == "bf16"
+        if mma_operand and bf16:
             return self.dev.upload(x, "bf16"), True
-        return self.dev.upload(x, "f32", round_tf32=mma_operand), True
+        return self.dev.upload(x, "f32", round_tf32=mma_operand and mode != "tf32x3"), True
 
     def _vec(self, v):
         """Small fp32 parameter vector (bias, gamma, beta): cached like a weight, never rounded."""
@@ -66,7 +78,10 @@ class FNN(_Namespace):
         self.buffer_pool = _PoolView(backend.device)
 
     # ---- GEMM family ------------------------------------------------------------------------
-    def _linear(self, x, weights, bias, act, residual=None, flags=0, w_tag="", w_transform=None, n_out=None):
+    def _linear(self, x, weights, bias, act, residual=None, flags=0, w_tag="", w_transform=None, n_out=None,
+                precision=None):
+        mode = self._mode(precision)
+        bf16, x3 = mode == "bf16", mode == "tf32x3"
         w_shape = weights.shape
         if len(w_shape) != 2:
             raise ValueError("weights must be 2-D (out_features, in_features)")
@@ -74,9 +89,9 @@ class FNN(_Namespace):
         x_shape = tuple(x.shape)
         if x_shape[-1] != K:
             raise ValueError(f"input feature size {x_shape[-1]} does not match weights {tuple(w_shape)}")
-        elt = 2 if self._bf16 else 4
-        kpad = (-K) % (16 // elt)
-        dt = "bf16" if self._bf16 else "f32"
+        elt = 2 if bf16 else 4
+        kpad = 0 if x3 else (-K) % (16 // elt)   # the split kernels of tf32x3 pad K themselves
+        dt = "bf16" if bf16 else "f32"
         if kpad and not isinstance(x, DeviceTensor):
             # TMA needs 16-byte row pitches: pad K with zeros on both operands
             x = np.pad(np.asarray(x, dtype=np.float32).reshape(-1, K), ((0, 0), (0, kpad)))
@@ -85,8 +100,8 @@ class FNN(_Namespace):
             w_tag += f"|kpad{kpad}"
         elif kpad:
             raise ValueError("device-resident operands need in_features * element size to be a multiple of 16 bytes")
-        xd, host = self._act_in(x)
-        wd = self.dev.weight(weights, dt, round_tf32=True, transform=w_transform, tag="w" + w_tag)
+        xd, host = self._act_in(x, mode=mode)
+        wd = self.dev.weight(weights, dt, round_tf32=not x3, transform=w_transform, tag="w" + w_tag)
         n_rows_w = wd.shape[0]
         bd = self._vec(bias) if not isinstance(bias, DeviceTensor) else bias
         rd = None
@@ -96,30 +111,31 @@ class FNN(_Namespace):
         n_cols = n_out if n_out is not None else n_rows_w
         y = self.dev.empty((M, n_cols), "f32")
         self.dev.check(self.lib.grilly_linear(self.ctx, _p(xd), _p(wd), _p(bd), _p(rd), _p(y), M, n_rows_w, K + kpad,
-                                              act, L.PREC_BF16 if self._bf16 else L.PREC_TF32, flags))
+                                              act, _PREC[mode], flags))
         return self._out(y, host, x_shape[:-1] + (n_cols,))
 
-    def linear(self, x, weights, bias=None):
-        """y = x @ W.T + b, W (out, in): backend/fnn.py:1394-1496."""
-        return self._linear(x, weights, bias, L.ACT_NONE)
+    def linear(self, x, weights, bias=None, precision=None):
+        """y = x @ W.T + b, W (out, in): backend/fnn.py:1394-1496. ``precision='tf32x3'`` (here or on the backend)
+        gives fp32-level products, for callers that take argmax / top-k indices from the result."""
+        return self._linear(x, weights, bias, L.ACT_NONE, precision=precision)
 
-    def fused_linear_gelu(self, x, weights, bias=None):
+    def fused_linear_gelu(self, x, weights, bias=None, precision=None):
         """gelu_tanh(x @ W.T + b): backend/fnn.py:2022-2123."""
-        return self._linear(x, weights, bias, L.ACT_GELU)
+        return self._linear(x, weights, bias, L.ACT_GELU, precision=precision)
 
-    def fused_linear_relu(self, x, weights, bias=None):
+    def fused_linear_relu(self, x, weights, bias=None, precision=None):
         """relu(x @ W.T + b): backend/fnn.py:2125-2212."""
-        return self._linear(x, weights, bias, L.ACT_RELU)
+        return self._linear(x, weights, bias, L.ACT_RELU, precision=precision)
 
-    def fused_linear_silu(self, x, weights, bias=None):
+    def fused_linear_silu(self, x, weights, bias=None, precision=None):
         """silu(x @ W.T + b): backend/fnn.py:2214-2303."""
-        return self._linear(x, weights, bias, L.ACT_SILU)
+        return self._linear(x, weights, bias, L.ACT_SILU, precision=precision)
 
-    def fused_qkv_projection(self, x, w_qkv, b_qkv=None, num_heads=None, head_dim=None):
+    def fused_qkv_projection(self, x, w_qkv, b_qkv=None, num_heads=None, head_dim=None, precision=None):
         """x @ [Wq;Wk;Wv].T + [bq;bk;bv] -> (..., 3*H*D), column blocks Q, K, V: fused-qkv-projection.glsl:48-74."""
         if num_heads is not None and head_dim is not None and w_qkv.shape[0] != 3 * num_heads * head_dim:
             raise ValueError("stacked QKV weight must have 3 * num_heads * head_dim rows")
-        return self._linear(x, w_qkv, b_qkv, L.ACT_NONE)
+        return self._linear(x, w_qkv, b_qkv, L.ACT_NONE, precision=precision)
 
     def fused_swiglu(self, x, w_gate, w_up, b_gate=None, b_up=None):
         """(x Wg^T + bg) * silu(x Wu^T + bu) as ONE GEMM over row-interleaved [g0,u0,g1,u1,...] weights with a
@@ -164,7 +180,9 @@ class FNN(_Namespace):
             raise ValueError("fused_layernorm_linear needs in_features to be a multiple of 4")
         key = ("lnfold", id(weights), id(gamma), id(beta), id(bias), mode)
         fold = self._b._folds.get(key)
-        if fold is None:
+        if fold is not None:
+            self._b._folds.move_to_end(key)
+        else:
             wd = self.dev.upload(np.asarray(weights, np.float32))
             gd = self.dev.upload(np.asarray(gamma, np.float32)) if gamma is not None else None
             bd = self.dev.upload(np.asarray(beta, np.float32)) if (beta is not None and mode == "layer") else None
@@ -173,8 +191,13 @@ class FNN(_Namespace):
             self.dev.check(self.lib.grilly_fold_layernorm_weights(self.ctx, _p(wd), _p(gd), _p(bd), _p(cd), _p(wf), _p(cs),
                                                                   _p(bf), N, K, L.PREC_TF32))
             self.dev.sync()
+            for t in (wd, gd, bd, cd):
+                if t is not None:
+                    t.free()
             fold = (wf, cs, bf, weights, gamma, beta, bias)  # keep the host arrays alive so ids stay unique
             self._b._folds[key] = fold
+            while len(self._b._folds) > self._b.MAX_FOLDS:   # least recently used first
+                self._b._folds.popitem(last=False)
         wf, cs, bf = fold[:3]
         xd, host = self._act_in(x, mma_operand=False)  # statistics need the unrounded rows
         M = xd.size // K
@@ -187,24 +210,24 @@ class FNN(_Namespace):
         stats.free()
         return out
 
-    def gemm(self, A, B):
+    def gemm(self, A, B, precision=None):
         """C = A @ B, row-major (M,K) x (K,N): backend/fnn.py:104-166, gemm_mnk.glsl:35-88."""
         if len(A.shape) != 2 or len(B.shape) != 2 or A.shape[1] != B.shape[0]:
             raise AssertionError(f"K mismatch: {tuple(A.shape)} @ {tuple(B.shape)}")  # the reference asserts (fnn.py:118)
+        mode = self._mode(precision)
         M, K = (int(s) for s in A.shape)
         N = int(B.shape[1])
-        q = 8 if self._bf16 else 4
+        q = 8 if mode == "bf16" else 4
         kpad, npad = (-K) % q, (-N) % q
         if (kpad or npad) and (isinstance(A, DeviceTensor) or isinstance(B, DeviceTensor)):
             raise ValueError("device-resident gemm operands need K and N to be multiples of 16 bytes")
         if kpad or npad:
             A = np.pad(np.asarray(A, np.float32), ((0, 0), (0, kpad)))
             B = np.pad(np.asarray(B, np.float32), ((0, kpad), (0, npad)))
-        ad, host_a = self._act_in(A)
-        bd, host_b = self._act_in(B)
+        ad, host_a = self._act_in(A, mode=mode)
+        bd, host_b = self._act_in(B, mode=mode)
         c = self.dev.empty((M, N + npad))
-        self.dev.check(self.lib.grilly_gemm_mnk(self.ctx, _p(ad), _p(bd), _p(c), M, K + kpad, N + npad,
-                                                L.PREC_BF16 if self._bf16 else L.PREC_TF32, 0))
+        self.dev.check(self.lib.grilly_gemm_mnk(self.ctx, _p(ad), _p(bd), _p(c), M, K + kpad, N + npad, _PREC[mode], 0))
         if host_a or host_b:
             out = c.numpy()
             return np.ascontiguousarray(out[:, :N]) if npad else out
@@ -342,6 +365,9 @@ class Attention(_Namespace):
             raise ValueError("queries, keys and values must have the same shape")
         if mask is not None and tuple(mask.shape) != (B, S):
             raise ValueError(f"mask must have shape {(B, S)}")
+        if self._b.precision == "tf32x3":
+            return self._attention_fp32(queries, keys, values, B, S, H, D, scale, mask, causal, use_rope, rope_base,
+                                        rope_scaling, rope_style)
         qd, host = self._act_in(queries)
         kd, _ = self._act_in(keys)
         vd, _ = self._act_in(values)
@@ -359,6 +385,37 @@ class Attention(_Namespace):
         self.dev.check(self.lib.grilly_flash_attention(
             self.ctx, _p(qd), _p(kd), _p(vd), _p(out), B, S, H, D, H * D, H * D, None, B * S, _p(md), sc, int(bool(causal)),
             rope, float(rope_base), float(rope_scaling), L.PREC_BF16 if self._bf16 else L.PREC_TF32, 0))
+        return self._out(out, host)
+
+    def _attention_fp32(self, queries, keys, values, B, S, H, D, scale, mask, causal, use_rope, rope_base, rope_scaling,
+                        rope_style):
+        """The exact-index mode of a 'tf32x3' backend: the same attention from the fp32 FMA kernels of the unfused
+        pipeline (scores, mask, softmax, output; every product and sum in fp32, no tensor-core rounding), all on the
+        device. It materialises the (B, H, S, S) scores, so it is meant for checking indices, not for long sequences."""
+        if use_rope and rope_style not in ("interleaved", "rotate_half"):
+            raise ValueError("rope_style must be 'interleaved' or 'rotate_half'")
+        qd, host = self._act_in(queries, mma_operand=False)
+        kd, _ = self._act_in(keys, mma_operand=False)
+        vd, _ = self._act_in(values, mma_operand=False)
+        if use_rope:
+            style = L.ROPE_INTERLEAVED if rope_style == "interleaved" else L.ROPE_ROTATE_HALF
+            qr, kr = self.dev.empty((B, S, H, D)), self.dev.empty((B, S, H, D))
+            for src, dst in ((qd, qr), (kd, kr)):
+                self.dev.check(self.lib.grilly_apply_rope(self.ctx, _p(src), _p(dst), None, B, S, H, D, S, float(rope_base),
+                                                          float(rope_scaling), style))
+            qd, kd = qr, kr
+        sc = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+        scores = self.dev.empty((B, H, S, S))
+        self.dev.check(self.lib.grilly_attention_scores(self.ctx, _p(qd), _p(kd), _p(scores), B, S, H, D, sc))
+        if causal:
+            self.dev.check(self.lib.grilly_attention_mask(self.ctx, _p(scores), None, B, H, S, 1, -1e9))
+        if mask is not None:
+            md, _ = self._act_in(np.asarray(mask, dtype=np.float32) if not isinstance(mask, DeviceTensor) else mask,
+                                 mma_operand=False)
+            self.dev.check(self.lib.grilly_attention_mask(self.ctx, _p(scores), _p(md), B, H, S, 0, -1e9))
+        self.dev.check(self.lib.grilly_softmax(self.ctx, _p(scores), _p(scores), B * H * S, S))
+        out = self.dev.empty((B, S, H, D))
+        self.dev.check(self.lib.grilly_attention_output(self.ctx, _p(scores), _p(vd), _p(out), B, S, H, D))
         return self._out(out, host)
 
     def flash_attention2_rope(self, queries, keys, values, num_heads=None, head_dim=None, scale=None, mask=None,
@@ -552,22 +609,43 @@ class _PoolView:
         self._dev = dev
 
     def get_stats(self) -> dict:
-        return self._dev.pool_stats()
+        """The keys ``BufferPool.get_stats`` returns (backend/buffer_pool.py:627-640): a *hit* is an acquire the pool
+        served from memory it already held, ``allocations`` counts the acquires that made the pool grow (= misses),
+        ``total_pooled_memory`` is what the pool holds beyond the live buffers. The stream-ordered pool has no size
+        buckets and never evicts (release threshold = unlimited). The native counters follow under their own names."""
+        return reference_pool_stats(self._dev.pool_stats())
+
+
+def reference_pool_stats(native: dict) -> dict:
+    """Maps the library's pool counters to the reference's ``get_stats`` dictionary (plus the native ones)."""
+    acquired, hits = int(native.get("acquired", 0)), int(native.get("pool_hits", 0))
+    misses = max(acquired - hits, 0)
+    stats = {
+        "hits": hits, "misses": misses, "allocations": misses, "evictions": 0,
+        "total_acquired": acquired, "total_released": int(native.get("released", 0)),
+        "total_pooled_memory": max(int(native.get("pool_reserved_bytes", 0)) - int(native.get("bytes_in_use", 0)), 0),
+        "buckets": {}, "hit_rate": hits / max(1, hits + misses), "vma_enabled": False,
+    }
+    stats.update({k: v for k, v in native.items() if k not in stats})
+    return stats
 
 
 class Compute:
     """Drop-in for ``grilly.Compute()`` (``VulkanCompute``, backend/compute.py:23-128) on one B200.
 
-    precision: 'tf32' (fp32 storage, tf32 tensor-core products, fp32 accumulate) or 'bf16'.
+    precision: 'tf32' (fp32 storage, tf32 tensor-core products, fp32 accumulate), 'bf16', or 'tf32x3': like 'tf32',
+    but linear / fused_linear_* / fused_qkv_projection / gemm split every operand into tf32 hi + lo and run three
+    products, which gives fp32-level results -- the mode for callers that compare argmax / top-k indices with an fp32
+    implementation (tf32 alone cannot order values closer than its rounding noise).
     """
 
     def __init__(self, shader_dir=None, device: int = 0, precision: str = "tf32"):
-        if precision not in ("tf32", "bf16"):
-            raise ValueError("precision must be 'tf32' or 'bf16'")
+        if precision not in ("tf32", "bf16", "tf32x3"):
+            raise ValueError("precision must be 'tf32', 'bf16' or 'tf32x3'")
         self.precision = precision
         self.device = Device(device)
         self.architecture = None
-        self._folds: dict = {}
+        self._folds: OrderedDict = OrderedDict()   # folded LayerNorm->linear weights, least recently used first
         self.fnn = FNN(self)
         self.attention = Attention(self)
         self.pooling = Pooling(self)
@@ -598,13 +676,28 @@ class Compute:
         """Stage an array on the GPU once; ops given DeviceTensors return DeviceTensors."""
         if self.precision == "bf16" and mma_operand:
             return self.device.upload(arr, "bf16")
-        return self.device.upload(arr, "f32", round_tf32=mma_operand)
+        return self.device.upload(arr, "f32", round_tf32=mma_operand and self.precision != "tf32x3")
+
+    MAX_FOLDS = 32
+
+    def register_weight(self, arr):
+        """Keep ``arr``'s device copies cached for the backend's lifetime (see :meth:`Device.register_weight`)."""
+        self.device.register_weight(arr)
 
     def invalidate(self, arr=None):
-        """Forget cached device copies of a weight that was modified in place (all weights if None)."""
+        """Forget cached device copies of a weight that was modified in place (all weights if None), including the
+        folded LayerNorm->linear weights that were built from it (as weights, gamma, beta or bias)."""
         self.device.invalidate(arr)
         if arr is None:
             self._folds.clear()
+            return
+        ptr = np.asarray(arr).__array_interface__["data"][0]
+
+        def same(h):
+            return h is not None and (h is arr or np.asarray(h).__array_interface__["data"][0] == ptr)
+
+        for k in [k for k, f in self._folds.items() if any(same(h) for h in f[3:])]:
+            del self._folds[k]
 
     def synchronize(self):
         self.device.sync()

@@ -3,6 +3,7 @@
 #include "internal.h"
 #include "args.h"
 #include <cudaTypedefs.h>
+#include <cstdlib>
 
 namespace gb {
 
@@ -116,6 +117,17 @@ int grilly_init(int device, grilly_ctx** out) {
     return GRILLY_ERR_CUDA;
   }
   *ctx->err_host = 0;
+  // tuning/debug overrides: read here once, never on the launch path
+  auto env_int = [](const char* name, int fallback) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : fallback;
+  };
+  ctx->tune.gemm_group = env_int("GRILLY_GEMM_GROUP", 0);
+  ctx->tune.gemm_bn = env_int("GRILLY_GEMM_BN", 0);
+  ctx->tune.gemm_pair = env_int("GRILLY_GEMM_PAIR", -1);
+  ctx->tune.gemm_swap = env_int("GRILLY_GEMM_SWAP", -1);
+  ctx->tune.attn_hpc = env_int("GRILLY_ATTN_HPC", 0);
+  ctx->tune.attn_general = getenv("GRILLY_ATTN_GENERAL") != nullptr ? 1 : 0;
   *out = ctx;
   return GRILLY_OK;
 }
@@ -140,6 +152,20 @@ const char* grilly_last_error(grilly_ctx* ctx) { return ctx ? ctx->last_error.c_
 int grilly_set_stream(grilly_ctx* ctx, void* cuda_stream) {
   CTX_GUARD(ctx);
   ctx->stream = cuda_stream ? reinterpret_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+  return GRILLY_OK;
+}
+
+int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value) {
+  CTX_GUARD(ctx);
+  if (!name) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "set_tuning: null name");
+  const std::string n(name);
+  if (n == "gemm_group") ctx->tune.gemm_group = value;
+  else if (n == "gemm_bn") ctx->tune.gemm_bn = value;
+  else if (n == "gemm_pair") ctx->tune.gemm_pair = value;
+  else if (n == "gemm_swap") ctx->tune.gemm_swap = value;
+  else if (n == "attn_hpc") ctx->tune.attn_hpc = value;
+  else if (n == "attn_general") ctx->tune.attn_general = value;
+  else return set_error(ctx, GRILLY_ERR_INVALID_ARG, "set_tuning: unknown knob '" + n + "'");
   return GRILLY_OK;
 }
 
@@ -221,12 +247,18 @@ int grilly_alloc(grilly_ctx* ctx, size_t bytes, void** dptr) {
   if (!dptr) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "alloc: null output pointer");
   if (bytes == 0) bytes = 16;
   void* p = nullptr;
+  // a "hit" in the sense of BufferPool.acquire (backend/buffer_pool.py:534-562): the pool served the request from
+  // memory it already held, i.e. its reserved size did not grow
+  uint64_t reserved_before = 0, reserved_after = 0;
+  cudaMemPoolGetAttribute(ctx->pool, cudaMemPoolAttrReservedMemCurrent, &reserved_before);
   cudaError_t e = cudaMallocAsync(&p, bytes, ctx->stream);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return set_error(ctx, e == cudaErrorMemoryAllocation ? GRILLY_ERR_OOM : GRILLY_ERR_CUDA,
                      std::string("cudaMallocAsync: ") + cudaGetErrorString(e));
   }
+  cudaMemPoolGetAttribute(ctx->pool, cudaMemPoolAttrReservedMemCurrent, &reserved_after);
+  if (reserved_after <= reserved_before) ctx->pool_hits++;
   ctx->live[p] = bytes;
   ctx->n_alloc++;
   ctx->bytes_in_use += bytes;
@@ -284,7 +316,7 @@ int grilly_pool_stats(grilly_ctx* ctx, uint64_t out[8]) {
   uint64_t reserved = 0;
   cudaMemPoolGetAttribute(ctx->pool, cudaMemPoolAttrReservedMemCurrent, &reserved);
   out[0] = ctx->n_alloc; out[1] = ctx->n_free; out[2] = ctx->bytes_in_use; out[3] = ctx->peak_bytes;
-  out[4] = reserved; out[5] = ctx->tmap_hits; out[6] = ctx->tmap_misses; out[7] = 0;
+  out[4] = reserved; out[5] = ctx->tmap_hits; out[6] = ctx->tmap_misses; out[7] = ctx->pool_hits;
   return GRILLY_OK;
 }
 
@@ -301,15 +333,18 @@ int grilly_cast_bf16_to_f32(grilly_ctx* ctx, const void* x, float* y, long long 
   return launch_bf16_to_f32(ctx, x, y, n);
 }
 
-static int check_prec(grilly_ctx* ctx, int precision) {
+static int check_prec(grilly_ctx* ctx, int precision, bool x3_ok = false) {
+  if (precision == GRILLY_PREC_TF32X3 && x3_ok) return GRILLY_OK;
+  if (precision == GRILLY_PREC_TF32X3)
+    return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "GRILLY_PREC_TF32X3 is offered by linear, fused_qkv_projection and gemm_mnk only");
   if (precision != GRILLY_PREC_TF32 && precision != GRILLY_PREC_BF16)
-    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "precision must be GRILLY_PREC_TF32 or GRILLY_PREC_BF16");
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "precision must be GRILLY_PREC_TF32, GRILLY_PREC_BF16 or GRILLY_PREC_TF32X3");
   return GRILLY_OK;
 }
 
 static int linear_nolock(grilly_ctx* ctx, const void* x, const void* w, const float* bias, const float* residual, void* y,
                          int M, int N, int K, int act, int precision, int flags) {
-  int rc = check_prec(ctx, precision);
+  int rc = check_prec(ctx, precision, true);
   if (rc) return rc;
   if (!x || !w || !y) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "linear: null operand");
   if (act < GRILLY_ACT_NONE || act > GRILLY_ACT_RELU) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "linear: unknown activation");
@@ -323,6 +358,10 @@ static int linear_nolock(grilly_ctx* ctx, const void* x, const void* w, const fl
   a.round_tf32 = (flags & GRILLY_FLAG_ROUND_TF32) ? 1 : 0;
   a.act = act;
   if (a.swiglu_pairs && residual) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "linear: SwiGLU pairs with a residual is not supported");
+  if (precision == GRILLY_PREC_TF32X3) {
+    if (M <= 0 || N <= 0 || K <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: M, N, K must be positive");
+    return linear_tf32x3(ctx, static_cast<const float*>(x), static_cast<const float*>(w), a);
+  }
   return launch_gemm(ctx, precision == GRILLY_PREC_BF16, false, x, w, a, 0);
 }
 
@@ -380,7 +419,7 @@ int grilly_layernorm_linear(grilly_ctx* ctx, const float* x, const void* wf, con
 int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int M, int K, int N, int precision,
                     int flags) {
   CTX_GUARD(ctx);
-  int rc = check_prec(ctx, precision);
+  int rc = check_prec(ctx, precision, true);
   if (rc) return rc;
   if (!a_dev || !b_dev || !c_dev) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm_mnk: null operand");
   GemmArgs a{};
@@ -388,6 +427,11 @@ int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void*
   a.out = c_dev; a.ld_out = N;
   a.out_bf16 = (flags & GRILLY_FLAG_OUT_BF16) ? 1 : 0;
   a.round_tf32 = (flags & GRILLY_FLAG_ROUND_TF32) ? 1 : 0;
+  if (precision == GRILLY_PREC_TF32X3) {
+    if (M <= 0 || N <= 0 || K <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: M, N, K must be positive");
+    if (N % 4) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "gemm_mnk: N * element size must be a multiple of 16 bytes (pad N)");
+    return gemm_mnk_tf32x3(ctx, static_cast<const float*>(a_dev), static_cast<const float*>(b_dev), a);
+  }
   return launch_gemm(ctx, precision == GRILLY_PREC_BF16, true, a_dev, b_dev, a, 0);
 }
 

@@ -13,6 +13,8 @@ struct GemmArgs {
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_k_blocks;
   int tile_group;         // fast-dimension blocks per group of the tile order (see tile_coords)
+  int multi_out;          // gemm_mnk only: number of FURTHER destinations (in g_gemm_extra_out) this launch stores to;
+                          // 0 for every other launch. Sits in the padding before the pointers: the struct does not grow.
   const float* bias;      // [N] (pre-activation) or null
   const float* residual;  // [M][ld_res] fp32, added after the activation, or null
   long long ld_res;

@@ -3,7 +3,6 @@
 #include "attention.cuh"
 #include "attention_short.cuh"
 #include "internal.h"
-#include <cstdlib>
 
 namespace gb {
 
@@ -64,7 +63,7 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
   // slot (sequences differ in length, so a slot's last unit decides how long the tail of the launch is)
   int hpc = args.H;
   while (hpc > 1 && static_cast<long long>(args.B) * ((args.H + hpc - 1) / hpc) < 6LL * Cfg::NSLOT * ctx->num_sms) hpc = (hpc + 1) / 2;
-  if (const char* env = getenv("GRILLY_ATTN_HPC")) hpc = atoi(env) > 0 ? atoi(env) : hpc;  // heads per unit, for tuning runs
+  if (ctx->tune.attn_hpc > 0) hpc = ctx->tune.attn_hpc;   // heads per unit, for tuning runs
   hpc = (hpc + Cfg::HPR - 1) / Cfg::HPR * Cfg::HPR;   // heads that share a loaded row chunk stay in one unit
   const int head_groups = (args.H + hpc - 1) / hpc;
   const long long units = static_cast<long long>(args.B) * head_groups;
@@ -90,9 +89,15 @@ int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, c
   if ((ld_q * elt) % 16 != 0 || (ld_k * elt) % 16 != 0 || (ld_v * elt) % 16 != 0) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: row pitch must be a multiple of 16 bytes");
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: q, k, v must be 16-byte aligned");
+  // the kernels store bf16 results as 32-bit pairs and fp32 results as 16-byte vectors where the pitch allows it
+  if (!args.out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: null output");
+  if (args.out_bf16 && ((args.ld_out & 1) || (reinterpret_cast<uintptr_t>(args.out) & 3)))
+    return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: a bf16 output needs an even row pitch and a 4-byte aligned base");
+  if (!args.out_bf16 && (reinterpret_cast<uintptr_t>(args.out) & 3))
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention: the output must be 4-byte aligned");
   // every sequence fits one key tile and nothing needs per-tile state: the multi-head kernel
   const bool short_ok = args.S <= ATTN_TILE && !args.causal && args.rope_style == ROPE_NONE && args.scale > 0.f &&
-                        args.B <= 2147483647 && getenv("GRILLY_ATTN_GENERAL") == nullptr;
+                        args.B <= 2147483647 && !ctx->tune.attn_general;
   if (short_ok) {
     if (!bf16 && args.D == 32) return launch_short<32, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
     if (!bf16 && args.D == 64) return launch_short<64, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);

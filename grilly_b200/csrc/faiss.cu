@@ -20,31 +20,6 @@
 
 namespace gb {
 
-// One warp per row: out[row] = [hi | lo | hi] (query_side) or [hi | hi | lo], each part dim_pad wide (zero padded),
-// norm2[row] = sum x^2 in fp32.
-__global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ x, float* __restrict__ out,
-                                                         float* __restrict__ norm2, long long rows, int dim, int dim_pad,
-                                                         int query_side) {
-  const int lane = threadIdx.x & 31;
-  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const float* xp = x + row * dim;
-  float* op = out + row * 3LL * dim_pad;
-  float s = 0.f;
-  for (int d = lane; d < dim_pad; d += 32) {
-    const float v = d < dim ? __ldg(xp + d) : 0.f;
-    const float hi = round_to_tf32(v);
-    const float lo = round_to_tf32(v - hi);
-    s = fmaf(v, v, s);
-    op[d] = hi;
-    op[dim_pad + d] = query_side ? lo : hi;
-    op[2 * dim_pad + d] = query_side ? hi : lo;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) norm2[row] = s;
-}
-
 // In place: out[q][d] holds q.d on entry; qn2 / dn2 are the squared norms.
 __global__ void __launch_bounds__(256) dot_to_distance_kernel(float* __restrict__ out, const float* __restrict__ qn2,
                                                               const float* __restrict__ dn2, int nq, int ndb, int mode) {
@@ -212,13 +187,12 @@ int grilly_faiss_distances(grilly_ctx* ctx, const float* queries, const float* d
     cudaGetLastError();
     rc = set_error(ctx, GRILLY_ERR_OOM, "faiss_distances: no memory for the split operands (3 x the size of queries + database)");
   } else {
-    split_rows_kernel<<<(num_queries + 7) / 8, 256, 0, ctx->stream>>>(queries, qs, qn, num_queries, dim, dim_pad, 1);
-    split_rows_kernel<<<(num_database + 7) / 8, 256, 0, ctx->stream>>>(database, ds, dn, num_database, dim, dim_pad, 0);
-    ctx->launches += 2;
+    rc = launch_split_rows(ctx, queries, qs, qn, num_queries, dim, dim_pad, true);
+    if (!rc) rc = launch_split_rows(ctx, database, ds, dn, num_database, dim, dim_pad, false);
     GemmArgs a{};
     a.M = num_queries; a.N = num_database; a.K = static_cast<int>(kq);
     a.out = out; a.ld_out = num_database;
-    rc = launch_gemm(ctx, false, false, qs, ds, a, 0);
+    if (!rc) rc = launch_gemm(ctx, false, false, qs, ds, a, 0);
     if (!rc) {
       const long long total = static_cast<long long>(num_queries) * num_database;
       const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 8LL * ctx->num_sms));

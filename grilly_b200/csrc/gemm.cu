@@ -3,15 +3,8 @@
 #include "gemm.cuh"
 #include "gemm_pair.cuh"
 #include "internal.h"
-#include <cstdlib>
 
 namespace gb {
-
-static int env_int(const char* name, int fallback) {   // tuning override, must be positive
-  const char* v = getenv(name);
-  const int x = v ? atoi(v) : 0;
-  return x > 0 ? x : fallback;
-}
 
 template <int BN, bool kBf16, bool kBMn, bool kSwap>
 static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& args) {
@@ -45,7 +38,7 @@ static int launch_one(grilly_ctx* ctx, const void* a, const void* b, GemmArgs& a
   args.num_k_blocks = (args.K + BK - 1) / BK;
   // co-running tiles (one per SM) load group*fast_rows + (SMs/group)*slow_rows operand rows per k-block: smallest
   // near group = sqrt(SMs * slow_rows / fast_rows)
-  args.tile_group = env_int("GRILLY_GEMM_GROUP", kSwap ? 16 : 8);
+  args.tile_group = ctx->tune.gemm_group > 0 ? ctx->tune.gemm_group : (kSwap ? 16 : 8);
   args.err = ctx->err_dev;
   auto kern = gemm_tcgen05_kernel<BN, kBf16, kBMn, kSwap>;
   if (!ctx->smem_attr_done.count(reinterpret_cast<const void*>(kern))) {
@@ -89,7 +82,7 @@ static int launch_pair(grilly_ctx* ctx, const void* x, const void* w, GemmArgs& 
     args.num_n_tiles = (args.M + Cfg::TILE - 1) / Cfg::TILE;
   }
   args.num_k_blocks = (args.K + BK - 1) / BK;
-  args.tile_group = env_int("GRILLY_GEMM_GROUP", 8);
+  args.tile_group = ctx->tune.gemm_group > 0 ? ctx->tune.gemm_group : 8;
   args.err = ctx->err_dev;
   auto kern = gemm_tcgen05_pair_kernel<kBf16, kBMn>;
   const void* key = reinterpret_cast<const void*>(kern);
@@ -174,18 +167,16 @@ int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, cons
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: operands must be 16-byte aligned");
   if (args.swiglu_pairs && (args.N & 1)) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm: SwiGLU pairs need an even N");
-  if (force_bn <= 0) {
-    // tuning/debug override of the tile width (64, 128, 192 or 256); a forced width also rules out the pair kernel
-    if (const char* env = getenv("GRILLY_GEMM_BN")) force_bn = atoi(env);
-  }
+  // tuning/debug override of the tile width (64, 128, 192 or 256); a forced width also rules out the pair kernel
+  if (force_bn <= 0) force_bn = ctx->tune.gemm_bn;
   bool pair = pick_pair(args.M, args.N, b_mn_major);
-  if (const char* env = getenv("GRILLY_GEMM_PAIR")) pair = atoi(env) != 0;  // tuning/debug override
+  if (ctx->tune.gemm_pair >= 0) pair = ctx->tune.gemm_pair != 0;
   if (pair && force_bn <= 0) {
     if (b_mn_major) return bf16 ? launch_pair<true, true>(ctx, a, b, args) : launch_pair<false, true>(ctx, a, b, args);
     return bf16 ? launch_pair<true, false>(ctx, a, b, args) : launch_pair<false, false>(ctx, a, b, args);
   }
   bool swap = pick_swap(args.N, b_mn_major);
-  if (const char* env = getenv("GRILLY_GEMM_SWAP")) swap = !b_mn_major && atoi(env) != 0;  // tuning/debug override
+  if (ctx->tune.gemm_swap >= 0) swap = !b_mn_major && ctx->tune.gemm_swap != 0;
   const int bn = force_bn > 0 ? force_bn : pick_bn(swap ? args.M : args.N);
   if (bf16) {
     if (b_mn_major) return dispatch_bn<true, true, false>(ctx, bn, a, b, args);
@@ -196,7 +187,8 @@ int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, cons
 }
 
 // gemm_mnk whose fp32 result goes to args.out and to n_extra further matrices of the same pitch (device pointers,
-// possibly peer-mapped). The list is placed in constant memory in stream order around the launch.
+// possibly peer-mapped). The list is placed in constant memory in stream order before the launch; the launch is
+// marked (GemmArgs::multi_out) as the one that reads it.
 int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, GemmArgs& args, void* const* extra, int n_extra) {
   if (n_extra < 0 || n_extra > 7) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "gemm_mnk_multi: at most 8 destinations");
   if (n_extra > 0 && (args.N % 32 != 0 || args.out_bf16))
@@ -205,12 +197,8 @@ int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, 
   h.n = n_extra;
   for (int i = 0; i < n_extra; ++i) h.p[i] = extra[i];
   if (n_extra > 0) GB_CUDA_CHECK(ctx, cudaMemcpyToSymbolAsync(g_gemm_extra_out, &h, sizeof(h), 0, cudaMemcpyHostToDevice, ctx->stream));
-  const int rc = launch_gemm(ctx, bf16, true, a, b, args, 0);
-  if (n_extra > 0) {
-    h = GemmExtraOut{};
-    GB_CUDA_CHECK(ctx, cudaMemcpyToSymbolAsync(g_gemm_extra_out, &h, sizeof(h), 0, cudaMemcpyHostToDevice, ctx->stream));
-  }
-  return rc;
+  args.multi_out = n_extra;   // only this launch reads the list
+  return launch_gemm(ctx, bf16, true, a, b, args, 0);
 }
 
 }  // namespace gb

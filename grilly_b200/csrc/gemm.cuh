@@ -57,7 +57,8 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 // Further destinations of a gemm_mnk result (fp32, same pitch as the first output), e.g. the C matrices of the other
 // GPUs of a column-split product. They travel in constant memory, not in GemmArgs: the `linear` kernels are compiled
 // at their register limit and a larger argument struct alone made them spill. Set by the launcher in the stream
-// before the launch and cleared after it; n = 0 for every other launch.
+// before the launch. Only a launch whose GemmArgs::multi_out is non-zero reads the list, so plain GEMMs that run on
+// the same GPU at the same time (other streams, other contexts) are not affected by it.
 struct GemmExtraOut {
   int n;
   void* p[7];
@@ -73,7 +74,7 @@ struct EpiFlags {
   bool vec_ok, vec8_ok, res_vec_ok, bias_vec_ok;
 };
 
-// gemm_mnk with several destinations (g_gemm_extra_out.n > 0): the plain fp32 product goes to args.out and to every
+// gemm_mnk with several destinations (args.multi_out > 0): the plain fp32 product goes to args.out and to every
 // further destination. A warp holds a 32 x 32 block with one row per lane; it is transposed inside the warp (five
 // exchange stages) so that every store instruction writes 32 consecutive columns of ONE row, a full 128-byte
 // line: stores to a peer GPU then leave as whole lines instead of 16-byte pieces of 32 different rows.
@@ -95,7 +96,7 @@ __device__ __forceinline__ void epilogue_chunk_multi(const GemmArgs& args, const
     }
   }
   // now v[i] of lane l is element (row0 + i, col0 + l)
-  for (int d = 0; d <= g_gemm_extra_out.n; ++d) {
+  for (int d = 0; d <= args.multi_out; ++d) {
     float* base = reinterpret_cast<float*>(d == 0 ? args.out : g_gemm_extra_out.p[d - 1]) + col0 + lane;
 #pragma unroll
     for (int i = 0; i < 32; ++i)
@@ -291,9 +292,6 @@ __device__ __forceinline__ void epilogue_swapped_fast(const GemmArgs& args, cons
       else if constexpr (ACT == ACT_RELU) v = fmaxf(v, 0.f);
       if constexpr (RES) v += res[u];
       if (rnd) v = round_to_tf32(v);
-#ifdef GEMM_EXPERIMENT_NOSTORE
-      if (__float_as_uint(v) == 0x7fc12345u)   // timing experiment only: keep the arithmetic, drop the stores
-#endif
       st_global_f32(op + static_cast<long long>(g + u) * args.ld_out, v);
     }
   }
@@ -396,15 +394,8 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
   } else {
     float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
     if (full) {
-#ifdef GEMM_EXPERIMENT_NOSTORE
-      // timing experiment only: keep the epilogue arithmetic, drop (almost) every store
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (__float_as_uint(v[j]) == 0x7fc12345u) op[static_cast<long long>(j) * args.ld_out] = v[j];
-#else
 #pragma unroll
       for (int j = 0; j < 32; ++j) op[static_cast<long long>(j) * args.ld_out] = v[j];
-#endif
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -516,9 +507,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-#ifdef GEMM_EXPERIMENT_NOLOAD
-      int issued = 0;
-#endif
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         // un-swapped: column blocks fastest (neighbouring CTAs share the A rows); swapped: the weight blocks
         // (128-row operand) fastest, so neighbouring CTAs share one block of tokens
@@ -534,11 +522,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
-#ifdef GEMM_EXPERIMENT_NOLOAD
-          // timing experiment only: after the ring has been filled once, hand stages over without reloading them
-          if (issued >= STAGES) { mbar_arrive(&full_bar[stage]); if (++stage == STAGES) { stage = 0; phase ^= 1u; } continue; }
-          ++issued;
-#endif
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * 128);
           if constexpr (kBMnMajor) {
@@ -588,14 +571,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // (units of 16 bytes), so a 32-bit add on the low word replaces rebuilding them for every MMA
           const uint32_t a_lo = a_desc_lo + stage * (Cfg::STAGE_BYTES >> 4);
           const uint32_t b_lo = b_desc_lo + stage * (Cfg::STAGE_BYTES >> 4);
-#ifndef GEMM_EXPERIMENT_NOMMA
 #pragma unroll
           for (int ks = 0; ks < KSTEPS; ++ks) {
             const uint64_t adesc = (static_cast<uint64_t>(a_desc_hi) << 32) | (a_lo + ks * 2);
             const uint64_t bdesc = (static_cast<uint64_t>(b_desc_hi) << 32) | (b_lo + ks * (B_KSTEP_BYTES >> 4));
             umma_ss<kBf16>(d_tmem, adesc, bdesc, IDESC, (kb | ks) != 0 ? 1u : 0u);
           }
-#endif
           umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -650,14 +631,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (c < NCHUNK) tmem_ld_wait();
         if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
         const int col0 = n_blk * BN + c * 32;
-#ifdef GEMM_EXPERIMENT_NOEPI
-        if (c < NCHUNK && col0 < 0) epilogue_chunk_swapped(args, cur, row, col0);  // timing experiment: drain only
-        continue;
-#endif
         if constexpr (kSwap) {
           if (c < NCHUNK && col0 < args.M) epilogue_chunk_swapped(args, cur, row, col0);
         } else {
-          if (g_gemm_extra_out.n > 0) {   // launcher guarantees fp32 output and N a multiple of 32
+          if (args.multi_out > 0) {   // launcher guarantees fp32 output and N a multiple of 32
             if (c < NCHUNK && col0 < args.N) epilogue_chunk_multi(args, cur, row - lane, col0, lane);
           } else if (c < NCHUNK && row_ok && col0 < args.N) {
             epilogue_chunk(args, f, cur, row, col0, mean, rstd);

@@ -97,9 +97,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-#ifdef GEMM_EXPERIMENT_NOLOAD
-      int issued = 0;
-#endif
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m_blk, n_blk;                                      // feature blocks fastest: neighbours share the tokens
         tile_coords(tile, args.num_m_tiles, args.num_n_tiles, args.tile_group, m_blk, n_blk);
@@ -109,11 +106,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { fail(ERR_WAIT_EMPTY); ok = false; break; }
           uint8_t* sw = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sx = sw + Cfg::HALF_BYTES;
-#ifdef GEMM_EXPERIMENT_NOLOAD
-          // timing experiment only: after the ring has been filled once, hand stages over without reloading them
-          if (issued >= STAGES) { if (leader) mbar_arrive(&full_bar[stage]); if (++stage == STAGES) { stage = 0; phase ^= 1u; } continue; }
-          ++issued;
-#endif
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);   // both CTAs' bytes land on this barrier
           const uint32_t bar = map_to_cta(&full_bar[stage], 0);
           tma_load_2d_pair(sw, &tmap_w, bar, kb * BK, w_row);
@@ -155,14 +147,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
           tc_fence_after();
           const uint32_t a_lo = a_desc_lo + stage * (Cfg::STAGE_BYTES >> 4);
           const uint32_t b_lo = b_desc_lo + stage * (Cfg::STAGE_BYTES >> 4);
-#ifndef GEMM_EXPERIMENT_NOMMA
 #pragma unroll
           for (int ks = 0; ks < KSTEPS; ++ks) {
             const uint64_t adesc = (static_cast<uint64_t>(a_desc_hi) << 32) | (a_lo + ks * 2);
             const uint64_t bdesc = (static_cast<uint64_t>(b_desc_hi) << 32) | (b_lo + ks * (B_KSTEP_BYTES >> 4));
             umma_ss_pair<kBf16>(d_tmem, adesc, bdesc, IDESC, (kb | ks) != 0 ? 1u : 0u);
           }
-#endif
           // the stage is free in both CTAs once these MMAs have read it
           umma_commit_pair(own_empty0 + stage * 8);
           umma_commit_pair(peer_empty0 + stage * 8);
@@ -210,13 +200,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         if (c < NCHUNK) tmem_ld_wait();
         if (c + G < NCHUNK) tmem_ld_32x32(taddr_row + (c + G) * 32, nxt);
         const int tok0 = n_blk * Cfg::TILE + c * 32;
-#ifdef GEMM_EXPERIMENT_NOEPI
-        if (c < NCHUNK && tok0 < 0) epilogue_chunk_swapped(args, cur, feat, tok0);  // timing experiment: drain only
-        continue;
-#endif
         if constexpr (kBMn) {
           // feat is the row of C, tok0 the first of 32 columns
-          if (g_gemm_extra_out.n > 0) {   // launcher guarantees fp32 output and N a multiple of 32
+          if (args.multi_out > 0) {   // launcher guarantees fp32 output and N a multiple of 32
             if (c < NCHUNK && tok0 < args.N) epilogue_chunk_multi(args, cur, feat - lane, tok0, lane);
           } else if (c < NCHUNK && feat < args.M && tok0 < args.N) {
             epilogue_chunk(args, f, cur, feat, tok0, 0.f, 1.f);

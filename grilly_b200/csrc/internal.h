@@ -47,6 +47,7 @@ struct grilly_ctx {
   std::string last_error;
   // pool statistics
   uint64_t n_alloc = 0, n_free = 0, bytes_in_use = 0, peak_bytes = 0;
+  uint64_t pool_hits = 0;       // allocations served without the pool's reserved size growing
   std::unordered_map<void*, size_t> live;
   // tensor-map cache
   std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> tmaps;
@@ -60,6 +61,16 @@ struct grilly_ctx {
   bool profiling = false;
   std::vector<ProfRec> prof;
   double attn_flops_hint = -1.0;  // set by a caller that knows the true sequence lengths
+  // Tuning/debug overrides, read from the environment ONCE in grilly_init (GRILLY_GEMM_GROUP, GRILLY_GEMM_BN,
+  // GRILLY_GEMM_PAIR, GRILLY_GEMM_SWAP, GRILLY_ATTN_HPC, GRILLY_ATTN_GENERAL); 0 / -1 = not set
+  struct Tuning {
+    int gemm_group = 0;      // fast-dimension blocks per group of the tile order
+    int gemm_bn = 0;         // forced N tile (64, 128, 192, 256); also rules out the pair kernel
+    int gemm_pair = -1;      // 0/1: never/always the CTA-pair kernel
+    int gemm_swap = -1;      // 0/1: never/always the swapped orientation for `linear`
+    int attn_hpc = 0;        // heads per work unit of the short attention kernel
+    int attn_general = 0;    // 1: always the general attention kernel
+  } tune;
   // RoPE tables, keyed by (S, D, base, scaling)
   struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };
   std::vector<RopeTable> rope_tables;
@@ -96,6 +107,11 @@ struct PoolArgs;
 // gemm.cu
 int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, const void* b, GemmArgs& args, int force_bn);
 int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, GemmArgs& args, void* const* extra, int n_extra);
+// tf32x3.cu: fp32-accurate products through tf32 hi/lo splits (K' = 3K)
+int launch_split_rows(grilly_ctx* ctx, const float* x, float* out, float* norm2, long long rows, int dim, int dim_pad,
+                      bool lo_second);
+int linear_tf32x3(grilly_ctx* ctx, const float* x, const float* w, GemmArgs& args);
+int gemm_mnk_tf32x3(grilly_ctx* ctx, const float* a, const float* b, GemmArgs& args);
 // attention.cu
 int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
                      long long ld_v, long long total_rows, AttnArgs& args);

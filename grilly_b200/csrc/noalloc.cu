@@ -27,11 +27,15 @@ constexpr int kMaxDevices = 64;
 // runtime's symbol lookup, not a device address: kernels get the pointer returned by cudaGetSymbolAddress.
 static __device__ __align__(256) float g_norm_stats_scratch[2 * kMaxRows];
 
+// One resolved address per device for the whole process. Contexts of different devices run under different context
+// mutexes, so the table has a lock of its own.
 float* g_scratch_addr[kMaxDevices] = {};
+std::mutex g_scratch_mu;
 
 int scratch_for_device(grilly_ctx* ctx, float** out) {
   if (ctx->device < 0 || ctx->device >= kMaxDevices)
     return gb::set_error(ctx, GRILLY_ERR_UNSUPPORTED, "layernorm_linear_noalloc: device index out of range");
+  std::lock_guard<std::mutex> table_lock(g_scratch_mu);
   if (!g_scratch_addr[ctx->device]) {
     // once per device, with that device current (the caller has already made it current)
     void* p = nullptr;
@@ -55,6 +59,8 @@ extern "C" int grilly_layernorm_linear_noalloc(grilly_ctx* ctx, const float* x_d
   if (!ctx) return GRILLY_ERR_INVALID_ARG;
   std::lock_guard<std::mutex> lock(ctx->mu);
   if (cudaSetDevice(ctx->device) != cudaSuccess) return gb::set_error(ctx, GRILLY_ERR_CUDA, "cudaSetDevice failed");
+  if (precision != GRILLY_PREC_TF32 && precision != GRILLY_PREC_BF16)
+    return gb::set_error(ctx, GRILLY_ERR_INVALID_ARG, "precision must be GRILLY_PREC_TF32 or GRILLY_PREC_BF16");
   if (!x_dev || !wf_dev || !y_dev) return gb::set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear_noalloc: null operand");
   if (M <= 0 || N <= 0 || K <= 0) return gb::set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear_noalloc: M, N, K must be positive");
   if (M > kMaxRows)

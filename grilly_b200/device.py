@@ -86,6 +86,7 @@ class Device:
         self.ctx = h
         self.index = index
         self._weights: dict = {}
+        self._pinned: dict = {}
         self._closed = False
 
     # ------------------------------------------------------------------ plumbing
@@ -97,6 +98,11 @@ class Device:
 
     def set_stream(self, cuda_stream_ptr: int | None) -> None:
         self.check(self.lib.grilly_set_stream(self.ctx, C.c_void_p(cuda_stream_ptr or 0)))
+
+    def set_tuning(self, name: str, value: int) -> None:
+        """Kernel-selection knob of this context (``grilly_set_tuning``): tests and sweeps use it to force a tile
+        width or the CTA-pair kernel; 0 (``gemm_pair``/``gemm_swap``: -1) restores the default choice."""
+        self.check(self.lib.grilly_set_tuning(self.ctx, name.encode(), int(value)))
 
     def launch_count(self) -> int:
         n = C.c_uint64(0)
@@ -154,31 +160,44 @@ class Device:
     def weight(self, arr, dtype: str = "f32", round_tf32: bool = True, transform=None, tag: str = "") -> DeviceTensor:
         """Device copy of a weight array, cached by the identity of the host buffer.
 
-        The key is (data pointer, shape, strides, dtype, requested device dtype, tag); an in-place
-        change of the host array is not seen until :meth:`invalidate` is called for it.
+        The key is (data pointer, shape, strides, dtype, requested device dtype, tag) and the entry lives as long as
+        the ndarray that owns the buffer (a weak reference to the root of the view chain), so a freed and reused
+        address can never serve stale weights. An in-place change of the host array is not seen until
+        :meth:`invalidate` is called for it. Anything that is not an ndarray (a list, a buffer object) is converted
+        and uploaded on every call.
         """
         if isinstance(arr, DeviceTensor):
             return arr
+        cacheable = isinstance(arr, np.ndarray)
         a = np.asarray(arr)
         key = (a.__array_interface__["data"][0], a.shape, a.strides, a.dtype.str, dtype, round_tf32, tag)
         hit = self._weights.get(key)
         if hit is not None:
             ref, t = hit
-            if ref() is not None or ref is _NOREF:
+            if ref() is not None:
                 return t
+            self._weights.pop(key)[1].free()   # the owner died: the address may belong to another array now
         host = transform(a) if transform is not None else a
         t = self.upload(host, dtype=dtype, round_tf32=round_tf32 and dtype == "f32")
-        try:
-            ref = weakref.ref(a if a.base is None else a.base)
-        except TypeError:
-            ref = _NOREF
-        self._weights[key] = (ref, t)
+        if not cacheable:
+            return t
+        root = a
+        while isinstance(root.base, np.ndarray):
+            root = root.base
+        self._weights[key] = (weakref.ref(root), t)
         if len(self._weights) > 512:
             self._prune()
         return t
 
+    def register_weight(self, arr) -> None:
+        """Pin an ndarray so that its device copies stay cached until :meth:`invalidate`, even if the caller drops
+        every reference: the device keeps one, which keeps the buffer and therefore the cache key valid."""
+        if not isinstance(arr, np.ndarray):
+            raise TypeError("register_weight expects a numpy.ndarray (other array-likes are converted per call)")
+        self._pinned[arr.__array_interface__["data"][0]] = arr
+
     def _prune(self) -> None:
-        dead = [k for k, (ref, _) in self._weights.items() if ref is not _NOREF and ref() is None]
+        dead = [k for k, (ref, _) in self._weights.items() if ref() is None]
         for k in dead:
             self._weights.pop(k)[1].free()
 
@@ -188,8 +207,10 @@ class Device:
             for _, t in self._weights.values():
                 t.free()
             self._weights.clear()
+            self._pinned.clear()
             return
         ptr = np.asarray(arr).__array_interface__["data"][0]
+        self._pinned.pop(ptr, None)
         for k in [k for k in self._weights if k[0] == ptr]:
             self._weights.pop(k)[1].free()
 
@@ -221,8 +242,8 @@ class Device:
     def pool_stats(self) -> dict:
         out = (C.c_uint64 * 8)()
         self.check(self.lib.grilly_pool_stats(self.ctx, out))
-        names = ["allocations", "frees", "bytes_in_use", "peak_bytes", "pool_reserved_bytes",
-                 "tensor_map_hits", "tensor_map_misses"]
+        names = ["acquired", "released", "bytes_in_use", "peak_bytes", "pool_reserved_bytes",
+                 "tensor_map_hits", "tensor_map_misses", "pool_hits"]
         d = {n: int(out[i]) for i, n in enumerate(names)}
         d["cached_weights"] = len(self._weights)
         return d
@@ -240,9 +261,3 @@ class Device:
         except Exception:
             pass
 
-
-def _noref():
-    return True
-
-
-_NOREF = _noref

@@ -33,7 +33,12 @@ enum {
   GRILLY_ERR_UNSUPPORTED = -6
 };
 
-enum { GRILLY_PREC_TF32 = 0, GRILLY_PREC_BF16 = 1 };
+/* GRILLY_PREC_TF32X3 (grilly_linear, grilly_fused_qkv_projection, grilly_gemm_mnk only): operands are raw fp32; every
+ * value is split into tf32 hi + lo and the product runs over 3K (hi.hi + lo.hi + hi.lo, fp32 accumulate), which gives
+ * fp32-level results (rel-L2 about 3e-6), so that argmax / top-k indices taken from the output agree with the
+ * reference's fp32 arithmetic (fnn-linear.glsl:43-57, gemm_mnk.glsl:48-87). Three times the MMAs, scratch of 3 x the
+ * operand bytes from the context's pool. */
+enum { GRILLY_PREC_TF32 = 0, GRILLY_PREC_BF16 = 1, GRILLY_PREC_TF32X3 = 2 };
 enum { GRILLY_ACT_NONE = 0, GRILLY_ACT_GELU = 1, GRILLY_ACT_SILU = 2, GRILLY_ACT_RELU = 3 };
 enum { GRILLY_NORM_LAYER = 0, GRILLY_NORM_RMS = 1 };
 enum { GRILLY_ELT_GELU = 1, GRILLY_ELT_SILU = 2, GRILLY_ELT_RELU = 3, GRILLY_ELT_ADD = 4, GRILLY_ELT_SWIGLU = 5 };
@@ -59,6 +64,12 @@ const char* grilly_last_error(grilly_ctx* ctx);
 int grilly_set_stream(grilly_ctx* ctx, void* cuda_stream);
 /* backend/core.py:417-418 vkQueueWaitIdle; also reports a device-side wait that gave up as GRILLY_ERR_TIMEOUT */
 int grilly_sync(grilly_ctx* ctx);
+/* Tuning / debug knobs of the kernel selection, normally left alone. They are read from the environment once in
+ * grilly_init (GRILLY_GEMM_GROUP, GRILLY_GEMM_BN, GRILLY_GEMM_PAIR, GRILLY_GEMM_SWAP, GRILLY_ATTN_HPC,
+ * GRILLY_ATTN_GENERAL) and can be changed here per context: name in {gemm_group, gemm_bn, gemm_pair, gemm_swap,
+ * attn_hpc, attn_general}; value 0 (gemm_pair, gemm_swap: -1) restores the default choice. The reference has no
+ * counterpart (its shaders have fixed workgroup sizes, backend/fnn.py:1465-1470). */
+int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value);
 /* number of kernels this context has launched (monotonic) */
 int grilly_launch_count(grilly_ctx* ctx, uint64_t* count);
 
@@ -91,7 +102,8 @@ int grilly_download(grilly_ctx* ctx, void* dst_host, const void* src_dev, size_t
 int grilly_host_alloc(grilly_ctx* ctx, size_t bytes, void** hptr);
 int grilly_host_free(grilly_ctx* ctx, void* hptr);
 /* backend/buffer_pool.py:627-640 get_stats(): out[0]=allocs out[1]=frees out[2]=bytes_in_use
- * out[3]=peak_bytes out[4]=pool_reserved_bytes out[5]=tensor_map_cache_hits out[6]=tensor_map_cache_misses out[7]=0 */
+ * out[3]=peak_bytes out[4]=pool_reserved_bytes out[5]=tensor_map_cache_hits out[6]=tensor_map_cache_misses
+ * out[7]=pool_hits (allocations the pool served from memory it already held; misses = allocs - hits) */
 int grilly_pool_stats(grilly_ctx* ctx, uint64_t out[8]);
 
 /* ---- conversions used when operands enter from NumPy ------------------------------------ */

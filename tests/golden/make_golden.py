@@ -135,7 +135,9 @@ def main_extras(src: str) -> None:
 
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    src = args[0] if args else "/root/reference"
+    if not args:
+        sys.exit("usage: python make_golden.py <path to the grilly source tree> [--extras-only]")
+    src = args[0]
     if "--extras-only" in sys.argv:
         main_extras(src)
     else:

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 import cases
-from conftest import TOL_BF16, TOL_TF32
+from conftest import TOL_BF16, TOL_TF32, index_mismatches
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -31,8 +31,32 @@ def test_config1_full_batch(backend):
     o = backend.attention.flash_attention2(q, k, v, 8, 64)
     ref = O.flash_attention2(q, k, v)
     assert O.rel_l2(o, ref) < TOL_TF32
-    # indices derived from the output: per (b, s, h) argmax over the head dim
-    assert (o.argmax(-1) == ref.argmax(-1)).mean() > 0.995
+    # indices derived from the output (argmax and top-5 over the head dim per (b, s, h)): in tf32 mode they may
+    # differ from the oracle's only where the oracle's own values are closer than the tolerance; count reported
+    for kk in (1, 5):
+        differ, real = index_mismatches(o, ref, kk, TOL_TF32)
+        print(f"tf32 attention cfg 1: top-{kk} differs in {differ} of {o.size // 64} rows, {real} of them not near-ties")
+        assert real == 0
+        assert differ < 0.02 * o.size / 64
+
+
+def test_config1_exact_indices_in_tf32x3_mode(backend_x3):
+    """A 'tf32x3' backend computes attention with fp32 products and sums: values agree with the oracle to fp32
+    accuracy and the argmax / top-5 indices over the head dim are identical at the full batch of 32."""
+    rng = np.random.default_rng(1)
+    q, k, v = (rng.standard_normal((32, 64, 8, 64)).astype(np.float32) for _ in range(3))
+    o = backend_x3.attention.flash_attention2(q, k, v, 8, 64)
+    ref = O.flash_attention2(q, k, v)
+    assert O.rel_l2(o, ref) < 1e-5
+    assert np.array_equal(o.argmax(-1), ref.argmax(-1))
+    assert index_mismatches(o, ref, 5, 1e-5) == (0, 0)
+    # masks, the causal rule and RoPE go through the same fp32 path
+    lens = rng.integers(1, 65, size=32)
+    mask = (np.arange(64)[None, :] < lens[:, None]).astype(np.float32)
+    om = backend_x3.attention.flash_attention2(q, k, v, mask=mask, causal=True)
+    assert O.rel_l2(om, O.flash_attention2(q, k, v, mask=mask, causal=True)) < 1e-5
+    orp = backend_x3.attention.flash_attention2_rope(q[:2], k[:2], v[:2], causal=True)
+    assert O.rel_l2(orp, O.flash_attention2_rope(q[:2], k[:2], v[:2], causal=True)) < 1e-5
 
 
 @pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 32), (2, 17, 3, 32), (2, 128, 12, 32), (1, 129, 2, 64), (2, 300, 4, 64),

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 import cases
-from conftest import TOL_TF32
+from conftest import TOL_TF32, index_mismatches
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -76,12 +76,11 @@ def test_encoder_forward_parity(small_model):
     # top-k identity of the cosine-similarity ranking derived from the embeddings
     sim_g, sim_r = out @ out.T, ref @ ref.T
     np.fill_diagonal(sim_g, -2), np.fill_diagonal(sim_r, -2)
-    top_r = np.argsort(-sim_r, axis=-1)[:, :5]
-    top_g = np.argsort(-sim_g, axis=-1)[:, :5]
-    srt = -np.sort(-sim_r, axis=-1)[:, :6]
-    clear = (np.abs(np.diff(srt, axis=-1)) > 4e-3).all(-1)  # rows whose reference ranking is not a near-tie
-    assert np.array_equal(top_g[clear], top_r[clear])
-    assert np.array_equal(sim_g.argmax(-1)[clear], sim_r.argmax(-1)[clear])
+    # (similarities are O(1) and carry twice the embeddings' tolerance: rankings closer than that cannot be kept)
+    for k in (1, 5):
+        differ, real = index_mismatches(sim_g, sim_r, k, 2 * TOL_TF32)
+        print(f"encoder cosine ranking: top-{k} differs in {differ} of 48 rows, {real} of them not near-ties")
+        assert real == 0
 
 
 def test_chunking_padding_and_batch_invariance(small_model):

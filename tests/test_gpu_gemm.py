@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import cases
-from conftest import TOL_BF16, TOL_TF32
+from conftest import TOL_BF16, TOL_TF32, index_mismatches
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -15,13 +15,13 @@ def test_linear_config0_against_reference_outputs(backend, golden):
     y = backend.fnn.linear(c["x"], c["w"], c["b"])
     assert y.dtype == np.float32 and y.shape == (32, 1536)
     assert O.rel_l2(y, golden["lin_y"]) < TOL_TF32
-    assert np.array_equal(y.argmax(-1), golden["lin_y"].argmax(-1))
+    assert index_mismatches(y, golden["lin_y"], 1, TOL_TF32)[1] == 0
     for name, fn in (("gelu", backend.fnn.fused_linear_gelu), ("silu", backend.fnn.fused_linear_silu),
                      ("relu", backend.fnn.fused_linear_relu)):
         out = fn(c["x"][:8], c["w"], c["b"])
         ref = golden[f"lin_{name}_y8"]
         assert O.rel_l2(out, ref) < TOL_TF32, name
-        assert np.array_equal(out.argmax(-1), ref.argmax(-1)), name
+        assert index_mismatches(out, ref, 1, TOL_TF32)[1] == 0, name
     # 3-D input, ragged sizes (K = 50 is padded to 52 at the boundary), with and without bias
     assert O.rel_l2(backend.fnn.linear(c["x3"], c["w3"], c["b3"]), golden["lin3_y"]) < TOL_TF32
     y3 = backend.fnn.linear(c["x3"], c["w3"])
@@ -35,14 +35,52 @@ def test_linear_config0_batch_4096(backend):
     y = backend.fnn.fused_linear_gelu(x, c["w"], c["b"])
     ref = O.fused_linear_gelu(x, c["w"], c["b"])
     assert O.rel_l2(y, ref) < TOL_TF32
-    # top-5 indices per row: identical wherever the oracle's own ranking is not a near-tie within tf32 noise
-    top_ref = np.argsort(-ref, axis=-1)[:, :5]
-    top_gpu = np.argsort(-y, axis=-1)[:, :5]
-    srt = -np.sort(-ref, axis=-1)[:, :6]
-    clear = (np.abs(np.diff(srt, axis=-1)) > 2e-3 * np.abs(srt[:, :1])).all(-1)
-    assert clear.mean() > 0.5
-    assert np.array_equal(top_gpu[clear], top_ref[clear])
-    assert (y.argmax(-1) == ref.argmax(-1)).mean() > 0.995
+    # default tf32 mode: argmax and top-5 may differ from the fp64 oracle only where the oracle's own values are
+    # closer together than the tf32 tolerance (no tf32 implementation can order those); the count is reported
+    for k in (1, 5):
+        differ, real = index_mismatches(y, ref, k, TOL_TF32)
+        print(f"tf32 linear+GELU 4096 rows: top-{k} differs in {differ} of 4096 rows, {real} of them not near-ties")
+        assert real == 0
+        assert differ < 4096 * 0.02
+
+
+def test_exact_indices_in_tf32x3_mode(backend_x3, golden):
+    """precision='tf32x3' (tf32 hi/lo split products, fp32-level results): argmax and top-5 indices of config 0 at
+    32 and at 4096 rows are IDENTICAL to the reference's, and the values agree to fp32 accuracy."""
+    c = cases.linear_cfg0()
+    y = backend_x3.fnn.linear(c["x"], c["w"], c["b"])
+    assert O.rel_l2(y, golden["lin_y"]) < 1e-5
+    assert np.array_equal(y.argmax(-1), golden["lin_y"].argmax(-1))
+    assert np.array_equal(np.argsort(-y, -1, kind="stable")[:, :5], np.argsort(-golden["lin_y"], -1, kind="stable")[:, :5])
+    yg = backend_x3.fnn.fused_linear_gelu(c["x"], c["w"], c["b"])
+    refg = O.fused_linear_gelu(c["x"], c["w"], c["b"])
+    assert O.rel_l2(yg, refg) < 2e-4          # one tanh.approx in the epilogue: 5e-4 absolute in tanh at most
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((4096, 384)).astype(np.float32)
+    y = backend_x3.fnn.linear(x, c["w"], c["b"])
+    ref = O.linear(x, c["w"], c["b"])
+    assert O.rel_l2(y, ref) < 1e-5
+    assert np.array_equal(y.argmax(-1), ref.argmax(-1))
+    assert np.array_equal(np.argsort(-y, -1, kind="stable")[:, :5], np.argsort(-ref, -1, kind="stable")[:, :5])
+    # a per-call override on a tf32 backend does the same, and gemm has the mode too
+    a, b = rng.standard_normal((300, 200)).astype(np.float32), rng.standard_normal((200, 260)).astype(np.float32)
+    cg = backend_x3.fnn.gemm(a, b)
+    assert O.rel_l2(cg, O.gemm(a, b)) < 1e-5
+    assert np.array_equal(np.argsort(-cg, -1, kind="stable")[:, :5], np.argsort(-O.gemm(a, b), -1, kind="stable")[:, :5])
+
+
+def test_tf32x3_per_call_override(backend):
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((200, 100)).astype(np.float32)       # K = 100: not a multiple of 4 floats
+    w = rng.standard_normal((70, 100)).astype(np.float32)
+    b = rng.standard_normal(70).astype(np.float32)
+    y = backend.fnn.linear(x, w, b, precision="tf32x3")
+    assert O.rel_l2(y, O.linear(x, w, b)) < 1e-5
+    assert O.rel_l2(backend.fnn.linear(x, w, b), O.linear(x, w, b)) > 1e-5   # the plain tf32 product is coarser
+    a, bm = rng.standard_normal((130, 72)).astype(np.float32), rng.standard_normal((72, 258)).astype(np.float32)
+    assert O.rel_l2(backend.fnn.gemm(a, bm, precision="tf32x3"), O.gemm(a, bm)) < 1e-5
+    with pytest.raises(ValueError):
+        backend.fnn.linear(x, w, b, precision="fp64")
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 8, 4), (7, 13, 20), (128, 64, 32), (129, 65, 36), (300, 200, 100), (1000, 1152, 384),
@@ -57,30 +95,38 @@ def test_linear_edge_shapes(backend, M, N, K):
 
 
 @pytest.mark.parametrize("bn", [64, 128, 192, 256])
-def test_every_n_tile(backend, bn, monkeypatch):
-    monkeypatch.setenv("GRILLY_GEMM_BN", str(bn))
-    rng = np.random.default_rng(bn)
-    x = rng.standard_normal((700, 384)).astype(np.float32)
-    w = (rng.standard_normal((1000, 384)) / 20).astype(np.float32)
-    assert O.rel_l2(backend.fnn.fused_linear_relu(x, w), O.fused_linear_relu(x, w)) < TOL_TF32
+def test_every_n_tile(backend, bn):
+    backend.device.set_tuning("gemm_bn", bn)
+    try:
+        rng = np.random.default_rng(bn)
+        x = rng.standard_normal((700, 384)).astype(np.float32)
+        w = (rng.standard_normal((1000, 384)) / 20).astype(np.float32)
+        assert O.rel_l2(backend.fnn.fused_linear_relu(x, w), O.fused_linear_relu(x, w)) < TOL_TF32
+    finally:
+        backend.device.set_tuning("gemm_bn", 0)
 
 
 @pytest.mark.parametrize("M,N,K", [(300, 520, 40), (1000, 384, 96), (2049, 1536, 384), (256, 256, 8)])
-def test_cta_pair_kernel(backend, backend_bf16, M, N, K, monkeypatch):
+def test_cta_pair_kernel(backend, backend_bf16, M, N, K):
     """The cta_group::2 kernel (two CTAs share one MMA, 256 x 256 tiles) on ragged shapes it would not be picked
     for by default: partial token tiles, a feature count that leaves the second CTA of a pair without rows."""
-    monkeypatch.setenv("GRILLY_GEMM_PAIR", "1")
-    rng = np.random.default_rng(M + N + K)
-    x = rng.standard_normal((M, K)).astype(np.float32)
-    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
-    b = rng.standard_normal(N).astype(np.float32)
-    assert O.rel_l2(backend.fnn.linear(x, w, b), O.linear(x, w, b)) < TOL_TF32
-    assert O.rel_l2(backend.fnn.fused_linear_gelu(x, w, b), O.fused_linear_gelu(x, w, b)) < TOL_TF32
-    assert O.rel_l2(backend_bf16.fnn.fused_linear_silu(x, w), O.fused_linear_silu(x, w)) < TOL_BF16
-    # the same launch through the single-CTA kernel gives the same numbers bit for bit (same MMA order per output)
-    y_pair = backend.fnn.linear(x, w, b)
-    monkeypatch.setenv("GRILLY_GEMM_PAIR", "0")
-    assert np.array_equal(y_pair, backend.fnn.linear(x, w, b))
+    backend.device.set_tuning("gemm_pair", 1)
+    backend_bf16.device.set_tuning("gemm_pair", 1)
+    try:
+        rng = np.random.default_rng(M + N + K)
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+        b = rng.standard_normal(N).astype(np.float32)
+        assert O.rel_l2(backend.fnn.linear(x, w, b), O.linear(x, w, b)) < TOL_TF32
+        assert O.rel_l2(backend.fnn.fused_linear_gelu(x, w, b), O.fused_linear_gelu(x, w, b)) < TOL_TF32
+        assert O.rel_l2(backend_bf16.fnn.fused_linear_silu(x, w), O.fused_linear_silu(x, w)) < TOL_BF16
+        # the same launch through the single-CTA kernel gives the same numbers bit for bit (same MMA order per output)
+        y_pair = backend.fnn.linear(x, w, b)
+        backend.device.set_tuning("gemm_pair", 0)
+        assert np.array_equal(y_pair, backend.fnn.linear(x, w, b))
+    finally:
+        backend.device.set_tuning("gemm_pair", -1)
+        backend_bf16.device.set_tuning("gemm_pair", -1)
 
 
 def test_linear_is_deterministic_and_weight_cache_is_used(backend):
