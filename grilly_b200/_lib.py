@@ -54,6 +54,7 @@ SIGNATURES = {
     "grilly_free": [_vp, _vp],
     "grilly_upload": [_vp, _vp, _vp, _sz],
     "grilly_download": [_vp, _vp, _vp, _sz],
+    "grilly_copy_2d": [_vp, _vp, _sz, _vp, _sz, _sz, _sz],
     "grilly_host_alloc": [_vp, _sz, _pp],
     "grilly_host_free": [_vp, _vp],
     "grilly_pool_stats": [_vp, C.POINTER(C.c_uint64)],

@@ -169,16 +169,19 @@ class FNN(_Namespace):
 
     def fused_layernorm_linear(self, x, gamma, beta, weights, bias=None, eps=1e-5, mode="layer"):
         """Linear(LayerNorm(x)) (or RMSNorm with mode='rms'): fused-layernorm-linear.glsl:67-128. One row-statistics
-        kernel plus the GEMM on the raw rows; gamma/beta are folded into the weights once and cached."""
-        if self._bf16:
-            raise NotImplementedError("fused_layernorm_linear runs in tf32 mode; in bf16 mode call layernorm then linear")
+        kernel plus the GEMM on the raw rows with the normalisation finished in its epilogue; gamma/beta are folded
+        into the weights once and cached (``invalidate(weights)`` after an in-place change). Rows whose mean is far
+        from zero against their spread (|mean| > 1.5 std) are normalised first instead, so the result keeps the
+        precision's tolerance for any input. Runs in the backend's precision (tf32 or bf16)."""
+        bf16 = self._bf16
         N, K = (int(s) for s in weights.shape)
         x_shape = tuple(x.shape)
         if x_shape[-1] != K:
             raise ValueError(f"input feature size {x_shape[-1]} does not match weights {tuple(weights.shape)}")
-        if K % 4:
-            raise ValueError("fused_layernorm_linear needs in_features to be a multiple of 4")
-        key = ("lnfold", id(weights), id(gamma), id(beta), id(bias), mode)
+        if K % (8 if bf16 else 4):
+            raise ValueError("fused_layernorm_linear needs in_features * element size to be a multiple of 16 bytes")
+        prec = L.PREC_BF16 if bf16 else L.PREC_TF32
+        key = ("lnfold", id(weights), id(gamma), id(beta), id(bias), mode, prec)
         fold = self._b._folds.get(key)
         if fold is not None:
             self._b._folds.move_to_end(key)
@@ -187,9 +190,9 @@ class FNN(_Namespace):
             gd = self.dev.upload(np.asarray(gamma, np.float32)) if gamma is not None else None
             bd = self.dev.upload(np.asarray(beta, np.float32)) if (beta is not None and mode == "layer") else None
             cd = self.dev.upload(np.asarray(bias, np.float32)) if bias is not None else None
-            wf, cs, bf = self.dev.empty((N, K)), self.dev.empty((N,)), self.dev.empty((N,))
+            wf, cs, bf = self.dev.empty((N, K), "bf16" if bf16 else "f32"), self.dev.empty((N,)), self.dev.empty((N,))
             self.dev.check(self.lib.grilly_fold_layernorm_weights(self.ctx, _p(wd), _p(gd), _p(bd), _p(cd), _p(wf), _p(cs),
-                                                                  _p(bf), N, K, L.PREC_TF32))
+                                                                  _p(bf), N, K, prec))
             self.dev.sync()
             for t in (wd, gd, bd, cd):
                 if t is not None:
@@ -199,13 +202,16 @@ class FNN(_Namespace):
             while len(self._b._folds) > self._b.MAX_FOLDS:   # least recently used first
                 self._b._folds.popitem(last=False)
         wf, cs, bf = fold[:3]
-        xd, host = self._act_in(x, mma_operand=False)  # statistics need the unrounded rows
+        if isinstance(x, DeviceTensor):
+            xd, host = x, False
+        else:
+            xd, host = self.dev.upload(x, "bf16" if bf16 else "f32"), True   # raw rows: the statistics need them unrounded
         M = xd.size // K
         y = self.dev.empty((M, N))
         stats = self.dev.empty((2 * M,))
         self.dev.check(self.lib.grilly_layernorm_linear(self.ctx, _p(xd), _p(wf), _p(cs), _p(bf), _p(y), _p(stats), M, N, K,
                                                         float(eps), L.NORM_RMS if mode == "rms" else L.NORM_LAYER,
-                                                        L.ACT_NONE, L.PREC_TF32, 0))
+                                                        L.ACT_NONE, prec, 0))
         out = self._out(y, host, x_shape[:-1] + (N,))
         stats.free()
         return out

@@ -108,9 +108,9 @@ int grilly_init(int device, grilly_ctx** out) {
     uint64_t thresh = UINT64_MAX;
     ok = cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &thresh) == cudaSuccess;
   }
-  ok = ok && cudaMalloc(&ctx->err_dev, 2 * sizeof(int)) == cudaSuccess;  // [0] status word, [1] attention work counter
-  ok = ok && cudaMemset(ctx->err_dev, 0, 2 * sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMallocHost(&ctx->err_host, sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&ctx->err_dev, 4 * sizeof(int)) == cudaSuccess;  // [0] status word, [1] attention work counter, [2] layernorm_linear's max |mean|/std
+  ok = ok && cudaMemset(ctx->err_dev, 0, 4 * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMallocHost(&ctx->err_host, 2 * sizeof(int)) == cudaSuccess;   // [0] status, [1] mirror of word [2]
   if (!ok) {
     cudaGetLastError();
     delete ctx;
@@ -298,6 +298,17 @@ int grilly_download(grilly_ctx* ctx, void* dst, const void* src, size_t bytes) {
   return check_device_status(ctx);
 }
 
+int grilly_copy_2d(grilly_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes,
+                   size_t rows) {
+  CTX_GUARD(ctx);
+  if (!dst_dev || !src_dev) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "copy_2d: null pointer");
+  if (width_bytes > dst_pitch || width_bytes > src_pitch) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "copy_2d: width exceeds a pitch");
+  if (width_bytes == 0 || rows == 0) return GRILLY_OK;
+  // cudaMemcpyDefault: either side may be memory of another GPU mapped into this process; the copy engines move it
+  GB_CUDA_CHECK(ctx, cudaMemcpy2DAsync(dst_dev, dst_pitch, src_dev, src_pitch, width_bytes, rows, cudaMemcpyDefault, ctx->stream));
+  return GRILLY_OK;
+}
+
 int grilly_host_alloc(grilly_ctx* ctx, size_t bytes, void** hptr) {
   CTX_GUARD(ctx);
   if (!hptr) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "host_alloc: null output pointer");
@@ -387,21 +398,29 @@ int grilly_fold_layernorm_weights(grilly_ctx* ctx, const float* w, const float* 
   return launch_fold_ln(ctx, w, gamma, beta, bias, wf, col_sum, bias_f, N, K, precision == GRILLY_PREC_BF16);
 }
 
-int grilly_layernorm_linear(grilly_ctx* ctx, const float* x, const void* wf, const float* col_sum, const float* bias_f,
-                            void* y, float* stats, int M, int N, int K, float eps, int norm_mode, int act, int precision,
-                            int flags) {
-  CTX_GUARD(ctx);
-  int rc = check_prec(ctx, precision);
-  if (rc) return rc;
-  if (!x || !wf || !y || !stats) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: null operand");
-  if (norm_mode == GRILLY_NORM_LAYER && !col_sum) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: col_sum is required");
-  if (precision == GRILLY_PREC_BF16)
-    return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "layernorm_linear: x is fp32, so only tf32 mode is supported; in bf16 mode use layernorm(OUT_BF16) + linear");
-  // row statistics into the scratch, then the GEMM on the raw rows with the normalisation finished in its epilogue
+}  // extern "C"
+
+namespace gb {
+// Linear(Norm(x)) shared by grilly_layernorm_linear and its no-allocation variant. mean / rstd: scratch for M floats
+// each. The folded form runs the GEMM on the RAW rows and finishes y = rstd (acc - mean col_sum) + bias' in the
+// epilogue; its rounding error grows with |row mean| / (row std), so in LayerNorm mode the statistics kernel also
+// reports the largest such ratio and beyond GRILLY_LNLINEAR_MAX_MEAN_OVER_STD the rows are normalised first
+// (x^ = (x - mean) rstd, rounded for the MMA, into scratch of M x K elements) and the GEMM runs on x^ with the same
+// folded weights: y = x^ W'^T + bias'. RMSNorm has no mean term and always takes the folded form.
+int layernorm_linear_impl(grilly_ctx* ctx, const void* x, const void* wf, const float* col_sum, const float* bias_f, void* y,
+                          float* mean, float* rstd, int M, int N, int K, float eps, int norm_mode, int act, int precision,
+                          int flags, bool may_allocate) {
+  const bool bf16 = precision == GRILLY_PREC_BF16;
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: M, N, K must be positive");
+  if (act < GRILLY_ACT_NONE || act > GRILLY_ACT_RELU) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: unknown activation");
+  if (norm_mode != GRILLY_NORM_LAYER && norm_mode != GRILLY_NORM_RMS) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: unknown norm mode");
+  unsigned* ratio_dev = reinterpret_cast<unsigned*>(ctx->err_dev + 2);
+  const bool layer = norm_mode == GRILLY_NORM_LAYER;
+  if (layer) GB_CUDA_CHECK(ctx, cudaMemsetAsync(ratio_dev, 0, sizeof(unsigned), ctx->stream));
   NormArgs n{};
-  n.x = x; n.rows = M; n.F = K; n.eps = eps; n.mode = norm_mode;
-  n.mean_out = stats; n.rstd_out = stats + M;
-  rc = launch_norm(ctx, n);
+  n.x = static_cast<const float*>(x); n.x_bf16 = bf16 ? 1 : 0; n.rows = M; n.F = K; n.eps = eps; n.mode = norm_mode;
+  n.mean_out = mean; n.rstd_out = rstd; n.ratio_max = layer ? ratio_dev : nullptr;
+  int rc = launch_norm(ctx, n);
   if (rc) return rc;
   GemmArgs a{};
   a.M = M; a.N = N; a.K = K;
@@ -410,10 +429,51 @@ int grilly_layernorm_linear(grilly_ctx* ctx, const float* x, const void* wf, con
   a.out_bf16 = (flags & GRILLY_FLAG_OUT_BF16) ? 1 : 0;
   a.round_tf32 = (flags & GRILLY_FLAG_ROUND_TF32) ? 1 : 0;
   a.act = act;
-  a.row_rstd = stats + M;
-  a.row_mean = norm_mode == GRILLY_NORM_LAYER ? stats : nullptr;
+  if (layer) {
+    // one small read-back decides the form (the only synchronisation of this entry point; RMS mode has none)
+    int* mirror = ctx->err_host + 1;
+    GB_CUDA_CHECK(ctx, cudaMemcpyAsync(mirror, ratio_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    GB_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    float ratio;
+    std::memcpy(&ratio, mirror, sizeof(float));
+    if (!(ratio <= GRILLY_LNLINEAR_MAX_MEAN_OVER_STD)) {   // also taken for NaN statistics
+      if (!may_allocate)
+        return set_error(ctx, GRILLY_ERR_UNSUPPORTED,
+                         "layernorm_linear_noalloc: a row mean is " + std::to_string(ratio) + " standard deviations from zero, beyond the "
+                         "folded form's accuracy envelope; grilly_layernorm_linear handles such rows (it normalises them into scratch first)");
+      const size_t elt = bf16 ? 2 : 4;
+      void* xn = nullptr;
+      if (cudaMallocAsync(&xn, static_cast<size_t>(M) * K * elt, ctx->stream) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(ctx, GRILLY_ERR_OOM, "layernorm_linear: no memory for the normalised rows");
+      }
+      NormArgs m = n;
+      m.mean_out = nullptr; m.rstd_out = nullptr; m.ratio_max = nullptr;
+      m.y = xn; m.out_bf16 = bf16 ? 1 : 0; m.round_tf32 = bf16 ? 0 : 1;   // gamma and beta already live in the folded weights
+      rc = launch_norm(ctx, m);
+      if (!rc) rc = launch_gemm(ctx, bf16, false, xn, wf, a, 0);
+      cudaFreeAsync(xn, ctx->stream);
+      return rc;
+    }
+  }
+  a.row_rstd = rstd;
+  a.row_mean = layer ? mean : nullptr;
   a.col_sum = col_sum;
-  return launch_gemm(ctx, false, false, x, wf, a, 0);
+  return launch_gemm(ctx, bf16, false, x, wf, a, 0);
+}
+}  // namespace gb
+
+extern "C" {
+
+int grilly_layernorm_linear(grilly_ctx* ctx, const void* x, const void* wf, const float* col_sum, const float* bias_f,
+                            void* y, float* stats, int M, int N, int K, float eps, int norm_mode, int act, int precision,
+                            int flags) {
+  CTX_GUARD(ctx);
+  int rc = check_prec(ctx, precision);
+  if (rc) return rc;
+  if (!x || !wf || !y || !stats) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: null operand");
+  if (norm_mode == GRILLY_NORM_LAYER && !col_sum) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: col_sum is required");
+  return layernorm_linear_impl(ctx, x, wf, col_sum, bias_f, y, stats, stats + M, M, N, K, eps, norm_mode, act, precision, flags, true);
 }
 
 int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int M, int K, int N, int precision,

@@ -64,6 +64,9 @@ struct NormArgs {
   int out_bf16;
   int round_tf32;
   int reverse;            // walk the rows from the last to the first (the rows a producer wrote last are still in L2)
+  int x_bf16;             // x (and residual) are bf16 instead of fp32
+  unsigned* ratio_max;    // optional: atomic max over rows of |mean| * rstd as fp32 bits (the cancellation measure of
+                          // the folded LayerNorm->linear form); the caller zeroes it first
 };
 
 struct EmbedArgs {

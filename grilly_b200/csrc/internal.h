@@ -112,6 +112,10 @@ int launch_split_rows(grilly_ctx* ctx, const float* x, float* out, float* norm2,
                       bool lo_second);
 int linear_tf32x3(grilly_ctx* ctx, const float* x, const float* w, GemmArgs& args);
 int gemm_mnk_tf32x3(grilly_ctx* ctx, const float* a, const float* b, GemmArgs& args);
+// api.cu: Linear(Norm(x)) shared by the allocating and the no-allocation entry points
+int layernorm_linear_impl(grilly_ctx* ctx, const void* x, const void* wf, const float* col_sum, const float* bias_f, void* y,
+                          float* mean, float* rstd, int M, int N, int K, float eps, int norm_mode, int act, int precision,
+                          int flags, bool may_allocate);
 // attention.cu
 int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, const void* v, long long ld_q, long long ld_k,
                      long long ld_v, long long total_rows, AttnArgs& args);

@@ -13,6 +13,12 @@
 //    contexts on the same device) race on it; calls issued on one stream are ordered and safe;
 //  * the array keeps whatever the previous call left. Nothing here relies on it starting at zero: the
 //    statistics kernel writes rows [0, M) before the GEMM reads exactly those rows;
+//  * in LayerNorm mode the result is computed by the folded form only (GEMM on the raw rows, normalisation finished
+//    in the epilogue), which is accurate while no row mean is more than GRILLY_LNLINEAR_MAX_MEAN_OVER_STD standard
+//    deviations from zero. The allocating entry point switches to normalise-then-GEMM beyond that, which needs
+//    M x K scratch; this one cannot, and returns GRILLY_ERR_UNSUPPORTED for such inputs (y is not written);
+//  * the first launch of each kernel variant makes the CUDA runtime load its code, which takes device memory for
+//    the code itself; a caller that must not see any allocation issues one warm-up call per shape class first;
 //  * the first call on each device looks up the array's device address (cudaGetSymbolAddress). Make that first
 //    call before any stream capture is started on the stream.
 #include "args.h"
@@ -79,19 +85,6 @@ extern "C" int grilly_layernorm_linear_noalloc(grilly_ctx* ctx, const float* x_d
   int rc = scratch_for_device(ctx, &stats);
   if (rc) return rc;
 
-  gb::NormArgs n{};
-  n.x = x_dev; n.rows = M; n.F = K; n.eps = eps; n.mode = norm_mode;
-  n.mean_out = stats; n.rstd_out = stats + kMaxRows;
-  if ((rc = gb::launch_norm(ctx, n))) return rc;
-  gb::GemmArgs a{};
-  a.M = M; a.N = N; a.K = K;
-  a.bias = bias_f_dev;
-  a.out = y_dev; a.ld_out = N;
-  a.out_bf16 = (flags & GRILLY_FLAG_OUT_BF16) ? 1 : 0;
-  a.round_tf32 = (flags & GRILLY_FLAG_ROUND_TF32) ? 1 : 0;
-  a.act = act;
-  a.row_rstd = stats + kMaxRows;
-  a.row_mean = norm_mode == GRILLY_NORM_LAYER ? stats : nullptr;
-  a.col_sum = col_sum_dev;
-  return gb::launch_gemm(ctx, false, false, x_dev, wf_dev, a, 0);
+  return gb::layernorm_linear_impl(ctx, x_dev, wf_dev, col_sum_dev, bias_f_dev, y_dev, stats, stats + kMaxRows, M, N, K, eps,
+                                   norm_mode, act, precision, flags, /*may_allocate=*/false);
 }

@@ -15,10 +15,11 @@ static inline int grid_for(long long work_items, int per_block, int num_sms, int
 int launch_norm(grilly_ctx* ctx, const NormArgs& a) {
   if (a.rows <= 0 || a.F <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm: rows and features must be positive");
   const int grid = grid_for(a.rows, 8, ctx->num_sms);
-  const bool aligned = (a.F % 4 == 0) && !(reinterpret_cast<uintptr_t>(a.x) & 15) && !(reinterpret_cast<uintptr_t>(a.y) & 15) &&
+  const bool aligned = !a.x_bf16 && (a.F % 4 == 0) && !(reinterpret_cast<uintptr_t>(a.x) & 15) && !(reinterpret_cast<uintptr_t>(a.y) & 15) &&
                        !(reinterpret_cast<uintptr_t>(a.residual) & 15) && !(reinterpret_cast<uintptr_t>(a.gamma) & 15) &&
                        !(reinterpret_cast<uintptr_t>(a.beta) & 15);
-  const double nbytes = static_cast<double>(a.rows) * a.F * (4.0 + (a.residual ? 4.0 : 0.0) + (a.y ? (a.out_bf16 ? 2.0 : 4.0) : 0.0));
+  const double in_elt = a.x_bf16 ? 2.0 : 4.0;
+  const double nbytes = static_cast<double>(a.rows) * a.F * (in_elt + (a.residual ? in_elt : 0.0) + (a.y ? (a.out_bf16 ? 2.0 : 4.0) : 0.0));
   const int pi = prof_begin(ctx, PROF_NORM, 8.0 * a.rows * a.F, nbytes);
   if (aligned && a.F <= 128 * 3) norm_rows_kernel<3><<<grid, 256, 0, ctx->stream>>>(a);
   else if (aligned && a.F <= 128 * 8) norm_rows_kernel<8><<<grid, 256, 0, ctx->stream>>>(a);

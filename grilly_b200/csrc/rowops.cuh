@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const NormArgs a) {
     if (lane == 0) {
       if (a.mean_out) a.mean_out[row] = mean;
       if (a.rstd_out) a.rstd_out[row] = rstd_n;
+      if (a.ratio_max) atomicMax(a.ratio_max, __float_as_uint(fabsf(mean) * rstd_n));   // non-negative floats order like their bits
     }
     if (!a.y) continue;
 #pragma unroll
@@ -101,13 +102,19 @@ __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a
        row += static_cast<long long>(gridDim.x) * warps_per_block) {
     const float* xp = a.x + row * a.F;
     const float* rp = a.residual ? a.residual + row * a.F : nullptr;
+    const __nv_bfloat16* xh = reinterpret_cast<const __nv_bfloat16*>(a.x) + row * a.F;
+    const __nv_bfloat16* rh = a.residual ? reinterpret_cast<const __nv_bfloat16*>(a.residual) + row * a.F : nullptr;
+    auto in = [&](int i) {
+      if (a.x_bf16) return __bfloat162float(xh[i]) + (a.residual ? __bfloat162float(rh[i]) : 0.f);
+      return xp[i] + (rp ? rp[i] : 0.f);
+    };
     float s = 0.f;
-    for (int i = lane; i < a.F; i += 32) s += xp[i] + (rp ? rp[i] : 0.f);
+    for (int i = lane; i < a.F; i += 32) s += in(i);
     float mean = 0.f;
     if (a.mode == NORM_LAYER) mean = warp_sum(s) / static_cast<float>(a.F);
     float sq = 0.f;
     for (int i = lane; i < a.F; i += 32) {
-      const float d = xp[i] + (rp ? rp[i] : 0.f) - mean;
+      const float d = in(i) - mean;
       sq += d * d;
     }
     const float var = warp_sum(sq) / static_cast<float>(a.F);
@@ -116,10 +123,11 @@ __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a
     if (lane == 0) {
       if (a.mean_out) a.mean_out[row] = mean;
       if (a.rstd_out) a.rstd_out[row] = rstd;
+      if (a.ratio_max) atomicMax(a.ratio_max, __float_as_uint(fabsf(mean) * rstd));
     }
     if (!a.y) continue;
     for (int i = lane; i < a.F; i += 32) {
-      float o = (xp[i] + (rp ? rp[i] : 0.f) - mean) * rstd * (a.gamma ? a.gamma[i] : 1.f) +
+      float o = (in(i) - mean) * rstd * (a.gamma ? a.gamma[i] : 1.f) +
                 ((a.beta && a.mode == NORM_LAYER) ? a.beta[i] : 0.f);
       if (a.round_tf32) o = round_to_tf32(o);
       if (a.out_bf16) reinterpret_cast<__nv_bfloat16*>(a.y)[row * a.F + i] = __float2bfloat16(o);

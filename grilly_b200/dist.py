@@ -215,7 +215,8 @@ class FusedNsplit:
         torch = self.torch
         if not hasattr(self, "_side"):
             self._side = torch.cuda.Stream(device=self.device)
-            self._peers = {r: self.handle.get_buffer(r, (self.M, self.N), torch.float32) for r in range(self.world) if r != self.rank}
+            # base addresses of the peers' C: peer memory is only ever a destination of copy-engine copies here
+            self._peer_ptrs = {r: int(self.handle.buffer_ptrs[r]) for r in range(self.world) if r != self.rank}
         self.handle.barrier()
         cur = torch.cuda.current_stream(self.device)
         c0, c1 = self.rank * self.n_loc, (self.rank + 1) * self.n_loc
@@ -229,9 +230,15 @@ class FusedNsplit:
                                                         ptr, 1, r1 - r0, self.K, self.n_loc, C.c_longlong(self.N), self.prec)
             self.dev.check(rc)
             self._side.wait_stream(cur)
-            with torch.cuda.stream(self._side):
-                for peer in self._peers.values():
-                    peer[r0:r1, c0:c1].copy_(self.c[r0:r1, c0:c1])
+            off = (r0 * self.N + c0) * 4
+            self.dev.set_stream(self._side.cuda_stream)
+            try:
+                for base in self._peer_ptrs.values():
+                    self.dev.check(self.dev.lib.grilly_copy_2d(self.dev.ctx, C.c_void_p(base + off), self.N * 4,
+                                                               C.c_void_p(self.c.data_ptr() + off), self.N * 4,
+                                                               self.n_loc * 4, r1 - r0))
+            finally:
+                self.dev.set_stream(self.bridge.stream.cuda_stream)
         cur.wait_stream(self._side)
         self.handle.barrier()
         return self.c

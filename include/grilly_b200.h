@@ -98,6 +98,11 @@ int grilly_free(grilly_ctx* ctx, void* dptr);
 int grilly_upload(grilly_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 /* backend/core.py:352-360 _download_buffer (returns after the copy has completed) */
 int grilly_download(grilly_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+/* Strided device-to-device copy of `rows` rows of `width_bytes` on the context's stream (cudaMemcpy2DAsync); dst or
+ * src may be peer-mapped memory of another GPU. Used to move row slabs of a column block of C between GPUs without
+ * handing peer memory to any kernel. No counterpart in the reference (no multi-GPU code, CHANGELOG.md:75). */
+int grilly_copy_2d(grilly_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes,
+                   size_t rows);
 /* pinned host staging memory for the two calls above */
 int grilly_host_alloc(grilly_ctx* ctx, size_t bytes, void** hptr);
 int grilly_host_free(grilly_ctx* ctx, void* hptr);
@@ -133,8 +138,18 @@ int grilly_fold_layernorm_weights(grilly_ctx* ctx, const float* w_dev, const flo
                                   int K, int precision);
 /* y = Linear(Norm(x)): row statistics kernel + GEMM with the normalisation finished in the epilogue.
  * fused-layernorm-linear.glsl:67-128 (mode GRILLY_NORM_LAYER); snn-rmsnorm.glsl:34-75 then fnn-linear (GRILLY_NORM_RMS).
- * x fp32 [M,K]; stats_dev is scratch for 2*M floats (mean, rstd). */
-int grilly_layernorm_linear(grilly_ctx* ctx, const float* x_dev, const void* wf_dev, const float* col_sum_dev,
+ * x [M,K] is fp32 (precision TF32) or bf16 (precision BF16; fold the weights with the same precision); stats_dev is
+ * scratch for 2*M floats (mean, rstd).
+ * Accuracy envelope: the GEMM consumes the RAW rows and the epilogue computes rstd * (acc - mean * col_sum), which
+ * loses accuracy by cancellation when a row's mean is large against its standard deviation (rel-L2 grows like
+ * sqrt(1 + (mean/std)^2) times the plain product's error). In LayerNorm mode the statistics kernel therefore also
+ * reports the largest |mean|/std of the call; the entry point reads it back (ONE stream synchronisation) and, above
+ * GRILLY_LNLINEAR_MAX_MEAN_OVER_STD, normalises the rows into pool scratch (M x K elements) and runs the GEMM on
+ * those instead, as fused-layernorm-linear.glsl:102-126 orders the operations. Either way the result is within the
+ * precision's tolerance (2e-3 tf32, 1e-2 bf16). RMS mode has no mean term: always the folded form, no
+ * synchronisation. */
+#define GRILLY_LNLINEAR_MAX_MEAN_OVER_STD 1.5f
+int grilly_layernorm_linear(grilly_ctx* ctx, const void* x_dev, const void* wf_dev, const float* col_sum_dev,
                             const float* bias_f_dev, void* y_dev, float* stats_dev, int M, int N, int K, float eps,
                             int norm_mode, int act, int precision, int flags);
 /* Same result as grilly_layernorm_linear, for callers that cannot allocate device memory while they run an op

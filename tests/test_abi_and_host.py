@@ -118,3 +118,115 @@ def test_chunk_plan(lib):
     assert list(bounds) == [0, 1, 2, 4] and total == 312
     bad = np.array([3, -1], np.int32)
     assert lib.grilly_plan_chunks(bad.ctypes.data, 2, 0, bounds.ctypes.data, cu.ctypes.data, None) < 0
+
+
+def test_importing_the_package_maps_no_cuda_library():
+    """The CPU arm of the benchmark imports grilly_b200.encoder for the weight container only: that import must
+    not load libgrilly_b200.so (checked in a fresh interpreter through /proc/self/maps)."""
+    import subprocess
+    import sys
+
+    code = ("import grilly_b200, grilly_b200.encoder; "
+            "print(any('libgrilly_b200' in line for line in open('/proc/self/maps')))")
+    out = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, check=True)
+    assert out.stdout.strip() == "False"
+
+
+def test_pool_stats_have_the_reference_keys():
+    """backend.fnn.buffer_pool.get_stats() as tutorials/06_transformer_components.py:142-145 reads it
+    (keys of BufferPool.get_stats, backend/buffer_pool.py:627-640)."""
+    from grilly_b200.compute import _PoolView
+
+    class FakeDevice:
+        def pool_stats(self):
+            return {"acquired": 40, "released": 38, "bytes_in_use": 1024, "peak_bytes": 4096, "pool_reserved_bytes": 8192,
+                    "tensor_map_hits": 7, "tensor_map_misses": 3, "pool_hits": 30, "cached_weights": 2}
+
+    pool = _PoolView(FakeDevice())
+    stats = pool.get_stats()
+    line = f"\nBuffer pool: {stats['total_acquired']} ops, {stats['hit_rate']:.1%} hit rate"   # the tutorial's line
+    assert line == "\nBuffer pool: 40 ops, 75.0% hit rate"
+    for key in ("hits", "misses", "allocations", "evictions", "total_acquired", "total_released", "total_pooled_memory",
+                "buckets", "hit_rate", "vma_enabled"):
+        assert key in stats
+    assert stats["hits"] + stats["misses"] == stats["total_acquired"] and stats["allocations"] == stats["misses"] == 10
+    assert stats["total_pooled_memory"] == 8192 - 1024 and stats["cached_weights"] == 2
+
+
+class _FakeTensor:
+    def __init__(self, host):
+        self.host, self.freed = np.array(host, copy=True), False
+        self.shape = self.host.shape
+
+    def free(self):
+        self.freed = True
+
+
+def _fake_device():
+    from grilly_b200.device import Device
+
+    dev = object.__new__(Device)
+    dev._weights, dev._pinned, dev._closed = {}, {}, True
+    dev.uploads = 0
+
+    def upload(arr, dtype="f32", round_tf32=False):
+        dev.uploads += 1
+        return _FakeTensor(arr)
+
+    dev.upload = upload
+    return dev
+
+
+def test_weight_cache_follows_the_owner_of_the_buffer():
+    """Device.weight caches by buffer identity while the owning ndarray lives, never serves a freed address, and
+    does not cache what is not an ndarray."""
+    import gc
+
+    dev = _fake_device()
+    w = np.arange(12, dtype=np.float32).reshape(3, 4)
+    t1 = dev.weight(w)
+    assert dev.weight(w) is t1 and dev.uploads == 1
+    assert dev.weight(w.T) is not t1 and dev.weight(w.T) is dev.weight(w.T)      # a view: own entry, alive with its root
+    n_before = dev.uploads
+    assert dev.weight([[1.0, 2.0], [3.0, 4.0]]) is not dev.weight([[1.0, 2.0], [3.0, 4.0]])   # lists are never cached
+    assert dev.uploads == n_before + 2 and all(isinstance(k[0], int) for k in dev._weights)
+    # the owner dies: the entry is dropped instead of being served to whoever gets the address next
+    key = next(k for k in dev._weights if k[0] == w.__array_interface__["data"][0] and k[1] == (3, 4))
+    del w
+    gc.collect()
+    ref, stale = dev._weights[key]
+    assert ref() is None
+    dev._prune()
+    assert key not in dev._weights and stale.freed
+    # a pinned array survives its last outside reference until invalidate()
+    p = np.ones((2, 2), np.float32)
+    ptr = p.__array_interface__["data"][0]
+    dev.register_weight(p)
+    tp = dev.weight(p)
+    del p
+    gc.collect()
+    assert any(k[0] == ptr and dev._weights[k][0]() is not None for k in dev._weights)
+    dev.invalidate(dev._pinned[ptr])
+    assert tp.freed and ptr not in dev._pinned
+    with pytest.raises(TypeError):
+        dev.register_weight([1.0, 2.0])
+
+
+def test_invalidate_drops_folded_layernorm_weights():
+    """Compute.invalidate(W) forgets the LayerNorm->linear folds built from W (or from its gamma/beta/bias), and the
+    fold cache is bounded."""
+    from collections import OrderedDict
+
+    from grilly_b200.compute import Compute
+
+    b = object.__new__(Compute)
+    b.device = _fake_device()
+    b._folds = OrderedDict()
+    w1, w2, g = np.ones((4, 4), np.float32), np.ones((4, 4), np.float32), np.ones(4, np.float32)
+    b._folds[("lnfold", id(w1), id(g), 0, 0, "layer")] = ("wf", "cs", "bf", w1, g, None, None)
+    b._folds[("lnfold", id(w2), id(g), 0, 0, "layer")] = ("wf", "cs", "bf", w2, g, None, None)
+    b.invalidate(w1)
+    assert len(b._folds) == 1 and next(iter(b._folds.values()))[3] is w2
+    b.invalidate(g)              # shared gamma: the remaining fold goes too
+    assert not b._folds
+    assert Compute.MAX_FOLDS >= 8

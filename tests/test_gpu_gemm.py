@@ -182,6 +182,38 @@ def test_fused_layernorm_linear(backend, mode):
     assert np.array_equal(out, out2)
 
 
+@pytest.mark.parametrize("ratio", [0.0, 1.0, 4.0, 16.0])
+def test_fused_layernorm_linear_accuracy_envelope(backend, backend_bf16, ratio):
+    """Row means of `ratio` standard deviations (fused-layernorm-linear.glsl:102-126 normalises before the product,
+    so the reference has no cancellation): small ratios take the folded form, large ones are normalised first; both
+    stay inside the tolerance, in tf32 and in bf16."""
+    rng = np.random.default_rng(80 + int(ratio))
+    x = (rng.standard_normal((700, 384)) + ratio * (1 + 0.2 * rng.standard_normal((700, 1)))).astype(np.float32)
+    g, bt = (1 + 0.1 * rng.standard_normal(384)).astype(np.float32), (0.1 * rng.standard_normal(384)).astype(np.float32)
+    w, b = (rng.standard_normal((512, 384)) * 0.05).astype(np.float32), rng.standard_normal(512).astype(np.float32)
+    ref = O.fused_layernorm_linear(x, g, bt, w, b)
+    err = O.rel_l2(backend.fnn.fused_layernorm_linear(x, g, bt, w, b), ref)
+    err16 = O.rel_l2(backend_bf16.fnn.fused_layernorm_linear(x, g, bt, w, b), ref)
+    print(f"|mean|/std = {ratio}: rel-L2 {err:.2e} (tf32), {err16:.2e} (bf16)")
+    assert err < TOL_TF32 and err16 < TOL_BF16
+    # RMSNorm has no mean term: always folded, any offset
+    ref_rms = O.linear(O.rmsnorm(x, g), w, b)
+    assert O.rel_l2(backend.fnn.fused_layernorm_linear(x, g, None, w, b, mode="rms"), ref_rms) < TOL_TF32
+    assert O.rel_l2(backend_bf16.fnn.fused_layernorm_linear(x, g, None, w, b, mode="rms"), ref_rms) < TOL_BF16
+
+
+def test_invalidate_refreshes_folded_weights(backend):
+    rng = np.random.default_rng(81)
+    x = rng.standard_normal((64, 128)).astype(np.float32)
+    g, bt = np.ones(128, np.float32), np.zeros(128, np.float32)
+    w = (rng.standard_normal((96, 128)) * 0.1).astype(np.float32)
+    y1 = backend.fnn.fused_layernorm_linear(x, g, bt, w)
+    w *= 3
+    backend.invalidate(w)
+    y2 = backend.fnn.fused_layernorm_linear(x, g, bt, w)
+    assert O.rel_l2(y2, 3 * y1) < 1e-5
+
+
 def test_fused_swiglu(backend):
     rng = np.random.default_rng(9)
     x = rng.standard_normal((200, 256)).astype(np.float32)
@@ -269,34 +301,28 @@ def test_gemm_mnk_golden_and_sweep(backend, golden):
         assert c.shape == (m, n) and O.rel_l2(c, O.gemm(a, b)) < TOL_TF32
 
 
-def test_gemm_mnk_full_size_property(backend):
-    """At the sweep's large sizes the O(N^3) oracle is too slow: check C v = A (B v) in float64 for random v
-    (a checksum that any wrong tile, k-block or swizzle would break) on the operands the tensor core sees."""
-    n = 8192
-    rng = np.random.default_rng(4 + 13)
-    a, b = rng.standard_normal((n, n)).astype(np.float32), rng.standard_normal((n, n)).astype(np.float32)
-    c = backend.fnn.gemm(a, b)
-    v = rng.standard_normal((n, 4))
-    lhs = c.astype(np.float64) @ v
-    rhs = a.astype(np.float64) @ (b.astype(np.float64) @ v)
-    assert O.rel_l2(lhs, rhs) < TOL_TF32
-    # row and column checksums localise an error to a tile
-    u = rng.standard_normal((4, n))
-    assert O.rel_l2(u @ c.astype(np.float64), (u @ a.astype(np.float64)) @ b.astype(np.float64)) < TOL_TF32
-
-
-def test_gemm_mnk_largest_sweep_size(backend):
-    """M = N = K = 16384, the largest size of the sweep, through the same checksum property (1 GiB per matrix)."""
-    n = 16384
-    rng = np.random.default_rng(4 + 14)
+@pytest.mark.parametrize("n", [4096, 8192, 16384])
+def test_gemm_mnk_full_size_property(backend, backend_bf16, n):
+    """At the sweep's large sizes the O(N^3) oracle is too slow: check C v = A (B v) and u C = (u A) B for random
+    u, v (checksums that any wrong tile, k-block or swizzle would break, and that localise an error to a tile), in
+    both modes of the sweep. The checks use float32 matrix-vector products (error ~1e-5, far below the tolerances),
+    which keeps them to seconds at 16384 (1 GiB per matrix)."""
+    rng = np.random.default_rng(4 + int(np.log2(n)))
     a = rng.standard_normal((n, n), dtype=np.float32)
     b = rng.standard_normal((n, n), dtype=np.float32)
-    c = backend.fnn.gemm(a, b)
-    # float32 matrix-vector products here (error ~1e-5, far below the tolerance) keep the check to a few seconds
-    v = rng.standard_normal((n, 2)).astype(np.float32)
-    assert O.rel_l2(c @ v, a @ (b @ v)) < TOL_TF32
-    u = rng.standard_normal((2, n)).astype(np.float32)
-    assert O.rel_l2(u @ c, (u @ a) @ b) < TOL_TF32
+    v = rng.standard_normal((n, 3)).astype(np.float32)
+    u = rng.standard_normal((3, n)).astype(np.float32)
+    want_v, want_u = a @ (b @ v), (u @ a) @ b
+    for be, tol in ((backend, TOL_TF32), (backend_bf16, TOL_BF16)):
+        c = be.fnn.gemm(a, b)
+        assert c.shape == (n, n) and c.dtype == np.float32
+        assert O.rel_l2(c @ v, want_v) < tol
+        assert O.rel_l2(u @ c, want_u) < tol
+        # the checksums would pass for a C that is right on average: a sample of entries against float64 dot products
+        rows, cols = rng.integers(0, n, size=64), rng.integers(0, n, size=64)
+        exact = np.einsum("ik,ki->i", a[rows].astype(np.float64), b[:, cols].astype(np.float64))
+        assert O.rel_l2(c[rows, cols], exact) < 3 * tol
+        del c
 
 
 def test_bf16_mode(backend_bf16):
