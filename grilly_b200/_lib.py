@@ -66,6 +66,7 @@ SIGNATURES = {
     "grilly_fold_layernorm_weights": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "grilly_layernorm_linear": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _i],
     "grilly_layernorm_linear_noalloc": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _i],
+    "grilly_linear_layernorm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i],
     "grilly_gemm_mnk": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i],
     "grilly_flash_attention": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _f, _i, _i, _f, _f, _i, _i],
     "grilly_attention_scores": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f],

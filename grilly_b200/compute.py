@@ -131,6 +131,45 @@ class FNN(_Namespace):
         """silu(x @ W.T + b): backend/fnn.py:2214-2303."""
         return self._linear(x, weights, bias, L.ACT_SILU, precision=precision)
 
+    def linear_residual_layernorm(self, x, weights, bias, residual, gamma=None, beta=None, eps=1e-5):
+        """LayerNorm(x @ W.T + b + residual) * gamma + beta: the post-LN step of a BERT layer, which the reference
+        spells ``layer_norm(linear(attn_out) + x)`` (utils/vulkan_sentence_transformer.py:997-1011, 1018-1033). For
+        128, 256, 384 or 512 output features it is one kernel (the statistics are taken in the GEMM's epilogue and
+        the pre-norm sum never reaches memory); other widths run the GEMM and the LayerNorm kernel."""
+        bf16 = self._bf16
+        N, K = (int(s) for s in weights.shape)
+        x_shape = tuple(x.shape)
+        if x_shape[-1] != K:
+            raise ValueError(f"input feature size {x_shape[-1]} does not match weights {tuple(weights.shape)}")
+        if residual is not None and tuple(residual.shape) != x_shape[:-1] + (N,):
+            raise ValueError(f"residual must have shape {x_shape[:-1] + (N,)}")
+        for name, v in (("bias", bias), ("gamma", gamma), ("beta", beta)):
+            if v is not None and int(np.prod(v.shape)) != N:
+                raise ValueError(f"{name} has {int(np.prod(v.shape))} entries, expected {N}")
+        elt = 2 if bf16 else 4
+        kpad = (-K) % (16 // elt)
+        w_transform, w_tag = None, ""
+        if kpad:
+            if isinstance(x, DeviceTensor):
+                raise ValueError("device-resident operands need in_features * element size to be a multiple of 16 bytes")
+            x = np.pad(np.asarray(x, dtype=np.float32).reshape(-1, K), ((0, 0), (0, kpad)))
+            w_transform = lambda a: np.pad(np.asarray(a, dtype=np.float32), ((0, 0), (0, kpad)))  # noqa: E731
+            w_tag = f"|kpad{kpad}"
+        xd, host = self._act_in(x)
+        wd = self.dev.weight(weights, "bf16" if bf16 else "f32", round_tf32=True, transform=w_transform, tag="w" + w_tag)
+        rd = None
+        if residual is not None:
+            rd = residual if isinstance(residual, DeviceTensor) else self.dev.upload(residual, "bf16" if bf16 else "f32")
+        M = xd.size // (K + kpad)
+        y = self.dev.empty((M, N))
+        scratch = self.dev.empty((M, N))
+        self.dev.check(self.lib.grilly_linear_layernorm(self.ctx, _p(xd), _p(wd), _p(self._vec(bias)), _p(rd), _p(self._vec(gamma)),
+                                                        _p(self._vec(beta)), _p(y), _p(scratch), M, N, K + kpad, float(eps),
+                                                        L.PREC_BF16 if bf16 else L.PREC_TF32, 0))
+        out = self._out(y, host, x_shape[:-1] + (N,))
+        scratch.free()
+        return out
+
     def fused_qkv_projection(self, x, w_qkv, b_qkv=None, num_heads=None, head_dim=None, precision=None):
         """x @ [Wq;Wk;Wv].T + [bq;bk;bv] -> (..., 3*H*D), column blocks Q, K, V: fused-qkv-projection.glsl:48-74."""
         if num_heads is not None and head_dim is not None and w_qkv.shape[0] != 3 * num_heads * head_dim:

@@ -128,6 +128,7 @@ int grilly_init(int device, grilly_ctx** out) {
   ctx->tune.gemm_swap = env_int("GRILLY_GEMM_SWAP", -1);
   ctx->tune.attn_hpc = env_int("GRILLY_ATTN_HPC", 0);
   ctx->tune.attn_general = getenv("GRILLY_ATTN_GENERAL") != nullptr ? 1 : 0;
+  ctx->tune.fused_ln = env_int("GRILLY_FUSED_LN", 1);
   *out = ctx;
   return GRILLY_OK;
 }
@@ -165,6 +166,7 @@ int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value) {
   else if (n == "gemm_swap") ctx->tune.gemm_swap = value;
   else if (n == "attn_hpc") ctx->tune.attn_hpc = value;
   else if (n == "attn_general") ctx->tune.attn_general = value;
+  else if (n == "fused_ln") ctx->tune.fused_ln = value;
   else return set_error(ctx, GRILLY_ERR_INVALID_ARG, "set_tuning: unknown knob '" + n + "'");
   return GRILLY_OK;
 }
@@ -474,6 +476,34 @@ int grilly_layernorm_linear(grilly_ctx* ctx, const void* x, const void* wf, cons
   if (!x || !wf || !y || !stats) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: null operand");
   if (norm_mode == GRILLY_NORM_LAYER && !col_sum) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "layernorm_linear: col_sum is required");
   return layernorm_linear_impl(ctx, x, wf, col_sum, bias_f, y, stats, stats + M, M, N, K, eps, norm_mode, act, precision, flags, true);
+}
+
+int grilly_linear_layernorm(grilly_ctx* ctx, const void* x, const void* w, const float* bias, const void* residual,
+                            const float* gamma, const float* beta, void* y, float* scratch, int M, int N, int K, float eps,
+                            int precision, int flags) {
+  CTX_GUARD(ctx);
+  int rc = check_prec(ctx, precision);
+  if (rc) return rc;
+  if (!x || !w || !y) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "linear_layernorm: null operand");
+  const bool bf16 = precision == GRILLY_PREC_BF16;
+  GemmLnArgs a{};
+  a.M = M; a.N = N; a.K = K;
+  a.bias = bias; a.residual = residual; a.ld_res = N; a.gamma = gamma; a.beta = beta; a.eps = eps;
+  a.out = y; a.ld_out = N;
+  a.out_bf16 = (flags & GRILLY_FLAG_OUT_BF16) ? 1 : 0;
+  a.round_tf32 = (flags & GRILLY_FLAG_ROUND_TF32) ? 1 : 0;
+  if (ctx->tune.fused_ln && M > 0 && K > 0 && gemm_ln_supported(bf16, N, K, a)) return launch_gemm_ln(ctx, bf16, x, w, a);
+  // other widths: the GEMM writes the fp32 sum (bias and residual in its epilogue), the row kernel normalises it
+  if (!scratch) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "linear_layernorm: this shape needs the M x N fp32 scratch");
+  GemmArgs g{};
+  g.M = M; g.N = N; g.K = K;
+  g.bias = bias; g.residual = static_cast<const float*>(residual); g.ld_res = N; g.residual_bf16 = (residual && bf16) ? 1 : 0;
+  g.out = scratch; g.ld_out = N;
+  if ((rc = launch_gemm(ctx, bf16, false, x, w, g, 0))) return rc;
+  NormArgs n{};
+  n.x = scratch; n.gamma = gamma; n.beta = beta; n.y = y; n.rows = M; n.F = N; n.eps = eps; n.mode = NORM_LAYER;
+  n.out_bf16 = a.out_bf16; n.round_tf32 = a.round_tf32;
+  return launch_norm(ctx, n);
 }
 
 int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int M, int K, int N, int precision,

@@ -33,6 +33,23 @@ struct GemmArgs {
   int* err;               // device status word
 };
 
+// y = LayerNorm(x W^T + bias + residual) * gamma + beta in one kernel (gemm_ln.cuh)
+struct GemmLnArgs {
+  int M, N, K;
+  int num_tiles, num_k_blocks;
+  const float* bias;       // [N] or null
+  const void* residual;    // [M][ld_res] fp32 (tf32 mode) or bf16 (bf16 mode), or null
+  long long ld_res;
+  const float* gamma;      // [N] or null (= 1)
+  const float* beta;       // [N] or null (= 0)
+  float eps;
+  void* out;               // [M][ld_out] fp32 or bf16
+  long long ld_out;
+  int out_bf16;            // bf16 mode only
+  int round_tf32;
+  int* err;
+};
+
 struct AttnArgs {
   int B, S, H, D;
   const int* cu_seqlens;   // [B+1] packed rows, or null for the padded layout

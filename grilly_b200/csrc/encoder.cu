@@ -5,11 +5,10 @@
 // Per layer (T = packed token rows, F = hidden):
 //   qkv  = x Wqkv^T + bqkv                      tcgen05 GEMM            [T, 3F]
 //   attn = softmax(q k^T / sqrt(d)) v           tcgen05 flash-attention [T, F]
-//   t    = attn Wo^T + bo + x                   GEMM, residual epilogue [T, F]
-//   x2   = LayerNorm(t)                         row kernel
+//   x2   = LayerNorm(attn Wo^T + bo + x)        GEMM with residual + LayerNorm epilogue [T, F]
 //   h    = gelu(x2 W1^T + b1)                   GEMM, GELU epilogue     [T, ffn]
-//   t    = h W2^T + b2 + x2                     GEMM, residual epilogue
-//   x    = LayerNorm(t)
+//   x    = LayerNorm(h W2^T + b2 + x2)          GEMM with residual + LayerNorm epilogue
+// (hidden sizes other than 128/256/384/512 run each of the two fused steps as GEMM + row kernel)
 // Sentences are processed in chunks of at most `chunk_tokens` rows through all
 // layers, reusing one set of activation buffers, so a chunk's activations stay
 // in the 126 MB L2 between producer and consumer kernels.
@@ -125,6 +124,10 @@ static int enc_linear(grilly_encoder* e, const void* x, const void* w, const flo
   return launch_gemm(e->ctx, e->bf16, false, x, w, a, 0);
 }
 
+// y = LayerNorm(x W^T + bias + residual): one kernel where the width allows it, else GEMM into t + row kernel
+static int enc_linear_norm(grilly_encoder* e, const void* x, const void* w, const float* bias, const void* residual,
+                           const float* g, const float* b, void* y, int M, int N, int K, bool out_fp32);
+
 static int enc_norm(grilly_encoder* e, const float* x, const float* g, const float* b, void* y, int rows, bool out_fp32) {
   NormArgs n{};
   n.x = x; n.gamma = g; n.beta = b; n.y = y; n.rows = rows; n.F = e->cfg.hidden; n.eps = e->cfg.layer_ln_eps;
@@ -133,6 +136,20 @@ static int enc_norm(grilly_encoder* e, const float* x, const float* g, const flo
   n.round_tf32 = e->bf16 ? 0 : 1;
   n.reverse = 1;   // the GEMM before it wrote the last rows last: start where L2 still holds them (about 4 % of this kernel)
   return launch_norm(e->ctx, n);
+}
+
+static int enc_linear_norm(grilly_encoder* e, const void* x, const void* w, const float* bias, const void* residual,
+                           const float* g, const float* b, void* y, int M, int N, int K, bool out_fp32) {
+  GemmLnArgs a{};
+  a.M = M; a.N = N; a.K = K;
+  a.bias = bias; a.residual = residual; a.ld_res = N; a.gamma = g; a.beta = b; a.eps = e->cfg.layer_ln_eps;
+  a.out = y; a.ld_out = N;
+  a.out_bf16 = (e->bf16 && !out_fp32) ? 1 : 0;
+  a.round_tf32 = e->bf16 ? 0 : 1;
+  if (e->ctx->tune.fused_ln && gemm_ln_supported(e->bf16, N, K, a)) return launch_gemm_ln(e->ctx, e->bf16, x, w, a);
+  int rc = enc_linear(e, x, w, bias, residual, e->t, M, N, K, ACT_NONE, true);
+  if (rc) return rc;
+  return enc_norm(e, e->t, g, b, y, M, out_fp32);
 }
 
 // Runs one chunk: sequences [b0, b1) whose packed rows are [0, rows) of the workspace.
@@ -166,12 +183,11 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
     ctx->attn_flops_hint = 4.0 * H * D * sum_len2;  // valid (query, key) pairs only
     const char* qkv = reinterpret_cast<const char*>(e->qkv);
     if ((rc = launch_attention(ctx, e->bf16, qkv, qkv + F * act, qkv + 2 * F * act, 3LL * F, 3LL * F, 3LL * F, rows, at))) return rc;
-    if ((rc = enc_linear(e, e->attn, wo, L.bo, e->x, e->t, rows, F, F, ACT_NONE, true))) return rc;
-    if ((rc = enc_norm(e, e->t, L.ln1_g, L.ln1_b, e->x2, rows, false))) return rc;
+    if ((rc = enc_linear_norm(e, e->attn, wo, L.bo, e->x, L.ln1_g, L.ln1_b, e->x2, rows, F, F, false))) return rc;
     if ((rc = enc_linear(e, e->x2, w1, L.b1, nullptr, e->h, rows, c.ffn, F, ACT_GELU_TANH, false))) return rc;
-    if ((rc = enc_linear(e, e->h, w2, L.b2, e->x2, e->t, rows, F, c.ffn, ACT_NONE, true))) return rc;
     // the last LayerNorm of the model feeds the pooling, which reads fp32
-    if ((rc = enc_norm(e, e->t, L.ln2_g, L.ln2_b, (last && e->bf16) ? static_cast<void*>(e->xf) : e->x, rows, last && e->bf16))) return rc;
+    if ((rc = enc_linear_norm(e, e->h, w2, L.b2, e->x2, L.ln2_g, L.ln2_b, (last && e->bf16) ? static_cast<void*>(e->xf) : e->x, rows, F,
+                              c.ffn, last && e->bf16))) return rc;
   }
   PoolArgs p{};
   p.x = final_hidden; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;

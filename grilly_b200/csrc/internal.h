@@ -70,6 +70,7 @@ struct grilly_ctx {
     int gemm_swap = -1;      // 0/1: never/always the swapped orientation for `linear`
     int attn_hpc = 0;        // heads per work unit of the short attention kernel
     int attn_general = 0;    // 1: always the general attention kernel
+    int fused_ln = 1;        // 0: linear + LayerNorm as two launches even where the one-kernel form exists
   } tune;
   // RoPE tables, keyed by (S, D, base, scaling)
   struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };
@@ -99,6 +100,7 @@ int get_tmap_2d(grilly_ctx* ctx, int dtype, const void* ptr, uint64_t inner, uin
                 uint32_t box_inner, uint32_t box_outer, CUtensorMap* out, int swizzle = TM_SW128);
 
 struct GemmArgs;
+struct GemmLnArgs;
 struct AttnArgs;
 struct NormArgs;
 struct EmbedArgs;
@@ -107,6 +109,10 @@ struct PoolArgs;
 // gemm.cu
 int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, const void* b, GemmArgs& args, int force_bn);
 int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, GemmArgs& args, void* const* extra, int n_extra);
+// y = LayerNorm(x W^T + bias + residual) in one kernel (csrc/gemm_ln.cuh); supported for out_features in
+// {128, 256, 384, 512}
+bool gemm_ln_supported(bool bf16, int N, int K, const GemmLnArgs& a);
+int launch_gemm_ln(grilly_ctx* ctx, bool bf16, const void* x, const void* w, GemmLnArgs& args);
 // tf32x3.cu: fp32-accurate products through tf32 hi/lo splits (K' = 3K)
 int launch_split_rows(grilly_ctx* ctx, const float* x, float* out, float* norm2, long long rows, int dim, int dim_pad,
                       bool lo_second);

@@ -66,8 +66,8 @@ int grilly_set_stream(grilly_ctx* ctx, void* cuda_stream);
 int grilly_sync(grilly_ctx* ctx);
 /* Tuning / debug knobs of the kernel selection, normally left alone. They are read from the environment once in
  * grilly_init (GRILLY_GEMM_GROUP, GRILLY_GEMM_BN, GRILLY_GEMM_PAIR, GRILLY_GEMM_SWAP, GRILLY_ATTN_HPC,
- * GRILLY_ATTN_GENERAL) and can be changed here per context: name in {gemm_group, gemm_bn, gemm_pair, gemm_swap,
- * attn_hpc, attn_general}; value 0 (gemm_pair, gemm_swap: -1) restores the default choice. The reference has no
+ * GRILLY_ATTN_GENERAL, GRILLY_FUSED_LN) and can be changed here per context: name in {gemm_group, gemm_bn, gemm_pair, gemm_swap,
+ * attn_hpc, attn_general, fused_ln}; value 0 (gemm_pair, gemm_swap: -1) restores the default choice. The reference has no
  * counterpart (its shaders have fixed workgroup sizes, backend/fnn.py:1465-1470). */
 int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value);
 /* number of kernels this context has launched (monotonic) */
@@ -163,6 +163,17 @@ int grilly_layernorm_linear(grilly_ctx* ctx, const void* x_dev, const void* wf_d
 int grilly_layernorm_linear_noalloc(grilly_ctx* ctx, const float* x_dev, const void* wf_dev, const float* col_sum_dev,
                                     const float* bias_f_dev, void* y_dev, int M, int N, int K, float eps, int norm_mode,
                                     int act, int precision, int flags);
+/* y = LayerNorm(x W^T + bias + residual) * gamma + beta: the post-LN step of a BERT layer, which the reference
+ * runs as linear, add, layer_norm (utils/vulkan_sentence_transformer.py:997-1011 and 1018-1033; fnn-linear.glsl,
+ * fnn-residual.glsl, fnn-layernorm.glsl:44-103; biased variance, eps inside the square root).
+ * x [M,K] and W [N,K] are fp32 (TF32) or bf16 (BF16); residual [M,N] has the operands' type; bias, gamma, beta fp32
+ * (each may be NULL). For N in {128, 256, 384, 512} this is ONE kernel (a 128-row tile holds whole output rows in
+ * tensor memory, the statistics are taken in the GEMM's epilogue and the pre-norm sum never reaches memory);
+ * scratch_dev may then be NULL. Other widths run the GEMM into scratch_dev (M*N floats) and the row kernel after it.
+ * Flags: GRILLY_FLAG_ROUND_TF32, GRILLY_FLAG_OUT_BF16 (BF16 mode only). Asynchronous. */
+int grilly_linear_layernorm(grilly_ctx* ctx, const void* x_dev, const void* w_dev, const float* bias_dev, const void* residual_dev,
+                            const float* gamma_dev, const float* beta_dev, void* y_dev, float* scratch_dev, int M, int N, int K,
+                            float eps, int precision, int flags);
 /* C[M,N] = A[M,K] * B[K,N], all row-major.  VulkanFNN.gemm backend/fnn.py:104-166 (gemm_mnk.glsl:35-88). */
 int grilly_gemm_mnk(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int M, int K, int N,
                     int precision, int flags);
