@@ -58,7 +58,7 @@ int get_tmap_2d(grilly_ctx* ctx, int dtype, const void* ptr, uint64_t inner, uin
   CUtensorMap m;
   CUresult r = g_encode(&m, dtype == TM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                         const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle == TM_SW128_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        swizzle == TM_SW128_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : swizzle == TM_SWNONE ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(ctx, GRILLY_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
   ctx->tmap_misses++;
@@ -129,6 +129,7 @@ int grilly_init(int device, grilly_ctx** out) {
   ctx->tune.attn_hpc = env_int("GRILLY_ATTN_HPC", 0);
   ctx->tune.attn_general = getenv("GRILLY_ATTN_GENERAL") != nullptr ? 1 : 0;
   ctx->tune.fused_ln = env_int("GRILLY_FUSED_LN", 1);
+  ctx->tune.ln_deep = env_int("GRILLY_LN_DEEP", -1);
   *out = ctx;
   return GRILLY_OK;
 }
@@ -167,6 +168,7 @@ int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value) {
   else if (n == "attn_hpc") ctx->tune.attn_hpc = value;
   else if (n == "attn_general") ctx->tune.attn_general = value;
   else if (n == "fused_ln") ctx->tune.fused_ln = value;
+  else if (n == "ln_deep") ctx->tune.ln_deep = value;
   else return set_error(ctx, GRILLY_ERR_INVALID_ARG, "set_tuning: unknown knob '" + n + "'");
   return GRILLY_OK;
 }

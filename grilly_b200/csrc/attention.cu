@@ -47,12 +47,15 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
   constexpr int ELT = kBf16 ? 2 : 4;
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
   const uint64_t width = static_cast<uint64_t>(args.H) * D;
-  CUtensorMap tq, tk, tv;
+  AttnShortMaps maps;
   int rc;
-  if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_q * ELT, 128 / ELT, ATTN_TILE, &tq))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_k * ELT, 128 / ELT, ATTN_TILE, &tk))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_v * ELT, 128 / ELT, ATTN_TILE, &tv,
-                        kBf16 ? TM_SW128 : TM_SW128_ATOM32))) return rc;
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t rows = 32u * (i + 1);
+    if ((rc = get_tmap_2d(ctx, dtype, q, width, total_rows, ld_q * ELT, 128 / ELT, rows, &maps.q[i]))) return rc;
+    if ((rc = get_tmap_2d(ctx, dtype, k, width, total_rows, ld_k * ELT, 128 / ELT, rows, &maps.k[i]))) return rc;
+    if ((rc = get_tmap_2d(ctx, dtype, v, width, total_rows, ld_v * ELT, 128 / ELT, rows, &maps.v[i],
+                          kBf16 ? TM_SW128 : TM_SW128_ATOM32))) return rc;
+  }
   args.err = ctx->err_dev;
   auto kern = flash_attn_short_kernel<D, kBf16>;
   if (!ctx->smem_attr_done.count(reinterpret_cast<const void*>(kern))) {
@@ -75,7 +78,7 @@ static int launch_short(grilly_ctx* ctx, const void* q, const void* k, const voi
   int* counter = ctx->err_dev + 1;                     // the slots of all CTAs take their units from this counter
   GB_CUDA_CHECK(ctx, cudaMemsetAsync(counter, 0, sizeof(int), ctx->stream));
   const int pi = prof_begin(ctx, PROF_ATTN, flops, bytes);
-  kern<<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tq, tk, tv, args, hpc, head_groups, static_cast<int>(units), counter);
+  kern<<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(maps, args, hpc, head_groups, static_cast<int>(units), counter);
   prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());

@@ -38,6 +38,13 @@ struct AttnShortCfg {
   static constexpr int TMEM_COLS = 512;
 };
 
+// Tensor maps of Q, K and V with boxes of 32, 64, 96 and 128 token rows: a unit fetches only as many rows as its
+// sentence has (rounded up to 32), not the whole 128-row tile, so that the copy engine moves about the algorithmic
+// bytes and a short sentence's tiles arrive sooner (its chain of dependent steps starts with these loads).
+struct AttnShortMaps {
+  CUtensorMap q[4], k[4], v[4];
+};
+
 // barrier over the `count` threads that name the same id (ids 1..15; 0 is __syncthreads)
 __device__ __forceinline__ void named_barrier(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -45,8 +52,7 @@ __device__ __forceinline__ void named_barrier(int id, int count) {
 
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(AttnShortCfg<D, kBf16>::THREADS, 1)
-flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                        const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args, int heads_per_unit,
+flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnArgs args, int heads_per_unit,
                         int head_groups, int total_units, int* work_counter) {
   using Cfg = AttnShortCfg<D, kBf16>;
   constexpr int ELT = Cfg::ELT;
@@ -82,7 +88,7 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     mbar_init(bar_or, 4);
     if (slot == 0) {
       *abort_flag = 0;
-      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      for (int i = 0; i < 4; ++i) { prefetch_tmap(&maps.q[i]); prefetch_tmap(&maps.k[i]); prefetch_tmap(&maps.v[i]); }
     }
     fence_mbar_init();
   }
@@ -140,19 +146,26 @@ flash_attn_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         // -------------------------------------------------------- TMA + MMA issuer
         const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
         // Q and K of the next head (pair) may be fetched as soon as S is complete, V once P V is complete
+        // boxes of n_s rows (32, 64, 96 or 128): rows beyond them keep whatever the slot's previous unit left, which
+        // no MMA result that is stored depends on (S columns and P V k-steps stop at n_s, query rows >= L are not stored)
+        const int bi = (n_s >> 5) - 1;
+        const uint32_t box_bytes = static_cast<uint32_t>(n_s) * 128u * NCH;   // one of Q, K, V
+        const CUtensorMap* mq = &maps.q[bi];
+        const CUtensorMap* mk = &maps.k[bi];
+        const CUtensorMap* mv = &maps.v[bi];
         auto load_qk = [&](int h) {
-          mbar_expect_tx(bar_qk, 2 * TILE_BYTES);
+          mbar_expect_tx(bar_qk, 2 * box_bytes);
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
-            tma_load_2d(tiles + c * ATTN_CHUNK_BYTES, &tmap_q, bar_qk, h * D + c * CHE, row0);
-            tma_load_2d(tiles + TILE_BYTES + c * ATTN_CHUNK_BYTES, &tmap_k, bar_qk, h * D + c * CHE, row0);
+            tma_load_2d(tiles + c * ATTN_CHUNK_BYTES, mq, bar_qk, h * D + c * CHE, row0);
+            tma_load_2d(tiles + TILE_BYTES + c * ATTN_CHUNK_BYTES, mk, bar_qk, h * D + c * CHE, row0);
           }
         };
         auto load_v = [&](int h) {
-          mbar_expect_tx(bar_v, TILE_BYTES);
+          mbar_expect_tx(bar_v, box_bytes);
 #pragma unroll
           for (int c = 0; c < NCH; ++c)
-            tma_load_2d(tiles + 2 * TILE_BYTES + c * ATTN_CHUNK_BYTES, &tmap_v, bar_v, h * D + c * CHE, row0);
+            tma_load_2d(tiles + 2 * TILE_BYTES + c * ATTN_CHUNK_BYTES, mv, bar_v, h * D + c * CHE, row0);
         };
         load_qk(h_begin);
         load_v(h_begin);

@@ -205,45 +205,75 @@ int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, 
 // ---- y = LayerNorm(x W^T + bias + residual) in one kernel (gemm_ln.cuh)
 bool gemm_ln_supported(bool bf16, int N, int K, const GemmLnArgs& a) {
   const int elt = bf16 ? 2 : 4;
-  if (N != 128 && N != 256 && N != 384 && N != 512) return false;          // whole rows in one accumulator
+  if (N != 128 && N != 256 && N != 384 && N != 512) return false;          // whole rows in the pair's two accumulators
   if ((static_cast<long long>(K) * elt) % 16 != 0) return false;
   if (a.out_bf16 && !bf16) return false;
   if (a.residual && ((a.ld_res * elt) % 16 != 0 || (reinterpret_cast<uintptr_t>(a.residual) & 15))) return false;
-  if ((reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.gamma) & 15) || (reinterpret_cast<uintptr_t>(a.beta) & 15)) return false;
   if ((reinterpret_cast<uintptr_t>(a.out) & 15) || (a.ld_out * (a.out_bf16 ? 2 : 4)) % 16 != 0) return false;
   return true;
 }
 
-template <int NCHUNK, bool kBf16>
-static int launch_ln_one(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
-  using Cfg = GemmLnCfg<NCHUNK>;
+template <int NCHUNK, bool kBf16, bool kDeep>
+static int launch_ln_cfg(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
+  using Cfg = GemmLnCfg<NCHUNK, kBf16, kDeep>;
   constexpr int ELT = kBf16 ? 2 : 4;
   constexpr int BK = 128 / ELT;
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
-  CUtensorMap ta, tb, to;
+  CUtensorMap ta, tb, tr, to;
   int rc;
   if ((rc = get_tmap_2d(ctx, dtype, x, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &ta))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, Cfg::N / 2, &tb))) return rc;
+  if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, Cfg::NHALF, &tb))) return rc;
+  // residual boxes of 128 rows x 32 columns: fp32 rows are 128 bytes (swizzled like the output), bf16 rows 64 bytes (plain)
+  if (!args.residual) tr = ta;
+  else if ((rc = get_tmap_2d(ctx, dtype, args.residual, args.N, args.M, static_cast<uint64_t>(args.ld_res) * ELT, 32, 128, &tr,
+                             kBf16 ? TM_SWNONE : TM_SW128))) return rc;
   if (args.out_bf16) to = ta;   // bf16 results leave through vector stores; the kernel does not touch this map
   else if ((rc = get_tmap_2d(ctx, TM_F32, args.out, args.N, args.M, static_cast<uint64_t>(args.ld_out) * 4, 32, 32, &to))) return rc;
   args.num_tiles = (args.M + 127) / 128;
   args.num_k_blocks = (args.K + BK - 1) / BK;
   args.err = ctx->err_dev;
-  auto kern = gemm_rowln_tcgen05_kernel<NCHUNK, kBf16>;
-  if (!ctx->smem_attr_done.count(reinterpret_cast<const void*>(kern))) {
+  auto kern = gemm_rowln_tcgen05_kernel<NCHUNK, kBf16, kDeep>;
+  const void* key = reinterpret_cast<const void*>(kern);
+  if (!ctx->smem_attr_done.count(key)) {
     GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    ctx->smem_attr_done.insert(reinterpret_cast<const void*>(kern));
+    ctx->smem_attr_done.insert(key);
   }
-  const int grid = args.num_tiles < ctx->num_sms ? args.num_tiles : ctx->num_sms;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(GEMM_LN_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = ctx->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  auto found = ctx->max_clusters.find(key);
+  if (found == ctx->max_clusters.end()) {
+    int n = 0;
+    cfg.gridDim = dim3(2 * (ctx->num_sms / 2), 1, 1);
+    GB_CUDA_CHECK(ctx, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    if (n <= 0) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "linear_layernorm: no CTA pair fits on this GPU");
+    found = ctx->max_clusters.emplace(key, n).first;
+  }
+  const int pairs = args.num_tiles < found->second ? args.num_tiles : found->second;
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
   const double mn = static_cast<double>(args.M) * args.N;
   const double bytes = static_cast<double>(ELT) * (static_cast<double>(args.M) * args.K + static_cast<double>(args.N) * args.K) +
                        12.0 * args.N + mn * (args.out_bf16 ? 2.0 : 4.0) + (args.residual ? mn * ELT : 0.0);
   const int pi = prof_begin(ctx, PROF_GEMM, 2.0 * mn * args.K, bytes);
-  kern<<<grid, GEMM_LN_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, to, args);
+  GB_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, tr, to, args));
   prof_end(ctx, pi);
   ctx->launches++;
-  GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;
+}
+
+template <int NCHUNK, bool kBf16>
+static int launch_ln_one(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
+  // a long K loop wants operand bytes in flight, a short one wants epilogue buffers (see GemmLnCfg)
+  const bool deep = ctx->tune.ln_deep >= 0 ? ctx->tune.ln_deep != 0 : static_cast<long long>(args.K) * (kBf16 ? 2 : 4) >= 3072;
+  return deep ? launch_ln_cfg<NCHUNK, kBf16, true>(ctx, x, w, args) : launch_ln_cfg<NCHUNK, kBf16, false>(ctx, x, w, args);
 }
 
 int launch_gemm_ln(grilly_ctx* ctx, bool bf16, const void* x, const void* w, GemmLnArgs& args) {
@@ -252,11 +282,11 @@ int launch_gemm_ln(grilly_ctx* ctx, bool bf16, const void* x, const void* w, Gem
     return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "linear_layernorm: the one-kernel form needs out_features in {128, 256, 384, 512} and 16-byte aligned rows");
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "linear_layernorm: operands must be 16-byte aligned");
-  switch (args.N / 32) {
+  switch (args.N / 64) {
+    case 2: return bf16 ? launch_ln_one<2, true>(ctx, x, w, args) : launch_ln_one<2, false>(ctx, x, w, args);
     case 4: return bf16 ? launch_ln_one<4, true>(ctx, x, w, args) : launch_ln_one<4, false>(ctx, x, w, args);
-    case 8: return bf16 ? launch_ln_one<8, true>(ctx, x, w, args) : launch_ln_one<8, false>(ctx, x, w, args);
-    case 12: return bf16 ? launch_ln_one<12, true>(ctx, x, w, args) : launch_ln_one<12, false>(ctx, x, w, args);
-    default: return bf16 ? launch_ln_one<16, true>(ctx, x, w, args) : launch_ln_one<16, false>(ctx, x, w, args);
+    case 6: return bf16 ? launch_ln_one<6, true>(ctx, x, w, args) : launch_ln_one<6, false>(ctx, x, w, args);
+    default: return bf16 ? launch_ln_one<8, true>(ctx, x, w, args) : launch_ln_one<8, false>(ctx, x, w, args);
   }
 }
 

@@ -71,6 +71,7 @@ struct grilly_ctx {
     int attn_hpc = 0;        // heads per work unit of the short attention kernel
     int attn_general = 0;    // 1: always the general attention kernel
     int fused_ln = 1;        // 0: linear + LayerNorm as two launches even where the one-kernel form exists
+    int ln_deep = -1;        // 0/1: never/always the deep-operand-ring variant of the one-kernel form
   } tune;
   // RoPE tables, keyed by (S, D, base, scaling)
   struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };
@@ -94,7 +95,7 @@ int prof_begin(grilly_ctx* ctx, int cls, double flops, double bytes);
 void prof_end(grilly_ctx* ctx, int idx);
 
 enum { TM_F32 = 0, TM_BF16 = 1 };
-enum { TM_SW128 = 0, TM_SW128_ATOM32 = 1 };  // 128-byte swizzle of 16-byte chunks, or of 32-byte chunks (tf32 MN-major)
+enum { TM_SW128 = 0, TM_SW128_ATOM32 = 1, TM_SWNONE = 2 };  // 128-byte swizzle of 16-byte chunks, or of 32-byte chunks (tf32 MN-major), or none
 // 2-D row-major tensor [outer][inner] with a row pitch, 128-byte swizzle, zero fill out of bounds.
 int get_tmap_2d(grilly_ctx* ctx, int dtype, const void* ptr, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
                 uint32_t box_inner, uint32_t box_outer, CUtensorMap* out, int swizzle = TM_SW128);

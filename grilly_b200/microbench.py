@@ -3,6 +3,7 @@
     linear     y = act(x W^T + b) (+ residual)      --m --n --k --act {none,gelu,silu,relu} --residual --precision
     gemm       C = A B, row-major                    --m --n --k --precision
     attention  flash_attention2 on packed sentences  --b --s --h --d (lengths uniform in [16, s]) --causal --rope
+    linear_ln  y = LayerNorm(x W^T + b + residual)   --m --n --k --precision (one kernel for n in 128/256/384/512)
     layernorm  y = LayerNorm(x)                      --m --n
     faiss      cosine distances (--m queries, --n database vectors, --k dim) and top-k (--topk) of the result
 
@@ -84,7 +85,7 @@ def _nsplit(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["linear", "gemm", "attention", "layernorm", "faiss"])
+    ap.add_argument("op", choices=["linear", "linear_ln", "gemm", "attention", "layernorm", "faiss"])
     ap.add_argument("--m", "--dim-m", dest="m", type=int, default=18432)
     ap.add_argument("--n", "--dim-n", dest="n", type=int, default=1536)
     ap.add_argument("--k", "--dim-k", dest="k", type=int, default=384)
@@ -129,6 +130,16 @@ def main(argv=None):
                                                      prec, L.FLAG_ROUND_TF32))
             flops = 2.0 * a.m * a.n * a.k
             nbytes = elt * (a.m * a.k + a.n * a.k) + 4.0 * a.m * a.n * (2 if a.residual else 1)
+        elif a.op == "linear_ln":
+            x = dev.upload(rng.standard_normal((a.m, a.k)).astype(np.float32), dt, round_tf32=True)
+            w = dev.upload((rng.standard_normal((a.n, a.k)) * 0.05).astype(np.float32), dt, round_tf32=True)
+            b, g, bt = dev.upload(np.zeros(a.n, np.float32)), dev.upload(np.ones(a.n, np.float32)), dev.upload(np.zeros(a.n, np.float32))
+            r = dev.upload(rng.standard_normal((a.m, a.n)).astype(np.float32), dt) if a.residual else None
+            y, scratch = dev.empty((a.m, a.n)), dev.empty((a.m, a.n))
+            fn = lambda: dev.check(lib.grilly_linear_layernorm(ctx, x.ptr, w.ptr, b.ptr, r.ptr if r else None, g.ptr, bt.ptr, y.ptr,  # noqa: E731
+                                                               scratch.ptr, a.m, a.n, a.k, 1e-5, prec, L.FLAG_ROUND_TF32 if not bf16 else 0))
+            flops = 2.0 * a.m * a.n * a.k
+            nbytes = elt * (a.m * a.k + a.n * a.k) + 4.0 * a.m * a.n + (elt * a.m * a.n if a.residual else 0)
         elif a.op == "gemm":
             A = dev.upload(rng.standard_normal((a.m, a.k)).astype(np.float32), dt, round_tf32=True)
             B = dev.upload(rng.standard_normal((a.k, a.n)).astype(np.float32), dt, round_tf32=True)
