@@ -20,6 +20,7 @@ NORM_LAYER, NORM_RMS = 0, 1
 ELT_GELU, ELT_SILU, ELT_RELU, ELT_ADD, ELT_SWIGLU = 1, 2, 3, 4, 5
 ROPE_NONE, ROPE_INTERLEAVED, ROPE_ROTATE_HALF = 0, 1, 2
 DIST_L2, DIST_COSINE, DIST_DOT = 1, 2, 3
+ARCH_POST_LN, ARCH_MODERNBERT = 0, 1
 FLAG_OUT_BF16, FLAG_ROUND_TF32, FLAG_SWIGLU_PAIRS = 1, 2, 4
 
 
@@ -29,6 +30,7 @@ class EncoderConfig(C.Structure):
         ("vocab", C.c_int), ("max_pos", C.c_int),
         ("embed_ln_eps", C.c_float), ("layer_ln_eps", C.c_float),
         ("has_token_type", C.c_int), ("precision", C.c_int), ("chunk_tokens", C.c_int),
+        ("arch", C.c_int), ("rope_base", C.c_float), ("final_ln_eps", C.c_float),
     ]
 
 
@@ -79,6 +81,11 @@ SIGNATURES = {
     "grilly_embedding_lookup": [_vp, _vp, _vp, _vp, _ll, _i, _i],
     "grilly_embed_layernorm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i],
     "grilly_mean_pool": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "grilly_layernorm_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f],
+    "grilly_softmax_backward": [_vp, _vp, _vp, _vp, _ll, _i],
+    "grilly_attention_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f],
+    "grilly_adam_update": [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _i],
+    "grilly_transpose_2d": [_vp, _vp, _vp, _i, _i],
     "grilly_encoder_create": [_vp, C.POINTER(EncoderConfig), _pp],
     "grilly_encoder_set_weight": [_vp, C.c_char_p, _i, _vp, _sz],
     "grilly_encoder_forward": [_vp, _vp, _vp, _i, _i, _vp],
@@ -88,6 +95,7 @@ SIGNATURES = {
     "grilly_encoder_destroy": [_vp],
     "grilly_gemm_mnk_multi": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _i],
     "grilly_faiss_distances": [_vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "grilly_faiss_search": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "grilly_faiss_topk": [_vp, _vp, _i, _i, _i, _vp, _vp],
     "grilly_gemm_pick_tile": [_i, _i, _i],
     "grilly_plan_chunks": [_vp, _i, _i, _vp, _vp, C.POINTER(_ll)],

@@ -18,7 +18,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 BUILD = PKG / "_build"
 LIB = PKG / "lib" / "libgrilly_b200.so"
-SOURCES = ["api.cu", "gemm.cu", "attention.cu", "rowops.cu", "encoder.cu", "noalloc.cu", "selftest.cu", "faiss.cu", "tf32x3.cu"]
+SOURCES = ["api.cu", "gemm.cu", "attention.cu", "rowops.cu", "encoder.cu", "noalloc.cu", "selftest.cu", "faiss.cu", "tf32x3.cu", "backward.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

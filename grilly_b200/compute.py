@@ -284,7 +284,8 @@ class FNN(_Namespace):
     def linear_backward(self, grad_output, x, weights, bias=None):
         """(grad_input, grad_weight, grad_bias) of y = x W^T + b as three products on the tensor cores, the way the
         reference's GEMM branch does it (backend/fnn.py:1501-1573): grad_output @ W, grad_output^T @ x, and the
-        column sums of grad_output as ones(1, rows) @ grad_output. grad_bias is None when there is no bias."""
+        column sums of grad_output as ones(1, rows) @ grad_output. Each operand is uploaded once; the transpose of
+        grad_output is taken on the device. grad_bias is None when there is no bias."""
         go = np.asarray(grad_output, dtype=np.float32)
         xs = np.asarray(x, dtype=np.float32)
         w = np.asarray(weights, dtype=np.float32)
@@ -293,10 +294,68 @@ class FNN(_Namespace):
         if w.shape != (go.shape[-1], xs.shape[-1]):
             raise ValueError(f"weights must have shape {(go.shape[-1], xs.shape[-1])}")
         go2, x2 = go.reshape(-1, go.shape[-1]), xs.reshape(-1, xs.shape[-1])
-        grad_input = self.gemm(go2, w).reshape(xs.shape)
-        grad_weight = self.gemm(np.ascontiguousarray(go2.T), x2)
-        grad_bias = self.gemm(np.ones((1, go2.shape[0]), np.float32), go2).reshape(-1) if bias is not None else None
+        rows, n_out, n_in = go2.shape[0], go2.shape[1], x2.shape[1]
+        q = 8 if self._bf16 else 4
+        if rows % q or n_out % q or n_in % q:
+            # ragged sizes: the padded host path
+            grad_input = self.gemm(go2, w).reshape(xs.shape)
+            grad_weight = self.gemm(np.ascontiguousarray(go2.T), x2)
+            grad_bias = self.gemm(np.ones((1, rows), np.float32), go2).reshape(-1) if bias is not None else None
+            return grad_input, grad_weight, grad_bias
+        god = self.dev.upload(go2)                       # raw fp32: rounded copies are made below
+        got = self.dev.empty((n_out, rows))
+        self.dev.check(self.lib.grilly_transpose_2d(self.ctx, _p(god), _p(got), rows, n_out))
+        go_m, got_m = self.to_mma(god), self.to_mma(got)
+        grad_input = self.gemm(go_m, self._b.to_device(w)).numpy().reshape(xs.shape)
+        grad_weight = self.gemm(got_m, self._b.to_device(x2)).numpy()
+        grad_bias = None
+        if bias is not None:
+            grad_bias = self.gemm(self._b.to_device(np.ones((1, rows), np.float32)), go_m).numpy().reshape(-1)
         return grad_input, grad_weight, grad_bias
+
+    def to_mma(self, t: DeviceTensor) -> DeviceTensor:
+        """A raw fp32 device tensor in the form the backend's MMAs consume: tf32-rounded fp32, or bf16."""
+        out = self.dev.empty(t.shape, "bf16" if self._bf16 else "f32")
+        if self._bf16:
+            self.dev.check(self.lib.grilly_cast_f32_to_bf16(self.ctx, _p(t), _p(out), t.size))
+        else:
+            self.dev.check(self.lib.grilly_round_tf32(self.ctx, _p(t), _p(out), t.size))
+        return out
+
+    def layernorm_backward(self, grad_output, x, gamma, mean=None, var=None, eps=1e-5):
+        """(grad_input, grad_gamma, grad_beta) of LayerNorm over the last dim: backend/fnn.py:1701-1847. ``mean`` and
+        ``var`` are the forward pass's statistics (shape (..., 1) or (...)); computed when not given."""
+        xs = np.asarray(x, dtype=np.float32)
+        go = np.asarray(grad_output, dtype=np.float32)
+        if go.shape != xs.shape:
+            raise ValueError("grad_output and x must have the same shape")
+        F = int(xs.shape[-1])
+        rows = xs.size // F
+        if gamma is not None and int(np.prod(np.shape(gamma))) != F:
+            raise ValueError(f"gamma has {int(np.prod(np.shape(gamma)))} entries, expected {F}")
+        xd, god = self.dev.upload(xs.reshape(rows, F)), self.dev.upload(go.reshape(rows, F))
+        md = self.dev.upload(np.asarray(mean, np.float32).reshape(rows)) if mean is not None else None
+        vd = self.dev.upload(np.asarray(var, np.float32).reshape(rows)) if var is not None else None
+        gi, gg, gb = self.dev.empty((rows, F)), self.dev.empty((F,)), self.dev.empty((F,))
+        self.dev.check(self.lib.grilly_layernorm_backward(self.ctx, _p(god), _p(xd), _p(self._vec(gamma)), _p(md), _p(vd), _p(gi),
+                                                          _p(gg), _p(gb), rows, F, float(eps)))
+        return gi.numpy().reshape(xs.shape), gg.numpy(), gb.numpy()
+
+    def softmax_backward(self, grad_output, softmax_output, dim=-1):
+        """softmax_output * (grad_output - sum(grad_output * softmax_output)) along ``dim``: backend/fnn.py:1849-1933."""
+        go = np.asarray(grad_output, dtype=np.float32)
+        y = np.asarray(softmax_output, dtype=np.float32)
+        if go.shape != y.shape:
+            raise ValueError("grad_output and softmax_output must have the same shape")
+        ax = dim % go.ndim
+        if ax != go.ndim - 1:
+            moved = self.softmax_backward(np.ascontiguousarray(np.moveaxis(go, ax, -1)), np.ascontiguousarray(np.moveaxis(y, ax, -1)))
+            return np.ascontiguousarray(np.moveaxis(moved, -1, ax))
+        cols = int(go.shape[-1])
+        god, yd = self.dev.upload(go), self.dev.upload(y)
+        gi = self.dev.empty(go.shape)
+        self.dev.check(self.lib.grilly_softmax_backward(self.ctx, _p(god), _p(yd), _p(gi), go.size // cols, cols))
+        return gi.numpy()
 
     def _norm(self, x, gamma, beta, eps, mode, residual=None):
         x_shape = tuple(x.shape)
@@ -548,6 +607,24 @@ class Attention(_Namespace):
         self.dev.check(self.lib.grilly_attention_output(self.ctx, _p(wd), _p(vd), _p(out), B, S, H, D))
         return self._out(out, host)
 
+    def attention_backward(self, grad_output, q, k, v, attn_weights, scale):
+        """(grad_q, grad_k, grad_v) of out = attn_weights @ v with attn_weights = softmax(scale q k^T): tensors in the
+        (B, H, S, D) layout and attn_weights (B, H, S, S), as backend/autograd_core.py:609-646 takes them
+        (shaders/attention-backward.glsl)."""
+        go, qs, ks, vs = (np.asarray(t, dtype=np.float32) for t in (grad_output, q, k, v))
+        aw = np.asarray(attn_weights, dtype=np.float32)
+        if qs.ndim != 4 or ks.shape != qs.shape or vs.shape != qs.shape or go.shape != qs.shape:
+            raise ValueError("grad_output, q, k, v must all be (B, H, S, D)")
+        B, H, S, D = (int(s) for s in qs.shape)
+        if aw.shape != (B, H, S, S):
+            raise ValueError(f"attn_weights must have shape {(B, H, S, S)}")
+        up = self.dev.upload
+        god, qd, kd, vd, ad = up(go), up(qs), up(ks), up(vs), up(aw)
+        gq, gk, gv = self.dev.empty(qs.shape), self.dev.empty(qs.shape), self.dev.empty(qs.shape)
+        self.dev.check(self.lib.grilly_attention_backward(self.ctx, _p(god), _p(qd), _p(kd), _p(vd), _p(ad), _p(gq), _p(gk), _p(gv),
+                                                          B, H, S, D, float(scale)))
+        return gq.numpy(), gk.numpy(), gv.numpy()
+
     def attention_concat_heads(self, attention_output):
         """(B, S, H, D) -> (B, S, H*D): backend/attention.py:302-359 (a reshape in this layout)."""
         B, S, H, D = (int(s) for s in attention_output.shape)
@@ -599,6 +676,22 @@ class Learning(_Namespace):
         return out.numpy()
 
 
+    def adam_update(self, weights, gradients, moment1, moment2, learning_rate, beta1=0.9, beta2=0.999, epsilon=1e-8,
+                    beta1_t=0.0, beta2_t=0.0, clear_grad=False):
+        """One Adam step: (updated_weights, updated_moment1, updated_moment2), new arrays of the inputs' shape
+        (backend/learning.py:967-1077, adam-update.glsl). ``beta1_t`` / ``beta2_t`` are beta^t for the bias
+        correction. ``clear_grad`` is accepted for signature compatibility: the caller's gradient array is a host
+        array and is left as it is, as on the reference's GPU branch."""
+        w = np.asarray(weights, dtype=np.float32)
+        arrs = [np.asarray(a, dtype=np.float32) for a in (gradients, moment1, moment2)]
+        if any(a.size != w.size for a in arrs):
+            raise ValueError("All arrays must have the same size")
+        wd, gd, m1, m2 = (self.dev.upload(a.reshape(-1)) for a in (w, *arrs))
+        self.dev.check(self.lib.grilly_adam_update(self.ctx, _p(wd), _p(gd), _p(m1), _p(m2), w.size, float(learning_rate), float(beta1),
+                                                   float(beta2), float(epsilon), float(beta1_t), float(beta2_t), int(bool(clear_grad))))
+        return wd.numpy().reshape(w.shape), m1.numpy().reshape(w.shape), m2.numpy().reshape(w.shape)
+
+
 class Faiss(_Namespace):
     """backend/faiss.py ``VulkanFAISS``: pairwise distances and exact top-k selection."""
 
@@ -625,6 +718,30 @@ class Faiss(_Namespace):
         code = self._TYPES.get(distance_type, L.DIST_COSINE)
         self.dev.check(self.lib.grilly_faiss_distances(self.ctx, _p(qd), _p(dd), _p(out), nq, ndb, dim, code))
         return self._out(out, host)
+
+    def search(self, queries, database, k, distance_type="cosine"):
+        """``topk(compute_distances(queries, database, distance_type), k)`` in one call that never materialises the
+        (num_queries, num_database) matrix: the database is walked in L2-sized chunks, each reduced to its k best at
+        once. Returns (indices uint32, distances fp32), each (num_queries, k), identical to the two-call form."""
+        if not isinstance(queries, DeviceTensor):
+            queries = np.asarray(queries, dtype=np.float32)
+            if queries.ndim == 1:
+                queries = queries.reshape(1, -1)
+        if len(queries.shape) != 2 or len(database.shape) != 2:
+            raise ValueError("queries must be (num_queries, dim) or (dim,), database (num_database, dim)")
+        nq, dim = (int(s) for s in queries.shape)
+        ndb, dim_db = (int(s) for s in database.shape)
+        if dim != dim_db:
+            raise ValueError(f"dimension mismatch: queries have {dim}, database has {dim_db}")
+        k = min(int(k), ndb)
+        if k <= 0:
+            raise ValueError("k must be positive")
+        qd, _ = self._act_in(queries, mma_operand=False)
+        dd = self.dev.weight(database, "f32", round_tf32=False, tag="faiss-db")
+        idx, val = self.dev.empty((nq, k), "i32"), self.dev.empty((nq, k))
+        code = self._TYPES.get(distance_type, L.DIST_COSINE)
+        self.dev.check(self.lib.grilly_faiss_search(self.ctx, _p(qd), _p(dd), nq, ndb, dim, k, code, _p(idx), _p(val)))
+        return idx.numpy().view(np.uint32), val.numpy()
 
     def topk(self, distances, k):
         """(indices uint32, distances fp32), each (num_queries, k): the k smallest entries of every row in ascending
@@ -711,6 +828,7 @@ class Compute:
         self.embedding_lookup = self.learning.embedding_lookup
         self.faiss_compute_distances = self.faiss.compute_distances   # backend/compute.py:143-150
         self.faiss_topk = self.faiss.topk
+        self.faiss_search = self.faiss.search
 
     def set_architecture(self, architecture: str):
         """backend/compute.py:70-128. There are no per-architecture kernels here: causal masking is a flag."""

@@ -108,6 +108,7 @@ struct PoolArgs {
   float* out;             // [B][F]
   int B, S, F;
   int normalize;          // 1: divide the pooled vector by (||v||_2 + 1e-8)
+  int cls;                // 1: take the sequence's first token instead of the mean (CLS pooling)
 };
 
 }  // namespace gb

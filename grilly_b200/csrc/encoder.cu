@@ -23,6 +23,7 @@ using namespace gb;
 struct EncLayer {
   float *wqkv = nullptr, *bqkv = nullptr, *wo = nullptr, *bo = nullptr, *ln1_g = nullptr, *ln1_b = nullptr;
   float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+  float *wgu = nullptr, *bgu = nullptr;   // pre-norm GeGLU layers: (2 ffn, hidden) rows (up_j, gate_j) and the bias alike
   // bf16 mode: the GEMM weights as bf16 (the fp32 slots above are then only the upload staging)
   void *wqkv_h = nullptr, *wo_h = nullptr, *w1_h = nullptr, *w2_h = nullptr;
 };
@@ -31,6 +32,7 @@ struct grilly_encoder {
   grilly_ctx* ctx = nullptr;
   grilly_encoder_config cfg{};
   float *word = nullptr, *pos = nullptr, *type = nullptr, *emb_g = nullptr, *emb_b = nullptr;
+  float *final_g = nullptr, *final_b = nullptr;   // pre-norm models: the LayerNorm after the last layer
   std::vector<EncLayer> layers;
   // activation workspace for one chunk
   long long cap_rows = 0;
@@ -111,12 +113,13 @@ static int ensure_io(grilly_encoder* e, int B, int S) {
 }
 
 static int enc_linear(grilly_encoder* e, const void* x, const void* w, const float* bias, const void* residual, void* y,
-                      int M, int N, int K, int act, bool out_fp32) {
+                      int M, int N, int K, int act, bool out_fp32, bool glu_pairs = false) {
   GemmArgs a{};
   a.M = M; a.N = N; a.K = K;
   a.bias = bias; a.residual = reinterpret_cast<const float*>(residual); a.ld_res = N;
   a.residual_bf16 = (residual && e->bf16) ? 1 : 0;
-  a.out = y; a.ld_out = N;
+  a.out = y; a.ld_out = glu_pairs ? N / 2 : N;
+  a.swiglu_pairs = glu_pairs ? 1 : 0;   // weight rows come as (multiplier_j, activated_j) pairs: out[:, j] = first * act(second)
   a.act = act;
   a.out_bf16 = (e->bf16 && !out_fp32) ? 1 : 0;
   // tf32 mode: outputs that feed an MMA directly are rounded to tf32; pre-LayerNorm sums stay full fp32
@@ -128,12 +131,13 @@ static int enc_linear(grilly_encoder* e, const void* x, const void* w, const flo
 static int enc_linear_norm(grilly_encoder* e, const void* x, const void* w, const float* bias, const void* residual,
                            const float* g, const float* b, void* y, int M, int N, int K, bool out_fp32);
 
-static int enc_norm(grilly_encoder* e, const float* x, const float* g, const float* b, void* y, int rows, bool out_fp32) {
+static int enc_norm(grilly_encoder* e, const float* x, const float* g, const float* b, void* y, int rows, bool out_fp32,
+                    float eps = -1.f) {
   NormArgs n{};
-  n.x = x; n.gamma = g; n.beta = b; n.y = y; n.rows = rows; n.F = e->cfg.hidden; n.eps = e->cfg.layer_ln_eps;
+  n.x = x; n.gamma = g; n.beta = b; n.y = y; n.rows = rows; n.F = e->cfg.hidden; n.eps = eps >= 0.f ? eps : e->cfg.layer_ln_eps;
   n.mode = NORM_LAYER;
   n.out_bf16 = (e->bf16 && !out_fp32) ? 1 : 0;
-  n.round_tf32 = e->bf16 ? 0 : 1;
+  n.round_tf32 = (e->bf16 || out_fp32) ? 0 : 1;
   n.reverse = 1;   // the GEMM before it wrote the last rows last: start where L2 still holds them (about 4 % of this kernel)
   return launch_norm(e->ctx, n);
 }
@@ -161,14 +165,43 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
   const int F = c.hidden, H = c.num_heads, D = F / H, Bc = b1 - b0;
   int rc;
   const size_t act = e->bf16 ? 2 : 4;
+  const bool prenorm = c.arch == GRILLY_ARCH_MODERNBERT;
   EmbedArgs em{};
-  em.ids = ids_dev + static_cast<long long>(b0) * S; em.cu_seqlens = cu_chunk_dev; em.word = e->word; em.pos = e->pos;
-  em.type0 = c.has_token_type ? e->type : nullptr; em.gamma = e->emb_g; em.beta = e->emb_b; em.out = reinterpret_cast<float*>(e->x);
+  em.ids = ids_dev + static_cast<long long>(b0) * S; em.cu_seqlens = cu_chunk_dev; em.word = e->word;
+  em.pos = prenorm ? nullptr : e->pos;   // pre-norm models carry positions as RoPE inside attention (:1147-1155)
+  em.type0 = (c.has_token_type && !prenorm) ? e->type : nullptr; em.gamma = e->emb_g; em.beta = e->emb_b; em.out = reinterpret_cast<float*>(e->x);
   em.B = Bc; em.S = S; em.F = F; em.vocab = c.vocab; em.max_pos = c.max_pos; em.eps = c.embed_ln_eps;
   em.round_tf32 = e->bf16 ? 0 : 1; em.out_bf16 = e->bf16 ? 1 : 0;
   if ((rc = launch_embed(ctx, em))) return rc;
   float* final_hidden = e->bf16 ? e->xf : reinterpret_cast<float*>(e->x);
-  for (int l = 0; l < c.num_layers; ++l) {
+  if (prenorm) {
+    // ---- ModernBERT branch of _forward_layer (utils/vulkan_sentence_transformer.py:799-970), fp32 storage / tf32 MMAs.
+    // The residual stream x is kept tf32-rounded: it is the QKV GEMM's operand as it stands (the attention norm is the
+    // identity), so rounding it where it is produced keeps the MMA from truncating it.
+    const float* cos_t = nullptr; const float* sin_t = nullptr;
+    if ((rc = get_rope_table(ctx, max_len, D, c.rope_base, 1.0f, &cos_t, &sin_t))) return rc;
+    for (int l = 0; l < c.num_layers; ++l) {
+      const EncLayer& L = e->layers[l];
+      if ((rc = enc_linear(e, e->x, L.wqkv, L.bqkv, nullptr, e->qkv, rows, 3 * F, F, ACT_NONE, false))) return rc;
+      AttnArgs at{};
+      at.B = Bc; at.S = max_len; at.H = H; at.D = D; at.cu_seqlens = cu_chunk_dev; at.scale = 1.0f / sqrtf(static_cast<float>(D));
+      at.out = e->attn; at.ld_out = F; at.round_tf32 = 1; at.key_mask = key_mask_dev;
+      at.rope_style = ROPE_ROTATE_HALF; at.rope_cos = cos_t; at.rope_sin = sin_t;
+      ctx->attn_flops_hint = 4.0 * H * D * sum_len2;
+      const char* qkv = reinterpret_cast<const char*>(e->qkv);
+      if ((rc = launch_attention(ctx, false, qkv, qkv + F * act, qkv + 2 * F * act, 3LL * F, 3LL * F, 3LL * F, rows, at))) return rc;
+      // x2 = x + attn Wo^T + bo (no norm after it); the MLP's LayerNorm reads it, the MLP's residual is it
+      if ((rc = enc_linear(e, e->attn, L.wo, L.bo, e->x, e->x2, rows, F, F, ACT_NONE, false))) return rc;
+      if ((rc = enc_norm(e, reinterpret_cast<const float*>(e->x2), L.ln2_g, L.ln2_b, e->attn, rows, false))) return rc;
+      // GeGLU: h[:, j] = (n Wup_j + bup_j) * gelu(n Wgate_j + bgate_j), one GEMM over the interleaved rows
+      if ((rc = enc_linear(e, e->attn, L.wgu, L.bgu, nullptr, e->h, rows, 2 * c.ffn, F, ACT_GELU_TANH, false, true))) return rc;
+      if ((rc = enc_linear(e, e->h, L.w2, L.b2, e->x2, e->x, rows, F, c.ffn, ACT_NONE, false))) return rc;
+    }
+    // final LayerNorm (:1166-1177), then CLS pooling (:1181-1183) and L2 normalisation
+    if ((rc = enc_norm(e, reinterpret_cast<const float*>(e->x), e->final_g, e->final_b, e->t, rows, true, c.final_ln_eps))) return rc;
+    final_hidden = e->t;
+  }
+  for (int l = 0; !prenorm && l < c.num_layers; ++l) {
     const EncLayer& L = e->layers[l];
     const bool last = l + 1 == c.num_layers;
     const void* wqkv = e->bf16 ? L.wqkv_h : static_cast<const void*>(L.wqkv);
@@ -191,6 +224,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
   }
   PoolArgs p{};
   p.x = final_hidden; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
+  p.cls = prenorm ? 1 : 0;
   if ((rc = launch_pool(ctx, p))) return rc;
   if (e->keep_hidden && e->hidden_all)
     GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->hidden_all + hidden_row0 * F, final_hidden, static_cast<size_t>(rows) * F * sizeof(float),
@@ -316,6 +350,10 @@ int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, gri
   if (cfg->precision == GRILLY_PREC_BF16 && (cfg->hidden % 8 || cfg->ffn % 8))
     return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: bf16 mode needs hidden and ffn to be multiples of 8");
   if (cfg->hidden % 4 || cfg->ffn % 4 || cfg->hidden > 1024) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: hidden and ffn must be multiples of 4, hidden at most 1024");
+  if (cfg->arch != GRILLY_ARCH_POST_LN && cfg->arch != GRILLY_ARCH_MODERNBERT) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: unknown architecture");
+  if (cfg->arch == GRILLY_ARCH_MODERNBERT && cfg->precision != GRILLY_PREC_TF32)
+    return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: the pre-norm (ModernBERT) architecture runs in tf32 mode");
+  if (cfg->arch == GRILLY_ARCH_MODERNBERT && !(cfg->rope_base > 0.f)) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: rope_base must be positive");
   cudaSetDevice(ctx->device);
   grilly_encoder* e = new grilly_encoder();
   e->ctx = ctx;
@@ -327,7 +365,9 @@ int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, gri
   auto A = [&](float** p, size_t n) { if (!rc) rc = enc_alloc(e, n * sizeof(float), reinterpret_cast<void**>(p)); };
   A(&e->word, static_cast<size_t>(cfg->vocab) * F); A(&e->pos, static_cast<size_t>(cfg->max_pos) * F); A(&e->type, 2 * F);
   A(&e->emb_g, F); A(&e->emb_b, F);
+  if (cfg->arch == GRILLY_ARCH_MODERNBERT) { A(&e->final_g, F); A(&e->final_b, F); }
   for (auto& L : e->layers) {
+    if (cfg->arch == GRILLY_ARCH_MODERNBERT) { A(&L.wgu, 2 * ffn * F); A(&L.bgu, 2 * ffn); }
     A(&L.wqkv, 3 * F * F); A(&L.bqkv, 3 * F); A(&L.wo, F * F); A(&L.bo, F); A(&L.ln1_g, F); A(&L.ln1_b, F);
     A(&L.w1, ffn * F); A(&L.b1, ffn); A(&L.w2, F * ffn); A(&L.b2, F); A(&L.ln2_g, F); A(&L.ln2_b, F);
     if (e->bf16) {
@@ -361,6 +401,8 @@ int grilly_encoder_set_weight(grilly_encoder* e, const char* name, int layer, co
     else if (n == "type") { dst = e->type; expect = 2 * F; }
     else if (n == "emb_ln_g") { dst = e->emb_g; expect = F; }
     else if (n == "emb_ln_b") { dst = e->emb_b; expect = F; }
+    else if (n == "final_g") { dst = e->final_g; expect = F; }
+    else if (n == "final_b") { dst = e->final_b; expect = F; }
   } else if (layer < e->cfg.num_layers) {
     EncLayer& L = e->layers[layer];
     if (n == "wqkv") { dst = L.wqkv; dst_h = L.wqkv_h; expect = 3 * F * F; is_gemm_weight = true; }
@@ -375,6 +417,8 @@ int grilly_encoder_set_weight(grilly_encoder* e, const char* name, int layer, co
     else if (n == "b2") { dst = L.b2; expect = F; }
     else if (n == "ln2_g") { dst = L.ln2_g; expect = F; }
     else if (n == "ln2_b") { dst = L.ln2_b; expect = F; }
+    else if (n == "wgu") { dst = L.wgu; expect = 2 * ffn * F; is_gemm_weight = true; }
+    else if (n == "bgu") { dst = L.bgu; expect = 2 * ffn; }
   }
   if (!dst) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_set_weight: unknown weight name '" + n + "' or layer");
   if (count != expect) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder_set_weight: '" + n + "' expects " + std::to_string(expect) + " values");

@@ -51,7 +51,8 @@ constexpr int TOPK_MAX_K = 1024;
 // launch back to column indices of the original row. Every segment must hold at least k elements.
 __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const float* __restrict__ vals, long long ld, int len, int segs,
                                                                  int k, const uint32_t* __restrict__ src_idx,
-                                                                 uint32_t* __restrict__ idx_out, float* __restrict__ val_out) {
+                                                                 uint32_t* __restrict__ idx_out, float* __restrict__ val_out,
+                                                                 uint32_t idx_base = 0, long long out_ld = 0, long long out_off = 0) {
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need, s_count, s_ties;
   __shared__ uint32_t warp_tot[TOPK_THREADS / 32];
@@ -149,10 +150,14 @@ __global__ void __launch_bounds__(TOPK_THREADS) topk_rows_kernel(const float* __
       __syncthreads();
     }
   }
+  // default: one packed row of k results per (row, segment); with out_ld the k results go to row_id * out_ld + out_off
+  // (the winners of one database chunk inside a wider candidate matrix) and idx_base is added to the positions
+  const long long out0 = out_ld > 0 ? static_cast<long long>(row_id) * out_ld + out_off + static_cast<long long>(seg) * k
+                                    : static_cast<long long>(blockIdx.x) * k;
   for (int i = t; i < k; i += TOPK_THREADS) {
     const uint32_t id = cand_idx[i];
-    idx_out[static_cast<long long>(blockIdx.x) * k + i] = src ? __ldg(src + id) : static_cast<uint32_t>(seg_begin) + id;
-    val_out[static_cast<long long>(blockIdx.x) * k + i] = __ldg(row + id);
+    idx_out[out0 + i] = src ? __ldg(src + id) : idx_base + static_cast<uint32_t>(seg_begin) + id;
+    val_out[out0 + i] = __ldg(row + id);
   }
 }
 
@@ -205,6 +210,78 @@ int grilly_faiss_distances(grilly_ctx* ctx, const float* queries, const float* d
   if (ds) cudaFreeAsync(ds, ctx->stream);
   if (qn) cudaFreeAsync(qn, ctx->stream);
   if (dn) cudaFreeAsync(dn, ctx->stream);
+  return rc;
+}
+
+int grilly_faiss_search(grilly_ctx* ctx, const float* queries, const float* database, int num_queries, int num_database, int dim,
+                        int k, int distance_type, unsigned int* indices_out, float* distances_out) {
+  if (!ctx) return GRILLY_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (cudaSetDevice(ctx->device) != cudaSuccess) return set_error(ctx, GRILLY_ERR_CUDA, "cudaSetDevice failed");
+  if (!queries || !database || !indices_out || !distances_out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_search: null operand");
+  if (num_queries <= 0 || num_database <= 0 || dim <= 0 || k <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_search: sizes must be positive");
+  if (k > num_database) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_search: k exceeds the number of database vectors");
+  if (k > TOPK_MAX_K) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "faiss_search: k is limited to 1024");
+  if (distance_type != GRILLY_DIST_L2 && distance_type != GRILLY_DIST_COSINE && distance_type != GRILLY_DIST_DOT)
+    return set_error(ctx, GRILLY_ERR_INVALID_ARG, "faiss_search: unknown distance type");
+  const int dim_pad = (dim + 3) & ~3;
+  const long long kq = 3LL * dim_pad;
+  if (kq > 2147483647LL) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "faiss_search: dim too large");
+  // Database chunks whose distance block (num_queries x chunk floats) stays in L2: the block is written by the GEMM,
+  // turned into distances and reduced to its k best per query while it is still there; the full matrix never exists.
+  long long chunk = (16LL << 20) / num_queries;
+  chunk = std::max<long long>(2048, std::min<long long>(chunk, 65536)) & ~255LL;
+  const int nchunks = static_cast<int>((num_database + chunk - 1) / chunk);
+  const long long per = (num_database + nchunks - 1) / nchunks;            // balanced: every chunk holds at least k vectors
+  const long long chunk_cols = (per + 3) & ~3LL;                            // row pitch of the distance block (16-byte rows)
+  const long long cand = static_cast<long long>(nchunks) * k;
+  float *qs = nullptr, *ds = nullptr, *qn = nullptr, *dn = nullptr, *blk = nullptr, *cval = nullptr;
+  uint32_t* cidx = nullptr;
+  cudaError_t e = cudaMallocAsync(&qs, static_cast<size_t>(num_queries) * kq * sizeof(float), ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&ds, static_cast<size_t>(chunk_cols) * kq * sizeof(float), ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&qn, static_cast<size_t>(num_queries) * sizeof(float), ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&dn, static_cast<size_t>(chunk_cols) * sizeof(float), ctx->stream);
+  if (e == cudaSuccess) e = cudaMallocAsync(&blk, static_cast<size_t>(num_queries) * chunk_cols * sizeof(float), ctx->stream);
+  if (e == cudaSuccess && nchunks > 1) e = cudaMallocAsync(&cval, static_cast<size_t>(num_queries) * cand * sizeof(float), ctx->stream);
+  if (e == cudaSuccess && nchunks > 1) e = cudaMallocAsync(&cidx, static_cast<size_t>(num_queries) * cand * sizeof(uint32_t), ctx->stream);
+  int rc = GRILLY_OK;
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    rc = set_error(ctx, GRILLY_ERR_OOM, "faiss_search: no memory for the scratch (split operands of one chunk, one distance block, candidates)");
+  } else {
+    rc = launch_split_rows(ctx, queries, qs, qn, num_queries, dim, dim_pad, true);
+    for (int c = 0; c < nchunks && !rc; ++c) {
+      const long long c0 = c * per;
+      const int n = static_cast<int>(std::min<long long>(per, num_database - c0));
+      const int n_pad = (n + 3) & ~3;
+      rc = launch_split_rows(ctx, database + c0 * dim, ds, dn, n, dim, dim_pad, false);
+      if (rc) break;
+      GemmArgs a{};
+      a.M = num_queries; a.N = n; a.K = static_cast<int>(kq);
+      a.out = blk; a.ld_out = n_pad;
+      if ((rc = launch_gemm(ctx, false, false, qs, ds, a, 0))) break;
+      // distances in place on the block (row pitch n_pad; the padding columns are never read)
+      const long long total = static_cast<long long>(num_queries) * n_pad;
+      const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 8LL * ctx->num_sms));
+      dot_to_distance_kernel<<<blocks, 256, 0, ctx->stream>>>(blk, qn, dn, num_queries, n_pad, distance_type);
+      if (nchunks == 1) {
+        topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(blk, n_pad, n, 1, k, nullptr, indices_out, distances_out);
+      } else {
+        topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(blk, n_pad, n, 1, k, nullptr, cidx, cval,
+                                                                        static_cast<uint32_t>(c0), cand, static_cast<long long>(c) * k);
+      }
+      ctx->launches += 2;
+      if (cudaGetLastError() != cudaSuccess) rc = set_error(ctx, GRILLY_ERR_CUDA, "faiss_search: launch failed");
+    }
+    if (!rc && nchunks > 1) {
+      topk_rows_kernel<<<num_queries, TOPK_THREADS, 0, ctx->stream>>>(cval, cand, static_cast<int>(cand), 1, k, cidx, indices_out, distances_out);
+      ctx->launches++;
+      if (cudaGetLastError() != cudaSuccess) rc = set_error(ctx, GRILLY_ERR_CUDA, "faiss_search: merge launch failed");
+    }
+  }
+  for (void* p : {static_cast<void*>(qs), static_cast<void*>(ds), static_cast<void*>(qn), static_cast<void*>(dn), static_cast<void*>(blk),
+                  static_cast<void*>(cval), static_cast<void*>(cidx)})
+    if (p) cudaFreeAsync(p, ctx->stream);
   return rc;
 }
 

@@ -305,7 +305,8 @@ __global__ void __launch_bounds__(128) pool_normalize_kernel(const PoolArgs a) {
   int row0, len;
   if (a.cu_seqlens) { row0 = a.cu_seqlens[b]; len = a.cu_seqlens[b + 1] - row0; }
   else { row0 = b * a.S; len = a.S; }
-  const float* mk = a.mask ? a.mask + static_cast<long long>(b) * a.S : nullptr;
+  if (a.cls) len = min(len, 1);   // CLS pooling: the first token stands for the sequence (zero vector for an empty one)
+  const float* mk = (a.mask && !a.cls) ? a.mask + static_cast<long long>(b) * a.S : nullptr;
   float count = 0.f;
   if (mk) { for (int s = 0; s < len; ++s) count += (mk[s] > 0.5f) ? 1.f : 0.f; }
   else count = static_cast<float>(len);

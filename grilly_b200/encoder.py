@@ -26,6 +26,8 @@ class EncoderWeights:
     emb_ln_g: np.ndarray
     emb_ln_b: np.ndarray
     layers: list = field(default_factory=list)  # dicts with the reference's per-layer keys
+    final_norm_weight: np.ndarray | None = None  # pre-norm (ModernBERT) models: the LayerNorm after the last layer
+    final_norm_bias: np.ndarray | None = None
 
     @staticmethod
     def random(rng, num_layers=6, hidden=384, ffn=1536, vocab=30522, max_pos=512, std=0.02):
@@ -47,34 +49,63 @@ class EncoderWeights:
         return EncoderWeights(word=n(vocab, hidden), pos=n(max_pos, hidden), type=n(2, hidden),
                               emb_ln_g=np.ones(hidden, f32), emb_ln_b=np.zeros(hidden, f32), layers=layers)
 
+    @staticmethod
+    def random_modernbert(rng, num_layers=2, hidden=384, ffn=576, vocab=30522, std=0.02):
+        """Random-init weights of the pre-norm architecture with the per-layer keys the reference's ModernBERT
+        branch reads (utils/vulkan_sentence_transformer.py:799-970): no position table, ``ffn_gate_weight`` (goes
+        through GELU) and ``ffn_up_weight`` (multiplies), one LayerNorm per layer (before the MLP), a final norm."""
+        f32 = np.float32
+        n = lambda *s: (rng.standard_normal(s) * std).astype(f32)  # noqa: E731
+        g = lambda: (1 + 0.1 * rng.standard_normal(hidden)).astype(f32)  # noqa: E731
+        layers = []
+        for _ in range(num_layers):
+            layers.append({
+                "attn_q_weight": n(hidden, hidden), "attn_q_bias": n(hidden), "attn_k_weight": n(hidden, hidden), "attn_k_bias": n(hidden),
+                "attn_v_weight": n(hidden, hidden), "attn_v_bias": n(hidden), "attn_out_weight": n(hidden, hidden), "attn_out_bias": n(hidden),
+                "ffn_ln_gamma": g(), "ffn_ln_beta": n(hidden),
+                "ffn_gate_weight": n(ffn, hidden), "ffn_gate_bias": n(ffn), "ffn_up_weight": n(ffn, hidden), "ffn_up_bias": n(ffn),
+                "ffn_w2": n(hidden, ffn), "ffn_b2": n(hidden),
+            })
+        return EncoderWeights(word=n(vocab, hidden), pos=np.zeros((1, hidden), f32), type=None, emb_ln_g=g(), emb_ln_b=n(hidden),
+                              layers=layers, final_norm_weight=g(), final_norm_bias=n(hidden))
+
     def as_dict(self) -> dict:
         return {"word": self.word, "pos": self.pos, "type": self.type, "emb_ln_g": self.emb_ln_g,
-                "emb_ln_b": self.emb_ln_b, "layers": self.layers}
+                "emb_ln_b": self.emb_ln_b, "layers": self.layers, "final_norm_weight": self.final_norm_weight,
+                "final_norm_bias": self.final_norm_bias}
 
 
 class SentenceEncoder:
-    """Post-LN BERT/MiniLM encoder with mean pooling and L2 normalisation, resident on one GPU.
+    """Sentence encoder resident on one GPU: the post-LN BERT/MiniLM architecture with mean pooling (arch 'bert'), or
+    the pre-norm ModernBERT one with RoPE, a GeGLU MLP, a final LayerNorm and CLS pooling (arch 'modernbert', tf32 mode);
+    L2-normalised embeddings either way.
 
     precision 'tf32': fp32 activations, tf32 tensor-core products (parity tolerance 2e-3).
     precision 'bf16': bf16 weights and activations between the GEMMs, fp32 accumulation, fp32 LayerNorm inputs and
     pooling (tolerance 1e-2); with head_dim 32 it handles sequences up to 128 tokens."""
 
     def __init__(self, weights: EncoderWeights, num_heads: int = 12, embed_ln_eps: float = 1e-12,
-                 layer_ln_eps: float = 1e-5, device: Device | int = 0, chunk_tokens: int = 0, precision: str = "tf32"):
+                 layer_ln_eps: float = 1e-5, device: Device | int = 0, chunk_tokens: int = 0, precision: str = "tf32",
+                 arch: str = "bert", rope_base: float = 10000.0, final_ln_eps: float = 1e-5):
         if precision not in ("tf32", "bf16"):
             raise ValueError("precision must be 'tf32' or 'bf16'")
+        if arch not in ("bert", "modernbert"):
+            raise ValueError("arch must be 'bert' or 'modernbert'")
+        self.arch = arch
         self.precision = precision
         self.dev = device if isinstance(device, Device) else Device(device)
         self._own_dev = not isinstance(device, Device)
         self.lib = self.dev.lib
         self.hidden = int(weights.word.shape[1])
         self.num_heads = num_heads
+        ffn_key = "ffn_w1" if arch == "bert" else "ffn_gate_weight"
         cfg = L.EncoderConfig(
             num_layers=len(weights.layers), hidden=self.hidden, num_heads=num_heads,
-            ffn=int(weights.layers[0]["ffn_w1"].shape[0]), vocab=int(weights.word.shape[0]),
+            ffn=int(weights.layers[0][ffn_key].shape[0]), vocab=int(weights.word.shape[0]),
             max_pos=int(weights.pos.shape[0]), embed_ln_eps=embed_ln_eps, layer_ln_eps=layer_ln_eps,
             has_token_type=int(weights.type is not None), precision=L.PREC_BF16 if precision == "bf16" else L.PREC_TF32,
-            chunk_tokens=int(chunk_tokens))
+            chunk_tokens=int(chunk_tokens), arch=L.ARCH_MODERNBERT if arch == "modernbert" else L.ARCH_POST_LN,
+            rope_base=float(rope_base), final_ln_eps=float(final_ln_eps))
         h = C.c_void_p()
         self.dev.check(self.lib.grilly_encoder_create(self.dev.ctx, C.byref(cfg), C.byref(h)))
         self.handle = h
@@ -85,6 +116,8 @@ class SentenceEncoder:
         self.dev.check(self.lib.grilly_encoder_set_weight(self.handle, name.encode(), layer, a.ctypes.data, a.size))
 
     def _upload(self, w: EncoderWeights) -> None:
+        if self.arch == "modernbert":
+            return self._upload_modernbert(w)
         self._set("word", -1, w.word)
         self._set("pos", -1, w.pos)
         if w.type is not None:
@@ -100,6 +133,27 @@ class SentenceEncoder:
             self._set("w1", i, lw["ffn_w1"]); self._set("b1", i, lw["ffn_b1"])
             self._set("w2", i, lw["ffn_w2"]); self._set("b2", i, lw["ffn_b2"])
             self._set("ln2_g", i, lw["ffn_ln_gamma"]); self._set("ln2_b", i, lw["ffn_ln_beta"])
+
+    def _upload_modernbert(self, w: EncoderWeights) -> None:
+        self._set("word", -1, w.word)
+        self._set("pos", -1, np.zeros((1, self.hidden), np.float32) if w.pos is None else w.pos)   # unused: positions are RoPE
+        self._set("emb_ln_g", -1, w.emb_ln_g)
+        self._set("emb_ln_b", -1, w.emb_ln_b)
+        self._set("final_g", -1, w.final_norm_weight)
+        self._set("final_b", -1, w.final_norm_bias)
+        for i, lw in enumerate(w.layers):
+            self._set("wqkv", i, np.concatenate([lw["attn_q_weight"], lw["attn_k_weight"], lw["attn_v_weight"]], 0))
+            self._set("bqkv", i, np.concatenate([lw["attn_q_bias"], lw["attn_k_bias"], lw["attn_v_bias"]], 0))
+            self._set("wo", i, lw["attn_out_weight"]); self._set("bo", i, lw["attn_out_bias"])
+            self._set("ln2_g", i, lw["ffn_ln_gamma"]); self._set("ln2_b", i, lw["ffn_ln_beta"])
+            # rows (up_j, gate_j): the pair epilogue computes first * gelu(second)  (:893-918: gelu(gate) * up)
+            ffn = lw["ffn_gate_weight"].shape[0]
+            wgu = np.empty((2 * ffn, self.hidden), np.float32)
+            wgu[0::2], wgu[1::2] = lw["ffn_up_weight"], lw["ffn_gate_weight"]
+            bgu = np.empty(2 * ffn, np.float32)
+            bgu[0::2], bgu[1::2] = lw["ffn_up_bias"], lw["ffn_gate_bias"]
+            self._set("wgu", i, wgu); self._set("bgu", i, bgu)
+            self._set("w2", i, lw["ffn_w2"]); self._set("b2", i, lw["ffn_b2"])
 
     def encode_ids(self, input_ids, attention_mask=None, out: np.ndarray | None = None) -> np.ndarray:
         """input_ids (B, S) ints, attention_mask (B, S) 1 = token / 0 = padding (prefix masks run packed, masks with holes run padded).

@@ -233,20 +233,61 @@ int grilly_embed_layernorm(grilly_ctx* ctx, const int* ids_dev, const int* cu_se
 int grilly_mean_pool(grilly_ctx* ctx, const float* x_dev, const float* mask_dev, const int* cu_seqlens_dev,
                      float* out_dev, int B, int S, int F, int normalize);
 
-/* ---- resident sentence encoder (post-LN BERT / MiniLM shape) ------------------------------ */
-/* VulkanSentenceTransformer.encode utils/vulkan_sentence_transformer.py:1109-1219 with the BERT branch of
- * _forward_layer :972-1033; weights live on the device between calls. */
+/* ---- backward pass and optimiser step (the training-side callers of the same tensors) ------------------------ */
+/* VulkanFNN.layernorm_backward backend/fnn.py:1701-1847 (fnn-layernorm-backward.glsl): grad_in [rows][F],
+ * grad_gamma [F] = sum_rows grad_out * x_norm, grad_beta [F] = sum_rows grad_out. gamma may be NULL (= 1); mean_dev /
+ * var_dev [rows] are the forward pass's statistics or NULL (then computed: biased variance). Deterministic (no
+ * atomics); scratch from the context's pool. */
+int grilly_layernorm_backward(grilly_ctx* ctx, const float* grad_out_dev, const float* x_dev, const float* gamma_dev,
+                              const float* mean_dev, const float* var_dev, float* grad_in_dev, float* grad_gamma_dev,
+                              float* grad_beta_dev, long long rows, int F, float eps);
+/* VulkanFNN.softmax_backward backend/fnn.py:1849-1933 (activation-softmax-backward.glsl): grad_in = y * (grad_out -
+ * sum(grad_out * y)) over the last dimension. */
+int grilly_softmax_backward(grilly_ctx* ctx, const float* grad_out_dev, const float* softmax_out_dev, float* grad_in_dev,
+                            long long rows, int cols);
+/* VulkanBackwardOps.attention_backward backend/autograd_core.py:609-646 (attention-backward.glsl): all tensors in the
+ * (B, H, S, D) layout that function uses, attn_weights (B, H, S, S) from the forward pass:
+ *   grad_v = A^T dO; grad_scores = softmax_backward(dO V^T, A) * scale; grad_q = grad_scores K; grad_k = grad_scores^T Q.
+ * fp32 products (batched, shared-memory tiled); scratch of B*H*S*S floats from the context's pool. */
+int grilly_attention_backward(grilly_ctx* ctx, const float* grad_out_dev, const float* q_dev, const float* k_dev, const float* v_dev,
+                              const float* attn_weights_dev, float* grad_q_dev, float* grad_k_dev, float* grad_v_dev, int B, int H,
+                              int S, int D, float scale);
+/* VulkanLearning.adam_update backend/learning.py:967-1077 (adam-update.glsl), in place on the device:
+ * m = b1 m + (1-b1) g; v = b2 v + (1-b2) g^2; w -= lr (m / (1 - b1^t)) / (sqrt(v / (1 - b2^t)) + eps); the bias
+ * corrections are skipped when beta^t >= 1, as in the reference's CPU branch; clear_grad zeroes g. */
+int grilly_adam_update(grilly_ctx* ctx, float* weights_dev, float* gradients_dev, float* moment1_dev, float* moment2_dev, long long n,
+                       float learning_rate, float beta1, float beta2, float epsilon, float beta1_t, float beta2_t, int clear_grad);
+/* out[c][r] = in[r][c] on the device: the grad_output^T operand of VulkanFNN.linear_backward's weight gradient
+ * (backend/fnn.py:1548-1573 transposes on the host). */
+int grilly_transpose_2d(grilly_ctx* ctx, const float* in_dev, float* out_dev, int rows, int cols);
+
+/* ---- resident sentence encoder ---------------------------------------------------------------- */
+/* VulkanSentenceTransformer.encode utils/vulkan_sentence_transformer.py:1109-1219; weights live on the device between
+ * calls. Two layer architectures, as _forward_layer has them:
+ *   GRILLY_ARCH_POST_LN   the BERT / DistilBERT / MiniLM branch (:972-1033): attention, LayerNorm(x + attn), GELU FFN,
+ *                         LayerNorm(x + ffn); learned positions and token type added to the embeddings; masked mean pool.
+ *   GRILLY_ARCH_MODERNBERT the pre-norm branch (:799-970): q/k/v from x itself (the attention norm is the identity),
+ *                         rotate-half RoPE on q and k, x += attn, LayerNorm before a GeGLU MLP
+ *                         (gelu(x Wgate^T) * (x Wup^T)) Wo), x += mlp; no position table; a final LayerNorm after the
+ *                         last layer and CLS pooling (first token) as encode() does for this model type (:1150-1181). */
+enum { GRILLY_ARCH_POST_LN = 0, GRILLY_ARCH_MODERNBERT = 1 };
 typedef struct grilly_encoder_config {
   int num_layers, hidden, num_heads, ffn, vocab, max_pos;
   float embed_ln_eps, layer_ln_eps;
   int has_token_type;   /* add token-type row 0 (BERT) */
   int precision;        /* GRILLY_PREC_TF32 or GRILLY_PREC_BF16 */
   int chunk_tokens;     /* process at most this many tokens at once so activations stay L2-resident; 0 = all */
+  int arch;             /* GRILLY_ARCH_POST_LN or GRILLY_ARCH_MODERNBERT (tf32 mode only) */
+  float rope_base;      /* MODERNBERT: RoPE base (local_rope_theta, :843-846) */
+  float final_ln_eps;   /* MODERNBERT: epsilon of the final LayerNorm */
 } grilly_encoder_config;
 
 int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, grilly_encoder** enc);
-/* name in {word, pos, type, emb_ln_g, emb_ln_b} (layer = -1) or {wqkv, bqkv, wo, bo, ln1_g, ln1_b, w1, b1, w2, b2,
- * ln2_g, ln2_b} (layer >= 0); data are fp32 host arrays in the reference's (out, in) layout. */
+/* name in {word, pos, type, emb_ln_g, emb_ln_b, final_g, final_b} (layer = -1) or {wqkv, bqkv, wo, bo, ln1_g, ln1_b, w1,
+ * b1, w2, b2, ln2_g, ln2_b, wgu, bgu} (layer >= 0); data are fp32 host arrays in the reference's (out, in) layout.
+ * MODERNBERT uses wqkv, bqkv, wo, bo, ln2_g/ln2_b (the MLP norm), w2/b2 (the MLP's output projection) and wgu / bgu:
+ * the (2 ffn, hidden) matrix whose rows alternate (up_j, gate_j) -- the row that multiplies first, the row that goes
+ * through GELU second -- and the bias interleaved the same way; final_g / final_b are the final LayerNorm. */
 int grilly_encoder_set_weight(grilly_encoder* enc, const char* name, int layer, const float* data_host, size_t count);
 /* ids_host int32 [B][S]; mask_host fp32 [B][S] (1 = token, 0 = padding) or NULL; out_host fp32 [B][hidden]:
  * mean-pooled, L2-normalised embeddings.  Includes the host->device and device->host copies.  Rows of ones followed
@@ -289,6 +330,14 @@ int grilly_faiss_distances(grilly_ctx* ctx, const float* queries, const float* d
  * index) and their column indices. Exact selection; 1 <= k <= min(num_database, 1024). Asynchronous. */
 int grilly_faiss_topk(grilly_ctx* ctx, const float* distances, int num_queries, int num_database, int k,
                       unsigned int* indices_out, float* distances_out);
+
+/* compute_distances followed by topk (backend/faiss.py:25-104 then :120-195, the two calls of the reference's search
+ * examples, README.md:117-122) without the (num_queries, num_database) matrix: the database is walked in chunks whose
+ * distance block stays in L2, each block is reduced to its k best per query at once, and the chunks' winners are
+ * merged. Same values, indices and tie order as grilly_faiss_distances + grilly_faiss_topk. 1 <= k <= min(num_database,
+ * 1024). Scratch (one chunk's split operands, one block, the candidates) from the context's pool. Asynchronous. */
+int grilly_faiss_search(grilly_ctx* ctx, const float* queries, const float* database, int num_queries, int num_database, int dim,
+                        int k, int distance_type, unsigned int* indices_out, float* distances_out);
 
 /* ---- host-side planning helpers (no GPU needed; exposed so the host logic can be tested on CPU) ------------- */
 /* N-tile (64/128/192/256) the GEMM launcher picks for an M x N output on a GPU with num_sms SMs. */

@@ -285,6 +285,40 @@ def encoder_layer(x, lw, mask, num_heads, eps=1e-5):
     return layernorm(f + x, lw["ffn_ln_gamma"], lw["ffn_ln_beta"], eps)
 
 
+def modernbert_layer(x, lw, mask, num_heads, rope_base=10000.0, eps=1e-5):
+    """Pre-norm ModernBERT layer: utils/vulkan_sentence_transformer.py:799-970 (NumPy branches). The attention norm is
+    the identity; q and k get rotate-half RoPE (positions 0..S-1); x += attn; LayerNorm; GeGLU MLP
+    (gelu(n Wgate^T + bgate) * (n Wup^T + bup)) W2^T + b2; x += mlp. The reference's clips (+-50 on the GELU input,
+    +-1e6 elsewhere) do not act on finite activations of this size and are left out."""
+    b, s, hid = x.shape
+    d = hid // num_heads
+    q = linear(x, lw["attn_q_weight"], lw["attn_q_bias"]).reshape(b, s, num_heads, d)
+    k = linear(x, lw["attn_k_weight"], lw["attn_k_bias"]).reshape(b, s, num_heads, d)
+    v = linear(x, lw["attn_v_weight"], lw["attn_v_bias"]).reshape(b, s, num_heads, d)
+    q, k = rope_rotate_half(q, None, rope_base, 1.0), rope_rotate_half(k, None, rope_base, 1.0)
+    a = attention(q, k, v, key_mask=mask).reshape(b, s, hid)
+    x = (np.asarray(x, np.float64) + linear(a, lw["attn_out_weight"], lw["attn_out_bias"])).astype(F32)
+    n = layernorm(x, lw["ffn_ln_gamma"], lw["ffn_ln_beta"], eps)
+    h = (gelu(linear(n, lw["ffn_gate_weight"], lw["ffn_gate_bias"])).astype(np.float64)
+         * linear(n, lw["ffn_up_weight"], lw["ffn_up_bias"])).astype(F32)
+    return (np.asarray(x, np.float64) + linear(h, lw["ffn_w2"], lw["ffn_b2"])).astype(F32)
+
+
+def modernbert_forward(ids, mask, w, num_heads, rope_base=10000.0, embed_eps=1e-12, layer_eps=1e-5, final_eps=1e-5,
+                       return_hidden=False):
+    """ModernBERT sentence encoder as ``encode`` runs it (utils/vulkan_sentence_transformer.py:1145-1201): token
+    embeddings, embedding LayerNorm (no positions), the layers, the final LayerNorm, CLS pooling, L2 normalise."""
+    ids = np.asarray(ids)
+    b, s = ids.shape
+    x = layernorm(embedding_lookup(ids, w["word"]), w["emb_ln_g"], w["emb_ln_b"], embed_eps)
+    mask = np.ones((b, s), dtype=F32) if mask is None else np.asarray(mask, dtype=F32)
+    for lw in w["layers"]:
+        x = modernbert_layer(x, lw, mask, num_heads, rope_base, layer_eps)
+    x = layernorm(x, w["final_norm_weight"], w["final_norm_bias"], final_eps)
+    out = embedding_normalize(x[:, 0, :])
+    return (out, x) if return_hidden else out
+
+
 def encoder_forward(ids, mask, w, num_heads, embed_eps=1e-12, layer_eps=1e-5, return_hidden=False):
     """MiniLM/BERT sentence encoder: embeddings (utils/vulkan_sentence_transformer.py:620-705), embedding
     LayerNorm (:726-744), the layers (:972-1033), masked mean pool (:1185-1191), L2 normalise (:1196-1201).
@@ -301,6 +335,52 @@ def encoder_forward(ids, mask, w, num_heads, embed_eps=1e-12, layer_eps=1e-5, re
         x = encoder_layer(x, lw, mask, num_heads, layer_eps)
     out = embedding_normalize(mean_pool(x, mask))
     return (out, x) if return_hidden else out
+
+
+# --------------------------------------------------------------------------- backward pass and optimiser
+def layernorm_backward(grad_output, x, gamma, mean=None, var=None, eps=1e-5):
+    """(grad_input, grad_gamma, grad_beta) of LayerNorm: the CPU branch of backend/fnn.py:1733-1751 (the same maths as
+    backend/autograd_core.py:566-606), in float64."""
+    go, x = np.asarray(grad_output, np.float64), np.asarray(x, np.float64)
+    mean = x.mean(axis=-1, keepdims=True) if mean is None else np.asarray(mean, np.float64).reshape(x.shape[:-1] + (1,))
+    var = x.var(axis=-1, keepdims=True) if var is None else np.asarray(var, np.float64).reshape(x.shape[:-1] + (1,))
+    std = np.sqrt(var + eps)
+    x_norm = (x - mean) / std
+    lead = tuple(range(x.ndim - 1))
+    grad_gamma, grad_beta = np.sum(go * x_norm, axis=lead), np.sum(go, axis=lead)
+    n = x.shape[-1]
+    dxn = go * (1.0 if gamma is None else np.asarray(gamma, np.float64))
+    dvar = np.sum(dxn * (x - mean) * (-0.5) * (var + eps) ** (-1.5), axis=-1, keepdims=True)
+    dmean = np.sum(dxn * (-1.0 / std), axis=-1, keepdims=True) + dvar * np.mean(-2.0 * (x - mean), axis=-1, keepdims=True)
+    grad_input = dxn / std + dvar * 2.0 * (x - mean) / n + dmean / n
+    return grad_input.astype(F32), grad_gamma.astype(F32), grad_beta.astype(F32)
+
+
+def softmax_backward(grad_output, softmax_output, dim=-1):
+    """s * (g - sum(g * s)): backend/fnn.py:1869-1872, backend/autograd_core.py:550-564."""
+    g, s = np.asarray(grad_output, np.float64), np.asarray(softmax_output, np.float64)
+    return (s * (g - np.sum(g * s, axis=dim, keepdims=True))).astype(F32)
+
+
+def attention_backward(grad_output, q, k, v, attn_weights, scale):
+    """(grad_q, grad_k, grad_v) on the (B, H, S, D) layout: backend/autograd_core.py:609-646,
+    shaders/attention-backward.glsl (grad_V = A^T dO; grad_scores = softmax_backward(dO V^T, A) * scale;
+    grad_Q = grad_scores K; grad_K = grad_scores^T Q)."""
+    go, q, k, v, a = (np.asarray(t, np.float64) for t in (grad_output, q, k, v, attn_weights))
+    grad_v = np.matmul(a.swapaxes(-2, -1), go)
+    grad_attn = np.matmul(go, v.swapaxes(-2, -1))
+    gs = a * (grad_attn - np.sum(grad_attn * a, axis=-1, keepdims=True)) * scale
+    return np.matmul(gs, k).astype(F32), np.matmul(gs.swapaxes(-2, -1), q).astype(F32), grad_v.astype(F32)
+
+
+def adam_update(w, g, m1, m2, lr, beta1=0.9, beta2=0.999, eps=1e-8, beta1_t=0.0, beta2_t=0.0):
+    """One Adam step (new weights, moment1, moment2): CPU branch of backend/learning.py:1003-1010, adam-update.glsl."""
+    w, g, m1, m2 = (np.asarray(t, np.float64) for t in (w, g, m1, m2))
+    m1n = beta1 * m1 + (1.0 - beta1) * g
+    m2n = beta2 * m2 + (1.0 - beta2) * g * g
+    mh = m1n / (1.0 - beta1_t) if beta1_t < 1.0 else m1n
+    vh = m2n / (1.0 - beta2_t) if beta2_t < 1.0 else m2n
+    return (w - lr * mh / (np.sqrt(vh) + eps)).astype(F32), m1n.astype(F32), m2n.astype(F32)
 
 
 # --------------------------------------------------------------------------- vector search

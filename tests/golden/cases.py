@@ -77,3 +77,43 @@ def linear_backward():
     rng = np.random.default_rng(11)
     return dict(grad_out=rng.standard_normal((3, 40, 160)).astype(f32), x=rng.standard_normal((3, 40, 96)).astype(f32),
                 w=(rng.standard_normal((160, 96)) / 10).astype(f32), bias=np.zeros(160, f32))
+
+
+def backward_ops():
+    """Training-side ops: LayerNorm backward on (4, 33, 96) with an offset input, softmax backward on (6, 5, 37),
+    attention backward on (B 2, H 3, S 20, D 16) with its forward softmax weights, one Adam step on 1000 values; seed 12."""
+    rng = np.random.default_rng(12)
+    ln_x = (rng.standard_normal((4, 33, 96)) * 2 + 0.7).astype(f32)
+    ln_go = rng.standard_normal((4, 33, 96)).astype(f32)
+    ln_g = (1 + 0.2 * rng.standard_normal(96)).astype(f32)
+    sm_logits = rng.standard_normal((6, 5, 37)) * 2
+    e = np.exp(sm_logits - sm_logits.max(-1, keepdims=True))
+    sm_y = (e / e.sum(-1, keepdims=True)).astype(f32)
+    sm_go = rng.standard_normal((6, 5, 37)).astype(f32)
+    q, k, v, go = (rng.standard_normal((2, 3, 20, 16)).astype(f32) for _ in range(4))
+    scale = 0.25
+    sc = np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), k.astype(np.float64)) * scale
+    ew = np.exp(sc - sc.max(-1, keepdims=True))
+    aw = (ew / ew.sum(-1, keepdims=True)).astype(f32)
+    w, g = rng.standard_normal(1000).astype(f32), rng.standard_normal(1000).astype(f32)
+    m1, m2 = (0.1 * rng.standard_normal(1000)).astype(f32), (0.01 * rng.random(1000)).astype(f32)
+    return dict(ln_x=ln_x, ln_go=ln_go, ln_g=ln_g, sm_y=sm_y, sm_go=sm_go, q=q, k=k, v=v, go=go, aw=aw, scale=scale,
+                w=w, g=g, m1=m1, m2=m2, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, beta1_t=0.9 ** 3, beta2_t=0.999 ** 3)
+
+
+def modernbert_layer():
+    """One pre-norm ModernBERT layer (hidden 384, 12 heads, GeGLU width 576), std 0.02, seed 13."""
+    rng = np.random.default_rng(13)
+    hid, ffn, B, S = 384, 576, 3, 40
+    n = lambda *s: (rng.standard_normal(s) * 0.02).astype(f32)  # noqa: E731
+    lw = {
+        "attn_q_weight": n(hid, hid), "attn_q_bias": n(hid), "attn_k_weight": n(hid, hid), "attn_k_bias": n(hid),
+        "attn_v_weight": n(hid, hid), "attn_v_bias": n(hid), "attn_out_weight": n(hid, hid), "attn_out_bias": n(hid),
+        "ffn_ln_gamma": (1 + n(hid)).astype(f32), "ffn_ln_beta": n(hid),
+        "ffn_gate_weight": n(ffn, hid), "ffn_gate_bias": n(ffn), "ffn_up_weight": n(ffn, hid), "ffn_up_bias": n(ffn),
+        "ffn_w2": n(hid, ffn), "ffn_b2": n(hid),
+    }
+    x = rng.standard_normal((B, S, hid)).astype(f32)
+    lens = np.array([40, 13, 27])
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(f32)
+    return dict(lw=lw, x=x, mask=mask, num_heads=12)

@@ -129,6 +129,37 @@ def main_extras(src: str) -> None:
     b = cases.linear_backward()
     gi, gw, gb = VulkanFNN(None, None, {}).linear_backward(b["grad_out"], b["x"], b["w"], b["bias"])
     g.update(lb_grad_input=np.asarray(gi, np.float32), lb_grad_weight=np.asarray(gw, np.float32), lb_grad_bias=np.asarray(gb, np.float32))
+    # backward ops through the reference's CPU branches (no shaders registered): backend/fnn.py:1733-1751 and
+    # :1869-1872, backend/autograd_core.py:609-646, backend/learning.py:1003-1010
+    from grilly.backend.autograd_core import VulkanBackwardOps
+    from grilly.backend.learning import VulkanLearning
+    c = cases.backward_ops()
+    fnn = VulkanFNN(None, None, {})
+    gi, gg, gbeta = fnn.layernorm_backward(c["ln_go"], c["ln_x"], c["ln_g"])
+    g.update(lnb_grad_input=np.asarray(gi, np.float32), lnb_grad_gamma=np.asarray(gg, np.float32), lnb_grad_beta=np.asarray(gbeta, np.float32))
+    g["smb_grad_input"] = np.asarray(fnn.softmax_backward(c["sm_go"], c["sm_y"]), np.float32)
+    ops = VulkanBackwardOps(backend=types.SimpleNamespace())
+    gq, gk, gv = ops.attention_backward(c["go"], c["q"], c["k"], c["v"], c["aw"], c["scale"])
+    g.update(atb_grad_q=np.asarray(gq, np.float32), atb_grad_k=np.asarray(gk, np.float32), atb_grad_v=np.asarray(gv, np.float32))
+    learn = object.__new__(VulkanLearning)
+    learn.shaders = {}
+    wn, m1n, m2n = learn.adam_update(c["w"], c["g"], c["m1"], c["m2"], c["lr"], c["beta1"], c["beta2"], c["eps"], c["beta1_t"], c["beta2_t"])
+    g.update(adam_w=np.asarray(wn, np.float32), adam_m1=np.asarray(m1n, np.float32), adam_m2=np.asarray(m2n, np.float32))
+    # one ModernBERT (pre-norm, RoPE, GeGLU) layer through the reference's NumPy branches
+    # (utils/vulkan_sentence_transformer.py:799-970; RoPE by VulkanAttention._rope_cpu, attention by _attention_cpu)
+    import inspect
+    import logging
+    from grilly.backend.attention import VulkanAttention
+    from grilly.utils.vulkan_sentence_transformer import VulkanSentenceTransformer
+    m = cases.modernbert_layer()
+    st = object.__new__(VulkanSentenceTransformer)
+    st.model_type = "modernbert"
+    st.config = types.SimpleNamespace(hidden_size=384, num_attention_heads=m["num_heads"], local_rope_theta=10000.0, rope_scaling=None)
+    st.backend = types.SimpleNamespace(attention=VulkanAttention(None, None, {}))
+    logging.disable(logging.CRITICAL)
+    kwargs = {"layer_idx": 0} if "layer_idx" in inspect.signature(st._forward_layer).parameters else {}
+    g["mb_y"] = np.asarray(st._forward_layer(m["x"], m["lw"], m["mask"], **kwargs), np.float32)
+    logging.disable(logging.NOTSET)
     np.savez_compressed(OUT_EXTRAS, **g)
     print(f"wrote {OUT_EXTRAS} ({OUT_EXTRAS.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 

@@ -101,3 +101,35 @@ def test_end_to_end_search_on_device(backend):
     assert np.array_equal(idx, ref_idx)
     with pytest.raises(Exception):
         backend.faiss.topk(np.zeros((1, 3000), np.float32), 2000)    # k above 1024 is rejected, not truncated
+
+
+@pytest.mark.parametrize("nq,ndb,dim,k", [(10, 1000, 256, 20), (8192, 5000, 64, 10), (3, 200000, 32, 100), (1, 7, 5, 7), (600, 2500, 384, 1)])
+@pytest.mark.parametrize("kind", ["cosine", "l2"])
+def test_search_equals_distances_then_topk(backend, nq, ndb, dim, k, kind):
+    """faiss.search never writes the (nq, ndb) matrix (the database is walked in chunks that are reduced to their k
+    best at once); values, indices and the order of ties are those of compute_distances followed by topk."""
+    rng = np.random.default_rng(nq + ndb)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    d = rng.standard_normal((ndb, dim)).astype(np.float32)
+    if ndb >= 100:
+        d[ndb // 2] = d[3]              # exact duplicates in different chunks: equal distances, the lower index first
+        d[ndb - 1] = d[3]
+    idx, val = backend.faiss.search(q, d, k, kind)
+    full = backend.faiss.compute_distances(q, d, kind)
+    idx2, val2 = backend.faiss.topk(full, k)
+    assert idx.dtype == np.uint32 and idx.shape == (nq, k) and val.shape == (nq, k)
+    assert np.array_equal(val, val2)
+    assert np.array_equal(idx, idx2)
+    ref_idx, ref_val = O.faiss_topk(O.faiss_distances(q[:64], d, kind), k)
+    np.testing.assert_allclose(val[:64], ref_val, rtol=1e-4, atol=5e-5)
+
+
+def test_search_flat_alias_and_errors(backend):
+    c = cases.faiss_search()
+    idx, val = backend.faiss_search(c["queries"], c["database"], 5, "dot")
+    want = np.argsort(O.faiss_distances(c["queries"], c["database"], "dot"), axis=1, kind="stable")[:, :5]
+    assert np.array_equal(idx, want.astype(np.uint32))
+    with pytest.raises(ValueError):
+        backend.faiss.search(c["queries"], c["database"][:, :-1], 5)
+    with pytest.raises(ValueError):
+        backend.faiss.search(c["queries"], c["database"], 0)
