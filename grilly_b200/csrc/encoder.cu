@@ -276,7 +276,7 @@ extern "C" int grilly_plan_chunks(const int* lengths, int B, int chunk_tokens, i
 static int forward_device_nolock(grilly_encoder* e, const int* ids_dev, const int* lengths, int B, int S, float* out_dev,
                                  int* cu_host_staging) {
   grilly_ctx* ctx = e->ctx;
-  if (S > e->cfg.max_pos) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sequence length exceeds the position table");
+  if (e->cfg.arch == GRILLY_ARCH_POST_LN && S > e->cfg.max_pos) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sequence length exceeds the position table");
   for (int b = 0; b < B; ++b)
     if (lengths[b] < 0 || lengths[b] > S) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: a valid length is outside [0, S]");
   std::vector<ChunkPlan> plan;
@@ -313,7 +313,7 @@ static int forward_device_nolock(grilly_encoder* e, const int* ids_dev, const in
 // mask applied as a key mask in attention and as the pooling mask, exactly as the reference does.
 static int forward_padded_nolock(grilly_encoder* e, const int* ids_dev, const float* mask_dev, int B, int S, float* out_dev) {
   grilly_ctx* ctx = e->ctx;
-  if (S > e->cfg.max_pos) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sequence length exceeds the position table");
+  if (e->cfg.arch == GRILLY_ARCH_POST_LN && S > e->cfg.max_pos) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sequence length exceeds the position table");
   int per_chunk = B;
   if (e->cfg.chunk_tokens > 0) per_chunk = std::max(1, e->cfg.chunk_tokens / S);
   int rc = ensure_workspace(e, static_cast<long long>(std::min(per_chunk, B)) * S);

@@ -81,7 +81,8 @@ def test_adam_update(backend, ref):
     c = cases.backward_ops()
     w, m1, m2 = backend.learning.adam_update(c["w"], c["g"], c["m1"], c["m2"], c["lr"], c["beta1"], c["beta2"], c["eps"],
                                              c["beta1_t"], c["beta2_t"])
-    assert O.rel_l2(w, ref["adam_w"]) < 2e-6 and O.rel_l2(m1, ref["adam_m1"]) < 2e-6 and O.rel_l2(m2, ref["adam_m2"]) < 2e-6
+    # the kernel forms 1 - beta in fp32 like adam-update.glsl does; 1 - 0.999f is 1.3e-5 off 0.001, which shows in m2
+    assert O.rel_l2(w, ref["adam_w"]) < 2e-6 and O.rel_l2(m1, ref["adam_m1"]) < 2e-6 and O.rel_l2(m2, ref["adam_m2"]) < 2e-5
     # shape is kept; beta^t = 1 switches the bias correction off as in the reference's CPU branch
     w2 = c["w"].reshape(10, 100)
     out = backend.learning.adam_update(w2, c["g"].reshape(10, 100), c["m1"].reshape(10, 100), c["m2"].reshape(10, 100), 1e-3,
@@ -89,6 +90,6 @@ def test_adam_update(backend, ref):
     want = O.adam_update(w2, c["g"].reshape(10, 100), c["m1"].reshape(10, 100), c["m2"].reshape(10, 100), 1e-3, beta1_t=1.0, beta2_t=1.0)
     assert out[0].shape == (10, 100)
     for a, b in zip(out, want):
-        assert O.rel_l2(a, b) < 2e-6
+        assert O.rel_l2(a, b) < 2e-5
     with pytest.raises(ValueError):
         backend.learning.adam_update(c["w"], c["g"][:5], c["m1"], c["m2"], 1e-3)
