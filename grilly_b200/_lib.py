@@ -17,7 +17,7 @@ ERR_INVALID_ARG, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = -1,
 PREC_TF32, PREC_BF16, PREC_TF32X3 = 0, 1, 2
 ACT_NONE, ACT_GELU, ACT_SILU, ACT_RELU = 0, 1, 2, 3
 NORM_LAYER, NORM_RMS = 0, 1
-ELT_GELU, ELT_SILU, ELT_RELU, ELT_ADD, ELT_SWIGLU = 1, 2, 3, 4, 5
+ELT_GELU, ELT_SILU, ELT_RELU, ELT_ADD, ELT_SWIGLU, ELT_GCU, ELT_ROSWISH = 1, 2, 3, 4, 5, 6, 7
 ROPE_NONE, ROPE_INTERLEAVED, ROPE_ROTATE_HALF = 0, 1, 2
 DIST_L2, DIST_COSINE, DIST_DOT = 1, 2, 3
 ARCH_POST_LN, ARCH_MODERNBERT = 0, 1
@@ -78,6 +78,7 @@ SIGNATURES = {
     "grilly_layernorm": [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _i, _i],
     "grilly_softmax": [_vp, _vp, _vp, _ll, _i],
     "grilly_eltwise": [_vp, _i, _vp, _vp, _vp, _ll, _i],
+    "grilly_activation_params": [_vp, _i, _vp, _vp, _ll, _f, _f],
     "grilly_embedding_lookup": [_vp, _vp, _vp, _vp, _ll, _i, _i],
     "grilly_embed_layernorm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i],
     "grilly_mean_pool": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],

@@ -79,7 +79,7 @@ class FNN(_Namespace):
 
     # ---- GEMM family ------------------------------------------------------------------------
     def _linear(self, x, weights, bias, act, residual=None, flags=0, w_tag="", w_transform=None, n_out=None,
-                precision=None):
+                precision=None, post=None):
         mode = self._mode(precision)
         bf16, x3 = mode == "bf16", mode == "tf32x3"
         w_shape = weights.shape
@@ -112,6 +112,8 @@ class FNN(_Namespace):
         y = self.dev.empty((M, n_cols), "f32")
         self.dev.check(self.lib.grilly_linear(self.ctx, _p(xd), _p(wd), _p(bd), _p(rd), _p(y), M, n_rows_w, K + kpad,
                                               act, _PREC[mode], flags))
+        if post is not None:                      # (op, p0, p1): an activation the GEMM epilogue does not carry
+            self.dev.check(self.lib.grilly_activation_params(self.ctx, post[0], _p(y), _p(y), y.size, float(post[1]), float(post[2])))
         return self._out(y, host, x_shape[:-1] + (n_cols,))
 
     def linear(self, x, weights, bias=None, precision=None):
@@ -169,6 +171,29 @@ class FNN(_Namespace):
         out = self._out(y, host, x_shape[:-1] + (N,))
         scratch.free()
         return out
+
+    def _act_params(self, op, x, p0=0.0, p1=0.0):
+        xd, host = self._act_in(x, mma_operand=False)
+        y = self.dev.empty(tuple(x.shape))
+        self.dev.check(self.lib.grilly_activation_params(self.ctx, op, _p(xd), _p(y), xd.size, float(p0), float(p1)))
+        return self._out(y, host)
+
+    def activation_gcu(self, input_data):
+        """Growing cosine unit x * cos(x): backend/fnn.py:385-440."""
+        return self._act_params(L.ELT_GCU, input_data)
+
+    def activation_roswish(self, input_data, alpha=1.0, beta=1.0):
+        """RoSwish (x + alpha) * sigmoid(beta * x) - alpha / 2: backend/fnn.py:442-497."""
+        return self._act_params(L.ELT_ROSWISH, input_data, alpha, beta)
+
+    def fused_linear_gcu(self, x, weights, bias=None, precision=None):
+        """gcu(x @ W.T + b): backend/fnn.py:2307-2385 (fused-linear-gcu.glsl). The GEMM and the activation run back to
+        back on the device (the GEMM's epilogue carries GELU, SiLU and ReLU; x cos x is applied to its result in place)."""
+        return self._linear(x, weights, bias, L.ACT_NONE, precision=precision, post=(L.ELT_GCU, 0.0, 0.0))
+
+    def fused_linear_roswish(self, x, weights, bias=None, alpha=1.0, beta=1.0, precision=None):
+        """roswish(x @ W.T + b): backend/fnn.py:2387-2463 (fused-linear-roswish.glsl); GEMM then the activation in place."""
+        return self._linear(x, weights, bias, L.ACT_NONE, precision=precision, post=(L.ELT_ROSWISH, alpha, beta))
 
     def fused_qkv_projection(self, x, w_qkv, b_qkv=None, num_heads=None, head_dim=None, precision=None):
         """x @ [Wq;Wk;Wv].T + [bq;bk;bv] -> (..., 3*H*D), column blocks Q, K, V: fused-qkv-projection.glsl:48-74."""

@@ -643,6 +643,13 @@ int grilly_eltwise(grilly_ctx* ctx, int op, const float* a, const float* b, floa
   return launch_eltwise(ctx, op, a, b, y, n, half);
 }
 
+int grilly_activation_params(grilly_ctx* ctx, int op, const float* x, float* y, long long n, float p0, float p1) {
+  CTX_GUARD(ctx);
+  if (!x || !y) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "activation: null operand");
+  if (op != GRILLY_ELT_GCU && op != GRILLY_ELT_ROSWISH) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "activation: op must be GRILLY_ELT_GCU or GRILLY_ELT_ROSWISH");
+  return launch_act_params(ctx, op, x, y, n, p0, p1);
+}
+
 int grilly_embedding_lookup(grilly_ctx* ctx, const int* ids, const float* table, float* out, long long n_tokens, int vocab,
                             int F) {
   CTX_GUARD(ctx);

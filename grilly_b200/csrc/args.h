@@ -7,7 +7,7 @@ enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU = 3 };
 enum : int { ROPE_NONE = 0, ROPE_INTERLEAVED = 1, ROPE_ROTATE_HALF = 2 };
 enum : int { NORM_LAYER = 0, NORM_RMS = 1 };
 enum : int { DIST_NONE = 0, DIST_L2 = 1, DIST_COSINE = 2, DIST_DOT = 3 };
-enum : int { ELT_GELU = 1, ELT_SILU = 2, ELT_RELU = 3, ELT_ADD = 4, ELT_SWIGLU = 5 };
+enum : int { ELT_GELU = 1, ELT_SILU = 2, ELT_RELU = 3, ELT_ADD = 4, ELT_SWIGLU = 5, ELT_GCU = 6, ELT_ROSWISH = 7 };
 
 struct GemmArgs {
   int M, N, K;

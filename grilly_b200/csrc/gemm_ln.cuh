@@ -21,8 +21,8 @@
 //
 // Roles per CTA: warp 0 operand TMA producer, warp 1 MMA issuer + TMEM allocation, warp 2 residual TMA producer,
 // warps 3..6 epilogue (one per TMEM lane quadrant). Every wait is bounded (ptx.cuh); a wait that gives up records a
-// status, raises the abort flag of both CTAs and the pair drains. Loads touch this GPU's memory only; nothing is
-// multicast.
+// status, raises the abort flag of both CTAs and the pair drains. Every load is a per-CTA load of this GPU's own
+// memory.
 #pragma once
 #include "gemm.cuh"
 

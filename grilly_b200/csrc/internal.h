@@ -130,6 +130,7 @@ int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, c
 int launch_norm(grilly_ctx* ctx, const NormArgs& a);
 int launch_softmax(grilly_ctx* ctx, const float* x, float* y, long long rows, int cols);
 int launch_eltwise(grilly_ctx* ctx, int op, const float* a, const float* b, float* y, long long n, int half);
+int launch_act_params(grilly_ctx* ctx, int op, const float* a, float* y, long long n, float p0, float p1);
 int launch_round_tf32(grilly_ctx* ctx, const float* x, float* y, long long n);
 int launch_f32_to_bf16(grilly_ctx* ctx, const float* x, void* y, long long n);
 int launch_bf16_to_f32(grilly_ctx* ctx, const void* x, float* y, long long n);

@@ -49,6 +49,14 @@ int launch_eltwise(grilly_ctx* ctx, int op, const float* a, const float* b, floa
   return GRILLY_OK;
 }
 
+int launch_act_params(grilly_ctx* ctx, int op, const float* a, float* y, long long n, float p0, float p1) {
+  if (n <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "activation: n must be positive");
+  act_params_kernel<<<grid_for(n, 256 * 4, ctx->num_sms, 16), 256, 0, ctx->stream>>>(op, a, y, n, p0, p1);
+  ctx->launches++;
+  GB_CUDA_CHECK(ctx, cudaGetLastError());
+  return GRILLY_OK;
+}
+
 int launch_round_tf32(grilly_ctx* ctx, const float* x, float* y, long long n) {
   if (n <= 0) return GRILLY_OK;
   round_tf32_kernel<<<grid_for(n, 256 * 4, ctx->num_sms, 16), 256, 0, ctx->stream>>>(x, y, n);

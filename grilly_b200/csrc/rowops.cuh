@@ -185,6 +185,17 @@ __global__ void __launch_bounds__(256) eltwise_kernel(int op, const float* __res
   }
 }
 
+// Activations with parameters: GCU x cos(x) (backend/fnn.py:385-440, activation-gcu.glsl) and RoSwish
+// (x + alpha) sigmoid(beta x) - alpha / 2 (backend/fnn.py:442-497, activation-roswish.glsl).
+__global__ void __launch_bounds__(256) act_params_kernel(int op, const float* __restrict__ a, float* __restrict__ y, long long n,
+                                                         float p0, float p1) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float x = a[i];
+    y[i] = op == ELT_GCU ? x * cosf(x) : (x + p0) / (1.f + expf(-p1 * x)) - 0.5f * p0;
+  }
+}
+
 __global__ void __launch_bounds__(256) round_tf32_kernel(const float* __restrict__ x, float* __restrict__ y, long long n) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)

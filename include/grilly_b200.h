@@ -41,7 +41,8 @@ enum {
 enum { GRILLY_PREC_TF32 = 0, GRILLY_PREC_BF16 = 1, GRILLY_PREC_TF32X3 = 2 };
 enum { GRILLY_ACT_NONE = 0, GRILLY_ACT_GELU = 1, GRILLY_ACT_SILU = 2, GRILLY_ACT_RELU = 3 };
 enum { GRILLY_NORM_LAYER = 0, GRILLY_NORM_RMS = 1 };
-enum { GRILLY_ELT_GELU = 1, GRILLY_ELT_SILU = 2, GRILLY_ELT_RELU = 3, GRILLY_ELT_ADD = 4, GRILLY_ELT_SWIGLU = 5 };
+enum { GRILLY_ELT_GELU = 1, GRILLY_ELT_SILU = 2, GRILLY_ELT_RELU = 3, GRILLY_ELT_ADD = 4, GRILLY_ELT_SWIGLU = 5,
+       GRILLY_ELT_GCU = 6, GRILLY_ELT_ROSWISH = 7 };
 enum { GRILLY_ROPE_NONE = 0, GRILLY_ROPE_INTERLEAVED = 1, GRILLY_ROPE_ROTATE_HALF = 2 };
 enum { GRILLY_DIST_L2 = 1, GRILLY_DIST_COSINE = 2, GRILLY_DIST_DOT = 3 };  /* faiss-distance.glsl:25 (there 0, 1, 2) */
 
@@ -220,6 +221,11 @@ int grilly_softmax(grilly_ctx* ctx, const float* x_dev, float* y_dev, long long 
  * half = output width for GRILLY_ELT_SWIGLU (input rows are 2*half wide). */
 int grilly_eltwise(grilly_ctx* ctx, int op, const float* a_dev, const float* b_dev, float* y_dev, long long n,
                    int half);
+/* activation_gcu backend/fnn.py:385-440 (x cos x; op GRILLY_ELT_GCU, p0 and p1 unused) and activation_roswish
+ * backend/fnn.py:442-497 ((x + alpha) sigmoid(beta x) - alpha / 2; op GRILLY_ELT_ROSWISH, p0 = alpha, p1 = beta). May run
+ * in place (y == x): fused_linear_gcu / fused_linear_roswish (backend/fnn.py:2307-2463) are grilly_linear followed by
+ * this on the result, on the device. */
+int grilly_activation_params(grilly_ctx* ctx, int op, const float* x_dev, float* y_dev, long long n, float p0, float p1);
 /* VulkanLearning.embedding_lookup backend/learning.py:811-877 (embedding-lookup.glsl:28-55) */
 int grilly_embedding_lookup(grilly_ctx* ctx, const int* ids_dev, const float* table_dev, float* out_dev,
                             long long n_tokens, int vocab, int F);

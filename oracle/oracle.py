@@ -51,6 +51,18 @@ def relu(x):
     return np.maximum(np.asarray(x, dtype=F32), F32(0))
 
 
+def gcu(x):
+    """x * cos(x): backend/fnn.py:399-400, utils/numba_ops.py (numba_gcu)."""
+    x = np.asarray(x, dtype=np.float64)
+    return (x * np.cos(x)).astype(F32)
+
+
+def roswish(x, alpha=1.0, beta=1.0):
+    """(x + alpha) * sigmoid(beta x) - alpha / 2: backend/fnn.py:456-457."""
+    x = np.asarray(x, dtype=np.float64)
+    return ((x + alpha) / (1.0 + np.exp(-beta * x)) - 0.5 * alpha).astype(F32)
+
+
 def fused_linear_gelu(x, w, b=None):
     """backend/fnn.py:2022-2123 (falls back to linear then activation_gelu, :2043-2046)."""
     return gelu(linear(x, w, b))

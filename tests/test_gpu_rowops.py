@@ -98,3 +98,16 @@ def test_bounded_wait_reports_timeout_and_context_survives(backend):
     dev.sync()  # the status word was cleared: no second report
     x = np.arange(12, dtype=np.float32).reshape(3, 4)
     assert np.array_equal(backend.fnn.activation_relu(x - 5), np.maximum(x - 5, 0))
+
+
+def test_gcu_and_roswish(backend):
+    """activation_gcu / activation_roswish and their fused-linear forms (backend/fnn.py:385-497, 2307-2463)."""
+    rng = np.random.default_rng(60)
+    x = (rng.standard_normal((7, 50)) * 3).astype(np.float32)
+    assert O.rel_l2(backend.fnn.activation_gcu(x), O.gcu(x)) < 2e-6
+    assert O.rel_l2(backend.fnn.activation_roswish(x, alpha=0.7, beta=1.3), O.roswish(x, 0.7, 1.3)) < 2e-6
+    xs = rng.standard_normal((3, 40, 96)).astype(np.float32)
+    w, b = (rng.standard_normal((64, 96)) / 10).astype(np.float32), rng.standard_normal(64).astype(np.float32)
+    y = backend.fnn.fused_linear_gcu(xs, w, b)
+    assert y.shape == (3, 40, 64) and O.rel_l2(y, O.gcu(O.linear(xs, w, b))) < 2e-3
+    assert O.rel_l2(backend.fnn.fused_linear_roswish(xs, w, b, alpha=0.5, beta=2.0), O.roswish(O.linear(xs, w, b), 0.5, 2.0)) < 2e-3
