@@ -20,17 +20,32 @@ import math
 import numpy as np
 
 from . import _lib as L
+from .clocks import ClockSampler
 from .device import Device
 
 
+LAST_CLOCKS = {}
+
+
 def _time(dev, fn, warmup, reps):
+    """ms per launch (CUDA events on the library's stream); the SM clocks sampled over the timed launches are left in
+    LAST_CLOCKS and printed with the number."""
     for _ in range(warmup):
         fn()
     dev.sync()
+    sampler = ClockSampler(getattr(dev, "index", 0)).start()
     dev.timer_start()
     for _ in range(reps):
         fn()
-    return dev.timer_stop() / reps
+    ms = dev.timer_stop() / reps
+    LAST_CLOCKS.clear()
+    LAST_CLOCKS.update(sampler.stop())
+    return ms
+
+
+def _clk() -> str:
+    c = LAST_CLOCKS
+    return f"[SM {c.get('sm_mhz')} of {c.get('sm_max_mhz')} MHz, reasons {c.get('reasons')}, {c.get('samples')} samples]"
 
 
 def _nsplit(a):
@@ -65,12 +80,16 @@ def _nsplit(a):
         step()
     torch.cuda.synchronize()
     dist.barrier()
+    sampler = ClockSampler(rank_local).start() if dist.get_rank() == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(a.reps):
         step()
     e1.record()
     torch.cuda.synchronize()
+    if sampler is not None:
+        LAST_CLOCKS.clear()
+        LAST_CLOCKS.update(sampler.stop())
     t = torch.tensor([e0.elapsed_time(e1) / a.reps], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if dist.get_rank() == 0:
@@ -78,7 +97,7 @@ def _nsplit(a):
         sent = (world - 1) / world * a.m * a.n * 4.0
         how = ("peer copies" if a.p2p_copy else "epilogue stores to peers") if a.fused else "all-gather"
         print(f"gemm n-split x{world} {a.m}x{a.n}x{a.k} {a.precision}: {ms * 1e3:.1f} us (max over ranks)  "
-              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s aggregate  {how} {sent / ms / 1e6:.1f} GB/s sent per GPU")
+              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s aggregate  {how} {sent / ms / 1e6:.1f} GB/s sent per GPU  {_clk()}")
     backend.cleanup()
     dist.destroy_process_group()
 
@@ -170,7 +189,7 @@ def main(argv=None):
             fn = lambda: dev.check(lib.grilly_faiss_distances(ctx, q.ptr, db.ptr, dist.ptr, a.m, a.n, a.k, L.DIST_COSINE))  # noqa: E731
             ms = _time(dev, fn, a.warmup, a.reps)
             print(f"faiss distances {a.m} x {a.n} x {a.k}: {ms * 1e3:.1f} us/launch  {2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s "
-                  f"(fp32 dot products; the split GEMM does 3x that)  {4.0 * (a.m * a.k + a.n * a.k + a.m * a.n) / ms / 1e6:.1f} GB/s (algorithmic)")
+                  f"(fp32 dot products; the split GEMM does 3x that)  {4.0 * (a.m * a.k + a.n * a.k + a.m * a.n) / ms / 1e6:.1f} GB/s (algorithmic)  {_clk()}")
             fn = lambda: dev.check(lib.grilly_faiss_topk(ctx, dist.ptr, a.m, a.n, a.topk, idx.ptr, val.ptr))  # noqa: E731
             flops = 0.0
             nbytes = 4.0 * a.m * a.n                       # every distance read once
@@ -184,7 +203,7 @@ def main(argv=None):
             nbytes = 8.0 * a.m * a.n
         ms = _time(dev, fn, a.warmup, a.reps)
         dev.sync()
-        print(f"{a.op} {vars(a)}\n  {ms * 1e3:.1f} us/launch  {flops / ms / 1e9:.1f} TFLOP/s  {nbytes / ms / 1e6:.1f} GB/s (algorithmic)")
+        print(f"{a.op} {vars(a)}\n  {ms * 1e3:.1f} us/launch  {flops / ms / 1e9:.1f} TFLOP/s  {nbytes / ms / 1e6:.1f} GB/s (algorithmic)  {_clk()}")
     finally:
         dev.close()
 
