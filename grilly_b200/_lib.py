@@ -74,6 +74,7 @@ SIGNATURES = {
     "grilly_attention_scores": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f],
     "grilly_attention_mask": [_vp, _vp, _vp, _i, _i, _i, _i, _f],
     "grilly_attention_output": [_vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "grilly_attention_output_ex": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i],
     "grilly_apply_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i],
     "grilly_layernorm": [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _i, _i],
     "grilly_softmax": [_vp, _vp, _vp, _ll, _i],

@@ -618,18 +618,25 @@ class Attention(_Namespace):
         return self._out(sd, host)
 
     def attention_output(self, attention_weights, values, num_heads, head_dim):
-        """weights @ V -> (B, S, H, D): backend/attention.py:205-300."""
+        """weights @ V -> (B, Sq, H, D): backend/attention.py:205-300. As the reference picks a shader by the backend's
+        architecture (backend/attention.py:226-229, backend/shader_registry.py:154-156), 'gpt' / 'granite' sum the keys
+        k <= q only (attention-output-gpt.glsl) and 't5' takes weights (B, H, Sq, Sk) over encoder values
+        (B, Sk, H, D) (attention-output-t5.glsl); every other architecture is the square bidirectional form."""
         wshape = tuple(int(s) for s in attention_weights.shape)
         if len(wshape) != 4:
             raise ValueError("attention_weights must be (B, H, S, S)")
-        B, H, S, _ = wshape
+        B, H, Sq, Sk = wshape
+        arch = (self.architecture or "").lower()
+        if arch != "t5" and Sq != Sk:
+            raise ValueError("attention_weights must be (B, H, S, S)")
         vB, vS, vH, D = self._bshd(values, num_heads, head_dim)
-        if (vB, vS, vH) != (B, S, H):
+        if (vB, vS, vH) != (B, Sk, H):
             raise ValueError("values do not match the attention weights")
         wd, host = self._act_in(attention_weights, mma_operand=False)
         vd, _ = self._act_in(values, mma_operand=False)
-        out = self.dev.empty((B, S, H, D))
-        self.dev.check(self.lib.grilly_attention_output(self.ctx, _p(wd), _p(vd), _p(out), B, S, H, D))
+        out = self.dev.empty((B, Sq, H, D))
+        causal = int(arch in ("gpt", "granite"))
+        self.dev.check(self.lib.grilly_attention_output_ex(self.ctx, _p(wd), _p(vd), _p(out), B, Sq, Sk, H, D, causal))
         return self._out(out, host)
 
     def attention_backward(self, grad_output, q, k, v, attn_weights, scale):
@@ -856,7 +863,8 @@ class Compute:
         self.faiss_search = self.faiss.search
 
     def set_architecture(self, architecture: str):
-        """backend/compute.py:70-128. There are no per-architecture kernels here: causal masking is a flag."""
+        """backend/compute.py:70-128: selects the form of ``attention.attention_output`` ('gpt' / 'granite' causal,
+        't5' decoder-over-encoder); everything else takes causal masking as a flag."""
         self.architecture = architecture
         self.attention.architecture = architecture
 

@@ -599,9 +599,14 @@ int grilly_attention_mask(grilly_ctx* ctx, float* scores, const float* mask, int
 }
 
 int grilly_attention_output(grilly_ctx* ctx, const float* weights, const float* v, float* out, int B, int S, int H, int D) {
+  return grilly_attention_output_ex(ctx, weights, v, out, B, S, S, H, D, 0);
+}
+
+int grilly_attention_output_ex(grilly_ctx* ctx, const float* weights, const float* v, float* out, int B, int Sq, int Sk, int H, int D,
+                               int causal) {
   CTX_GUARD(ctx);
   if (!weights || !v || !out) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_output: null operand");
-  return launch_attn_output(ctx, weights, v, out, B, S, H, D);
+  return launch_attn_output(ctx, weights, v, out, B, Sq, Sk, H, D, causal ? 1 : 0);
 }
 
 int grilly_apply_rope(grilly_ctx* ctx, const float* x, float* y, const int* position_ids, int B, int S, int H, int D,

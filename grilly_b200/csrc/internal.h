@@ -142,7 +142,7 @@ int launch_fold_ln(grilly_ctx* ctx, const float* w, const float* gamma, const fl
 int get_rope_table(grilly_ctx* ctx, int S, int D, float base, float scaling, const float** cos_t, const float** sin_t);
 int launch_attn_scores(grilly_ctx* ctx, const float* q, const float* k, float* scores, int B, int S, int H, int D, float scale);
 int launch_attn_mask(grilly_ctx* ctx, float* scores, const float* mask, int B, int H, int S, int use_causal, float mask_value);
-int launch_attn_output(grilly_ctx* ctx, const float* w, const float* v, float* out, int B, int S, int H, int D);
+int launch_attn_output(grilly_ctx* ctx, const float* w, const float* v, float* out, int B, int Sq, int Sk, int H, int D, int causal);
 int launch_rope_rows(grilly_ctx* ctx, bool bf16, const void* src, void* dst, long long rows, long long pitch, int H, int D,
                      int S, const int* cu_seqlens, int B, const float* cos_t, const float* sin_t, int style);
 int launch_rope_apply(grilly_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,

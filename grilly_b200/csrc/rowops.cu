@@ -191,9 +191,9 @@ int launch_attn_mask(grilly_ctx* ctx, float* scores, const float* mask, int B, i
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;
 }
-int launch_attn_output(grilly_ctx* ctx, const float* w, const float* v, float* out, int B, int S, int H, int D) {
-  if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_output: sizes must be positive");
-  attn_output_kernel<<<grid_for(static_cast<long long>(B) * H * S, 8, ctx->num_sms), 256, 0, ctx->stream>>>(w, v, out, B, S, H, D);
+int launch_attn_output(grilly_ctx* ctx, const float* w, const float* v, float* out, int B, int Sq, int Sk, int H, int D, int causal) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0 || D <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "attention_output: sizes must be positive");
+  attn_output_kernel<<<grid_for(static_cast<long long>(B) * H * Sq, 8, ctx->num_sms), 256, 0, ctx->stream>>>(w, v, out, B, Sq, Sk, H, D, causal);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());
   return GRILLY_OK;

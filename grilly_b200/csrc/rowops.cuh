@@ -375,22 +375,25 @@ __global__ void __launch_bounds__(256) attn_mask_kernel(float* __restrict__ scor
     else if (mask[b * S + kk] < 0.5f) scores[i] = mask_value;
   }
 }
-// out[b,q,h,:] = sum_k W[b,h,q,k] V[b,k,h,:]; one warp per (b,h,q), lanes over the head dim.
+// out[b,q,h,:] = sum_k W[b,h,q,k] V[b,k,h,:]; one warp per (b,h,q), lanes over the head dim. W is (B,H,Sq,Sk) and V
+// (B,Sk,H,D): Sq == Sk for attention-output.glsl; causal keeps k <= q (attention-output-gpt.glsl); Sq != Sk is the
+// decoder-over-encoder form of attention-output-t5.glsl.
 __global__ void __launch_bounds__(256) attn_output_kernel(const float* __restrict__ w, const float* __restrict__ v,
-                                                          float* __restrict__ out, int B, int S, int H, int D) {
+                                                          float* __restrict__ out, int B, int Sq, int Sk, int H, int D, int causal) {
   const int lane = threadIdx.x & 31;
-  const long long n_rows = static_cast<long long>(B) * H * S;
+  const long long n_rows = static_cast<long long>(B) * H * Sq;
   const int warps_per_block = blockDim.x >> 5;
   for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < n_rows;
        row += static_cast<long long>(gridDim.x) * warps_per_block) {
-    const int qi = static_cast<int>(row % S);
-    const int h = static_cast<int>((row / S) % H);
-    const int b = static_cast<int>(row / (static_cast<long long>(S) * H));
-    const float* wp = w + row * S;
+    const int qi = static_cast<int>(row % Sq);
+    const int h = static_cast<int>((row / Sq) % H);
+    const int b = static_cast<int>(row / (static_cast<long long>(Sq) * H));
+    const float* wp = w + row * Sk;
+    const int k_end = causal ? min(qi + 1, Sk) : Sk;
     for (int d = lane; d < D; d += 32) {
       float acc = 0.f;
-      for (int kk = 0; kk < S; ++kk) acc = fmaf(__ldg(wp + kk), __ldg(v + ((static_cast<long long>(b) * S + kk) * H + h) * D + d), acc);
-      out[((static_cast<long long>(b) * S + qi) * H + h) * D + d] = acc;
+      for (int kk = 0; kk < k_end; ++kk) acc = fmaf(__ldg(wp + kk), __ldg(v + ((static_cast<long long>(b) * Sk + kk) * H + h) * D + d), acc);
+      out[((static_cast<long long>(b) * Sq + qi) * H + h) * D + d] = acc;
     }
   }
 }

@@ -204,6 +204,11 @@ int grilly_attention_mask(grilly_ctx* ctx, float* scores_dev, const float* mask_
 /* attention_output backend/attention.py:205-300 (attention-output.glsl:28-70): weights (B,H,S,S), v (B,S,H,D) -> (B,S,H,D) */
 int grilly_attention_output(grilly_ctx* ctx, const float* weights_dev, const float* v_dev, float* out_dev, int B, int S,
                             int H, int D);
+/* The architecture-specific forms the reference's registry selects for attention_output (backend/shader_registry.py:154-156,
+ * backend/attention.py:226-229): causal != 0 sums keys k <= q only (attention-output-gpt.glsl, also used for 'granite');
+ * Sq != Sk is the decoder-over-encoder form (attention-output-t5.glsl): weights (B,H,Sq,Sk), v (B,Sk,H,D) -> (B,Sq,H,D). */
+int grilly_attention_output_ex(grilly_ctx* ctx, const float* weights_dev, const float* v_dev, float* out_dev, int B, int Sq,
+                               int Sk, int H, int D, int causal);
 /* stand-alone RoPE on (B,S,H,D) fp32, VulkanAttention.apply_rope backend/attention.py:599-676 (rope.glsl:52-126);
  * position_ids_dev int32 [B][S] or NULL for 0..S-1; max_pos = number of table rows to build. */
 int grilly_apply_rope(grilly_ctx* ctx, const float* x_dev, float* y_dev, const int* position_ids_dev, int B, int S,

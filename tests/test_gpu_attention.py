@@ -169,3 +169,30 @@ def test_unfused_pipeline_matches_flash_and_oracle(backend):
     cm = a.attention_mask(a.attention_scores(q.reshape(B, S, H * D), k.reshape(B, S, H * D), H, D), use_causal=True)
     assert np.all(cm[:, :, 3, 4:] == np.float32(-1e9)) and np.all(cm[:, :, 3, :4] == scores[:, :, 3, :4])
     assert np.array_equal(a.attention_mask(scores, use_causal=False), scores)
+
+
+def test_attention_output_architecture_forms(backend):
+    """attention_output as the reference's registry selects it (backend/shader_registry.py:154-156): the causal sum of
+    attention-output-gpt.glsl and the decoder-over-encoder form of attention-output-t5.glsl."""
+    rng = np.random.default_rng(77)
+    B, H, S, D, Sk = 2, 3, 37, 16, 53
+    w = rng.random((B, H, S, S)).astype(np.float32)
+    v = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    try:
+        backend.set_architecture("gpt")
+        got = backend.attention.attention_output(w, v, H, D)
+        ref = np.einsum("bhqk,bkhd->bqhd", np.tril(w).astype(np.float64), v.astype(np.float64))
+        assert got.shape == (B, S, H, D) and O.rel_l2(got, ref) < 2e-6
+        backend.set_architecture("t5")
+        wx = rng.random((B, H, S, Sk)).astype(np.float32)
+        ve = rng.standard_normal((B, Sk, H, D)).astype(np.float32)
+        got = backend.attention.attention_output(wx, ve, H, D)
+        ref = np.einsum("bhqk,bkhd->bqhd", wx.astype(np.float64), ve.astype(np.float64))
+        assert got.shape == (B, S, H, D) and O.rel_l2(got, ref) < 2e-6
+        backend.set_architecture("bert")
+        with pytest.raises(ValueError):
+            backend.attention.attention_output(wx, ve, H, D)
+        got = backend.attention.attention_output(w, v, H, D)
+        assert O.rel_l2(got, np.einsum("bhqk,bkhd->bqhd", w.astype(np.float64), v.astype(np.float64))) < 2e-6
+    finally:
+        backend.set_architecture(None)
