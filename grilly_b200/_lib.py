@@ -56,6 +56,7 @@ SIGNATURES = {
     "grilly_free": [_vp, _vp],
     "grilly_upload": [_vp, _vp, _vp, _sz],
     "grilly_download": [_vp, _vp, _vp, _sz],
+    "grilly_memset": [_vp, _vp, _i, _sz],
     "grilly_copy_2d": [_vp, _vp, _sz, _vp, _sz, _sz, _sz],
     "grilly_host_alloc": [_vp, _sz, _pp],
     "grilly_host_free": [_vp, _vp],

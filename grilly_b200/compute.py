@@ -510,11 +510,41 @@ class Attention(_Namespace):
                 raise ValueError("rope_style must be 'interleaved' or 'rotate_half'")
             rope = L.ROPE_INTERLEAVED if rope_style == "interleaved" else L.ROPE_ROTATE_HALF
         sc = float(scale) if scale is not None else 1.0 / math.sqrt(D)
-        out = self.dev.empty((B, S, H, D))
+        Dk = self._kernel_head_dim(D, S, bool(causal) or rope != L.ROPE_NONE)
+        if Dk != D:
+            # a head dim between the kernels' sizes runs zero-padded: zero columns of q, k add nothing to a score and
+            # zero columns of v give output columns that are dropped again (all on the device)
+            if rope != L.ROPE_NONE:
+                raise ValueError(f"use_rope needs head_dim in {self._head_dims(S, True)} ({self._b.precision} mode)")
+            qd, kd, vd = (self._pad_heads(t, B * S * H, D, Dk) for t in (qd, kd, vd))
+        out = self.dev.empty((B, S, H, Dk))
         self.dev.check(self.lib.grilly_flash_attention(
-            self.ctx, _p(qd), _p(kd), _p(vd), _p(out), B, S, H, D, H * D, H * D, None, B * S, _p(md), sc, int(bool(causal)),
+            self.ctx, _p(qd), _p(kd), _p(vd), _p(out), B, S, H, Dk, H * Dk, H * Dk, None, B * S, _p(md), sc, int(bool(causal)),
             rope, float(rope_base), float(rope_scaling), L.PREC_BF16 if self._bf16 else L.PREC_TF32, 0))
-        return self._out(out, host)
+        if Dk != D:
+            out = self._pad_heads(out, B * S * H, Dk, D)
+        return self._out(out, host, (B, S, H, D))
+
+    def _head_dims(self, S: int, general: bool):
+        """Head dims the attention kernels are instantiated for."""
+        if not self._bf16:
+            return (32, 64, 96, 128)
+        return (64, 128) if (general or S > 128) else (32, 64, 128)
+
+    def _kernel_head_dim(self, D: int, S: int, general: bool) -> int:
+        for d in self._head_dims(S, general):
+            if D <= d:
+                return d
+        raise ValueError(f"head_dim {D} exceeds 128")
+
+    def _pad_heads(self, t: DeviceTensor, rows: int, d_from: int, d_to: int) -> DeviceTensor:
+        """(rows, d_from) -> (rows, d_to) on the device: zero-padded when d_to > d_from, cut when smaller."""
+        elt = 2 if t.dtype == "bf16" else 4
+        out = self.dev.empty((rows, d_to), t.dtype)
+        if d_to > d_from:
+            self.dev.check(self.lib.grilly_memset(self.ctx, _p(out), 0, rows * d_to * elt))
+        self.dev.check(self.lib.grilly_copy_2d(self.ctx, _p(out), d_to * elt, _p(t), d_from * elt, min(d_from, d_to) * elt, rows))
+        return out
 
     def _attention_fp32(self, queries, keys, values, B, S, H, D, scale, mask, causal, use_rope, rope_base, rope_scaling,
                         rope_style):

@@ -302,6 +302,13 @@ int grilly_download(grilly_ctx* ctx, void* dst, const void* src, size_t bytes) {
   return check_device_status(ctx);
 }
 
+int grilly_memset(grilly_ctx* ctx, void* dst, int byte_value, size_t nbytes) {
+  CTX_GUARD(ctx);
+  if (!dst && nbytes) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "memset: null destination");
+  if (nbytes) GB_CUDA_CHECK(ctx, cudaMemsetAsync(dst, byte_value, nbytes, ctx->stream));
+  return GRILLY_OK;
+}
+
 int grilly_copy_2d(grilly_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes,
                    size_t rows) {
   CTX_GUARD(ctx);

@@ -111,10 +111,12 @@ int launch_attention(grilly_ctx* ctx, bool bf16, const void* q, const void* k, c
   if (args.H > 65535 || args.B > 65535) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "attention: B and H are limited to 65535 for sequences longer than 128");
   if (!bf16 && args.D == 32) return launch_one<32, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   if (!bf16 && args.D == 64) return launch_one<64, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+  if (!bf16 && args.D == 96) return launch_one<96, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
+  if (!bf16 && args.D == 128) return launch_one<128, false>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   if (bf16 && args.D == 64) return launch_one<64, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   if (bf16 && args.D == 128) return launch_one<128, true>(ctx, q, k, v, ld_q, ld_k, ld_v, total_rows, args);
   return set_error(ctx, GRILLY_ERR_UNSUPPORTED,
-                   "attention: head_dim must be 32 or 64 (tf32 mode), 64 or 128 (bf16 mode), or 32 in bf16 mode for sequences up to 128");
+                   "attention: head_dim must be 32, 64, 96 or 128 (tf32 mode), 64 or 128 (bf16 mode), or 32 in bf16 mode for sequences up to 128");
 }
 
 }  // namespace gb

@@ -33,7 +33,7 @@ template <int D, bool kBf16>
 struct AttnCfg {
   static constexpr int ELT = kBf16 ? 2 : 4;
   static constexpr int NCH = D * ELT / 128;            // 128-B chunks per Q/K/V row
-  static_assert(D * ELT % 128 == 0 && NCH >= 1 && NCH <= 2, "head_dim*elt must be 128 or 256 bytes");
+  static_assert(D * ELT % 128 == 0 && NCH >= 1 && NCH <= 4 && D <= 128, "head_dim*elt must be 128, 256, 384 or 512 bytes");
   static constexpr int Q_BYTES = NCH * ATTN_CHUNK_BYTES;
   static constexpr int SMEM_BYTES = 3 * Q_BYTES + 1024 + 128;
   // TMEM columns: S (fp32 scores, overwritten in place by P in the MMA operand precision) at [0,128),

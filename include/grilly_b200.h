@@ -104,6 +104,8 @@ int grilly_download(grilly_ctx* ctx, void* dst_host, const void* src_dev, size_t
  * handing peer memory to any kernel. No counterpart in the reference (no multi-GPU code, CHANGELOG.md:75). */
 int grilly_copy_2d(grilly_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes,
                    size_t rows);
+/* Fills nbytes at dst_dev with a byte value on the context's stream (cudaMemsetAsync). */
+int grilly_memset(grilly_ctx* ctx, void* dst_dev, int byte_value, size_t nbytes);
 /* pinned host staging memory for the two calls above */
 int grilly_host_alloc(grilly_ctx* ctx, size_t bytes, void** hptr);
 int grilly_host_free(grilly_ctx* ctx, void* hptr);

@@ -196,3 +196,31 @@ def test_attention_output_architecture_forms(backend):
         assert O.rel_l2(got, np.einsum("bhqk,bkhd->bqhd", w.astype(np.float64), v.astype(np.float64))) < 2e-6
     finally:
         backend.set_architecture(None)
+
+
+@pytest.mark.parametrize("D,S,causal", [(96, 200, False), (128, 300, True), (128, 100, False), (80, 150, True), (48, 64, False), (16, 40, False)])
+def test_more_head_dims_tf32(backend, D, S, causal):
+    """Head dims 96 and 128 have their own tf32 instances of the long-sequence kernel; anything else up to 128 runs
+    zero-padded to the next instantiated size."""
+    rng = np.random.default_rng(D * 1000 + S)
+    B, H = 2, 3
+    q, k, v = (rng.standard_normal((B, S, H, D)).astype(np.float32) for _ in range(3))
+    got = backend.attention.flash_attention2(q, k, v, causal=causal)
+    ref = O.flash_attention2(q, k, v, causal=causal)
+    assert got.shape == (B, S, H, D) and O.rel_l2(got, ref) < TOL_TF32
+
+
+@pytest.mark.parametrize("D,S,causal", [(32, 300, True), (96, 200, False), (80, 64, False), (32, 64, False)])
+def test_more_head_dims_bf16(backend_bf16, D, S, causal):
+    rng = np.random.default_rng(D * 1000 + S + 1)
+    B, H = 2, 4
+    q, k, v = (rng.standard_normal((B, S, H, D)).astype(np.float32) for _ in range(3))
+    got = backend_bf16.attention.flash_attention2(q, k, v, causal=causal)
+    ref = O.flash_attention2(q, k, v, causal=causal)
+    assert got.shape == (B, S, H, D) and O.rel_l2(got, ref) < TOL_BF16
+
+
+def test_rope_with_a_padded_head_dim_is_refused(backend):
+    q = np.zeros((1, 8, 2, 48), np.float32)
+    with pytest.raises(ValueError):
+        backend.attention.flash_attention2_rope(q, q, q, causal=True)
