@@ -33,7 +33,7 @@ struct GemmArgs {
   int* err;               // device status word
 };
 
-// y = LayerNorm(x W^T + bias + residual) * gamma + beta in one kernel (gemm_ln.cuh)
+// y = LayerNorm(x W^T + bias + residual) * gamma + beta in one kernel (gemm_ln_pair.cuh)
 struct GemmLnArgs {
   int M, N, K;
   int num_tiles, num_k_blocks;

@@ -2,7 +2,7 @@
 // TMA descriptors and launches one persistent CTA per SM.
 #include "gemm.cuh"
 #include "gemm_pair.cuh"
-#include "gemm_ln.cuh"
+#include "gemm_ln_pair.cuh"
 #include "internal.h"
 
 namespace gb {
@@ -202,10 +202,10 @@ int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, 
   return launch_gemm(ctx, bf16, true, a, b, args, 0);
 }
 
-// ---- y = LayerNorm(x W^T + bias + residual) in one kernel (gemm_ln.cuh)
+// ---- y = LayerNorm(x W^T + bias + residual) in one kernel (gemm_ln_pair.cuh)
 bool gemm_ln_supported(bool bf16, int N, int K, const GemmLnArgs& a) {
   const int elt = bf16 ? 2 : 4;
-  if (N != 128 && N != 256 && N != 384 && N != 512) return false;          // whole rows in the pair's two accumulators
+  if (N != 128 && N != 256 && N != 384 && N != 512) return false;          // whole rows in one CTA's tensor memory
   if ((static_cast<long long>(K) * elt) % 16 != 0) return false;
   if (a.out_bf16 && !bf16) return false;
   if (a.residual && ((a.ld_res * elt) % 16 != 0 || (reinterpret_cast<uintptr_t>(a.residual) & 15))) return false;
@@ -213,26 +213,27 @@ bool gemm_ln_supported(bool bf16, int N, int K, const GemmLnArgs& a) {
   return true;
 }
 
-template <int NCHUNK, bool kBf16, bool kDeep>
-static int launch_ln_cfg(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
-  using Cfg = GemmLnCfg<NCHUNK, kBf16, kDeep>;
+// The shared-MMA form (gemm_ln_pair.cuh): 256 token rows per CTA pair, whole rows per CTA.
+template <int N, int SUB, int BUFS, bool kBf16>
+static int launch_ln_pair_cfg(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
+  using Cfg = GemmLnPairCfg<N, SUB, BUFS, kBf16>;
   constexpr int ELT = kBf16 ? 2 : 4;
   constexpr int BK = 128 / ELT;
   const int dtype = kBf16 ? TM_BF16 : TM_F32;
   CUtensorMap ta, tb, tr, to;
   int rc;
   if ((rc = get_tmap_2d(ctx, dtype, x, args.K, args.M, static_cast<uint64_t>(args.K) * ELT, BK, 128, &ta))) return rc;
-  if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, Cfg::NHALF, &tb))) return rc;
-  // residual boxes of 128 rows x 32 columns: fp32 rows are 128 bytes (swizzled like the output), bf16 rows 64 bytes (plain)
+  if ((rc = get_tmap_2d(ctx, dtype, w, args.K, args.N, static_cast<uint64_t>(args.K) * ELT, BK, Cfg::BH, &tb))) return rc;
+  // residual boxes of 32 rows x 32 columns: fp32 rows are 128 bytes (swizzled like the output), bf16 rows 64 bytes (plain)
   if (!args.residual) tr = ta;
-  else if ((rc = get_tmap_2d(ctx, dtype, args.residual, args.N, args.M, static_cast<uint64_t>(args.ld_res) * ELT, 32, 128, &tr,
+  else if ((rc = get_tmap_2d(ctx, dtype, args.residual, args.N, args.M, static_cast<uint64_t>(args.ld_res) * ELT, 32, 32, &tr,
                              kBf16 ? TM_SWNONE : TM_SW128))) return rc;
   if (args.out_bf16) to = ta;   // bf16 results leave through vector stores; the kernel does not touch this map
   else if ((rc = get_tmap_2d(ctx, TM_F32, args.out, args.N, args.M, static_cast<uint64_t>(args.ld_out) * 4, 32, 32, &to))) return rc;
-  args.num_tiles = (args.M + 127) / 128;
+  args.num_tiles = (args.M + 255) / 256;
   args.num_k_blocks = (args.K + BK - 1) / BK;
   args.err = ctx->err_dev;
-  auto kern = gemm_rowln_tcgen05_kernel<NCHUNK, kBf16, kDeep>;
+  auto kern = gemm_rowln_pair_kernel<N, SUB, BUFS, kBf16>;
   const void* key = reinterpret_cast<const void*>(kern);
   if (!ctx->smem_attr_done.count(key)) {
     GB_CUDA_CHECK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -244,7 +245,7 @@ static int launch_ln_cfg(grilly_ctx* ctx, const void* x, const void* w, GemmLnAr
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(GEMM_LN_THREADS, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = ctx->stream;
   cfg.attrs = attr;
@@ -269,11 +270,17 @@ static int launch_ln_cfg(grilly_ctx* ctx, const void* x, const void* w, GemmLnAr
   return GRILLY_OK;
 }
 
-template <int NCHUNK, bool kBf16>
-static int launch_ln_one(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
-  // a long K loop wants operand bytes in flight, a short one wants epilogue buffers (see GemmLnCfg)
+template <bool kBf16>
+static int launch_ln_pair(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
+  // 384 features: a long K loop is bound by the operand bytes in flight from L2 and takes a fourth stage for one
+  // staging buffer per epilogue warp; a short one is bound by the epilogue and takes three warps per TMEM lane quadrant
   const bool deep = ctx->tune.ln_deep >= 0 ? ctx->tune.ln_deep != 0 : static_cast<long long>(args.K) * (kBf16 ? 2 : 4) >= 3072;
-  return deep ? launch_ln_cfg<NCHUNK, kBf16, true>(ctx, x, w, args) : launch_ln_cfg<NCHUNK, kBf16, false>(ctx, x, w, args);
+  switch (args.N) {
+    case 128: return launch_ln_pair_cfg<128, 2, 2, kBf16>(ctx, x, w, args);
+    case 256: return launch_ln_pair_cfg<256, 2, 2, kBf16>(ctx, x, w, args);
+    case 384: return deep ? launch_ln_pair_cfg<384, 2, 1, kBf16>(ctx, x, w, args) : launch_ln_pair_cfg<384, 3, 2, kBf16>(ctx, x, w, args);
+    default: return launch_ln_pair_cfg<512, 2, 2, kBf16>(ctx, x, w, args);
+  }
 }
 
 int launch_gemm_ln(grilly_ctx* ctx, bool bf16, const void* x, const void* w, GemmLnArgs& args) {
@@ -282,12 +289,7 @@ int launch_gemm_ln(grilly_ctx* ctx, bool bf16, const void* x, const void* w, Gem
     return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "linear_layernorm: the one-kernel form needs out_features in {128, 256, 384, 512} and 16-byte aligned rows");
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "linear_layernorm: operands must be 16-byte aligned");
-  switch (args.N / 64) {
-    case 2: return bf16 ? launch_ln_one<2, true>(ctx, x, w, args) : launch_ln_one<2, false>(ctx, x, w, args);
-    case 4: return bf16 ? launch_ln_one<4, true>(ctx, x, w, args) : launch_ln_one<4, false>(ctx, x, w, args);
-    case 6: return bf16 ? launch_ln_one<6, true>(ctx, x, w, args) : launch_ln_one<6, false>(ctx, x, w, args);
-    default: return bf16 ? launch_ln_one<8, true>(ctx, x, w, args) : launch_ln_one<8, false>(ctx, x, w, args);
-  }
+  return bf16 ? launch_ln_pair<true>(ctx, x, w, args) : launch_ln_pair<false>(ctx, x, w, args);
 }
 
 }  // namespace gb

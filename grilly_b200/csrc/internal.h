@@ -71,7 +71,7 @@ struct grilly_ctx {
     int attn_hpc = 0;        // heads per work unit of the short attention kernel
     int attn_general = 0;    // 1: always the general attention kernel
     int fused_ln = 1;        // 0: linear + LayerNorm as two launches even where the one-kernel form exists
-    int ln_deep = -1;        // 0/1: never/always the deep-operand-ring variant of the one-kernel form
+    int ln_deep = -1;        // 0/1: never/always the four-stage variant of the one-kernel form at 384 features
   } tune;
   // RoPE tables, keyed by (S, D, base, scaling)
   struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };
@@ -110,7 +110,7 @@ struct PoolArgs;
 // gemm.cu
 int launch_gemm(grilly_ctx* ctx, bool bf16, bool b_mn_major, const void* a, const void* b, GemmArgs& args, int force_bn);
 int launch_gemm_multi(grilly_ctx* ctx, bool bf16, const void* a, const void* b, GemmArgs& args, void* const* extra, int n_extra);
-// y = LayerNorm(x W^T + bias + residual) in one kernel (csrc/gemm_ln.cuh); supported for out_features in
+// y = LayerNorm(x W^T + bias + residual) in one kernel (csrc/gemm_ln_pair.cuh); supported for out_features in
 // {128, 256, 384, 512}
 bool gemm_ln_supported(bool bf16, int N, int K, const GemmLnArgs& a);
 int launch_gemm_ln(grilly_ctx* ctx, bool bf16, const void* x, const void* w, GemmLnArgs& args);

@@ -249,6 +249,33 @@ def test_linear_residual_layernorm(backend, backend_bf16, M, N, K):
     assert O.rel_l2(out, two) < 1e-5
 
 
+@pytest.mark.parametrize("N,K", [(128, 256), (256, 384), (384, 384), (384, 1536), (512, 128)])
+def test_linear_residual_layernorm_many_tiles_per_cta(backend, backend_bf16, N, K):
+    """Enough rows that every CTA pair walks several 256-row tiles (both accumulators where two fit tensor memory, the
+    staging buffers reused for the next tile's residual boxes, a ragged last tile): the one-kernel form against the
+    two-launch form on all rows, and against the oracle on a spread of them."""
+    M = 74 * 256 * 5 + 77
+    rng = np.random.default_rng(N + K)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((M, N), dtype=np.float32) + 0.3
+    g, bt = (1 + 0.2 * rng.standard_normal(N)).astype(np.float32), (0.3 * rng.standard_normal(N)).astype(np.float32)
+    rows = np.r_[0:300, M // 2:M // 2 + 300, M - 400:M]
+    ref = O.layernorm(O.linear(x[rows], w, b) + res[rows], g, bt, 1e-5)
+    for be, tol, tol2 in ((backend, TOL_TF32, 1e-5), (backend_bf16, TOL_BF16, 1e-5)):
+        out = be.fnn.linear_residual_layernorm(x, w, b, res, g, bt, 1e-5)
+        be.device.set_tuning("fused_ln", 0)
+        try:
+            two = be.fnn.linear_residual_layernorm(x, w, b, res, g, bt, 1e-5)
+        finally:
+            be.device.set_tuning("fused_ln", 1)
+        assert np.isfinite(out).all()
+        assert O.rel_l2(out, two) < tol2
+        assert float(np.abs(out - two).max()) < 1e-3      # no single row is off
+        assert O.rel_l2(out[rows], ref) < tol
+
+
 def test_linear_residual_layernorm_3d_and_large_mean(backend):
     rng = np.random.default_rng(77)
     x = rng.standard_normal((3, 50, 384)).astype(np.float32)
