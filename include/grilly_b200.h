@@ -323,8 +323,10 @@ int grilly_encoder_destroy(grilly_encoder* enc);
  * peer-mapped memory of other GPUs (plain stores only): with each GPU computing one column block of a product and
  * writing it into every GPU's C at its column offset, the exchange of a column-split GEMM happens inside the kernel,
  * tile by tile, instead of in an all-gather after it. No counterpart in the reference, which has no multi-GPU code
- * (CHANGELOG.md:75). One launch at a time per GPU uses this entry point (the destination list lives in constant
- * memory of the library). Asynchronous. */
+ * (CHANGELOG.md:75). One launch of THIS entry point at a time per GPU: the destination list lives in constant memory
+ * of the library and is rewritten in stream order by every call, so two contexts or streams that overlap such
+ * launches on one GPU would mix their lists. Other GEMM launches never read the list (the multi-destination epilogue
+ * is selected by an argument of this launch alone) and may overlap freely. Asynchronous. */
 int grilly_gemm_mnk_multi(grilly_ctx* ctx, const void* a_dev, const void* b_dev, void* const* c_ptrs, int num_outputs, int M,
                           int K, int N, long long ld_c, int precision);
 
