@@ -49,20 +49,47 @@ struct AttnCfg {
 // low n bits set (n <= 0 -> none, n >= 32 -> all)
 __device__ __forceinline__ uint32_t prefix_bits(int n) { return n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u)); }
 
+// The softmax is bound by the instructions it issues per score. sm_100 has two-lane fp32 forms (one instruction
+// multiplies-adds or adds two independent pairs) and a three-input maximum: they halve the multiply-adds and additions
+// per score and cut a third of the maxima.
+__device__ __forceinline__ void fma_f32x2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{ .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd; }"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void mul_f32x2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{ .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mul.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd; }"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void add_f32x2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{ .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n add.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd; }"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float max3_f32(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Reductions over 32 registers with four independent chains (a single chain of 32 dependent ops is latency-bound).
 __device__ __forceinline__ float row_max32(const uint32_t (&r)[32]) {
-  float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
+  float m[4];
 #pragma unroll
-  for (int i = 4; i < 32; i += 4) {
-    m0 = fmaxf(m0, __uint_as_float(r[i])); m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-    m2 = fmaxf(m2, __uint_as_float(r[i + 2])); m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+  for (int q = 0; q < 4; ++q) {
+    m[q] = max3_f32(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1]), __uint_as_float(r[8 * q + 2]));
+    m[q] = max3_f32(m[q], __uint_as_float(r[8 * q + 3]), __uint_as_float(r[8 * q + 4]));
+    m[q] = max3_f32(m[q], __uint_as_float(r[8 * q + 5]), __uint_as_float(r[8 * q + 6]));
+    m[q] = fmaxf(m[q], __uint_as_float(r[8 * q + 7]));
   }
-  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  return fmaxf(max3_f32(m[0], m[1], m[2]), m[3]);
 }
 __device__ __forceinline__ float row_sum32(const float (&p)[32]) {
-  float s0 = p[0], s1 = p[1], s2 = p[2], s3 = p[3];
+  float s0 = p[0], s1 = p[1], s2 = p[2], s3 = p[3];   // two two-lane chains
 #pragma unroll
-  for (int i = 4; i < 32; i += 4) { s0 += p[i]; s1 += p[i + 1]; s2 += p[i + 2]; s3 += p[i + 3]; }
+  for (int i = 4; i < 32; i += 4) {
+    add_f32x2(s0, s1, s0, s1, p[i], p[i + 1]);
+    add_f32x2(s2, s3, s2, s3, p[i + 2], p[i + 3]);
+  }
   return (s0 + s1) + (s2 + s3);
 }
 
@@ -390,8 +417,14 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               p[i] = fast_exp2(((keepw >> i) & 1u) ? x : (((validw >> i) & 1u) ? x_masked : -INFINITY));
             }
           } else {
+            const float neg_m = -m_l2;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) p[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -m_l2));
+            for (int i = 0; i < 32; i += 2) {
+              float x0, x1;
+              fma_f32x2(x0, x1, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), sl2, sl2, neg_m, neg_m);
+              p[i] = fast_exp2(x0);
+              p[i + 1] = fast_exp2(x1);
+            }
           }
           if constexpr (kBf16) {
             // two bf16 per 32-bit column (even key in the low half): chunk c -> columns [16c, 16c+16).
@@ -419,8 +452,11 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       if (lane == 0) mbar_arrive(bar_p);
 
       l_run = l_run * alpha + l_tile;
+      // the running maximum of a row stops moving after the first key tiles: skip the rescale when no row of the warp needs it
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-      for (int d = 0; d < D; ++d) o_acc[d] *= alpha;
+        for (int d = 0; d < D; d += 2) mul_f32x2(o_acc[d], o_acc[d + 1], o_acc[d], o_acc[d + 1], alpha, alpha);
+      }
 
       if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
       tc_fence_after();
@@ -431,7 +467,9 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+          for (int i = 0; i < 32; i += 2)
+            add_f32x2(o_acc[c * 32 + i], o_acc[c * 32 + i + 1], o_acc[c * 32 + i], o_acc[c * 32 + i + 1], __uint_as_float(r[i]),
+                      __uint_as_float(r[i + 1]));
         }
       }
       tc_fence_before();
