@@ -43,7 +43,7 @@ struct AttnCfg {
   static constexpr bool SHARE_O = kBf16 && D <= 64;
   static constexpr int TMEM_COLS = SHARE_O ? 128 : 256;
   static constexpr int O_COL = SHARE_O ? 64 : ATTN_TILE;
-  static constexpr int MIN_CTAS = SHARE_O ? 3 : 1;   // four would cap registers at 96 and spill (measured slower)
+  static constexpr int MIN_CTAS = SHARE_O ? 3 : (D <= 64 ? 2 : 1);   // by TMEM columns; four would cap registers at 96 and spill (measured slower)
 };
 
 // low n bits set (n <= 0 -> none, n >= 32 -> all)
@@ -330,7 +330,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     float o_acc[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) o_acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;   // reference point of the exponentials (log2 units, integer-valued) and row sum
     const float* kmask = args.key_mask ? args.key_mask + static_cast<long long>(b) * args.S : nullptr;
     bool ok = true;
 
@@ -360,64 +360,127 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 
       float alpha = 1.f, l_tile = 0.f;
       if (warp_active) {
-        // Only tiles that touch the end of the sequence, the causal diagonal or a key mask need per-element
-        // mask logic (warp-uniform test); interior tiles work on the raw scores: max, then exp2(s*c - m*c).
+        // The exponentials of a row refer to a reference point m_ref kept in log2 units (scale folded in) and at an
+        // INTEGER value: moving it multiplies everything accumulated so far by an exact power of two.
+        // Only tiles that touch the end of the sequence, the causal diagonal or a key mask need per-element mask logic
+        // (warp-uniform test) and take two sweeps over the scores (row maximum first). Interior tiles take ONE sweep:
+        // a chunk's exponentials use the reference point as it stands, and only if a chunk's maximum has outgrown it by
+        // more than 2^8 is it moved up, with the row's earlier P chunks, row sums and accumulator scaled down to match
+        // (rare after the first key tiles; P stays at most 2^9, harmless in bf16 / tf32 and in the fp32 sums).
         const bool tile_mask = kmask != nullptr || k0 + ATTN_TILE > L || (args.causal && k0 + ATTN_TILE - 1 > q0) ||
                                !(args.scale > 0.f);
         const float sl2 = args.scale * kLog2e;
-        // ---- pass 1: row maximum
-        float m_tile = -INFINITY;
-        // bit i of validw: key kc + i exists; of the returned word: it also passes the key mask and the causal rule
-        // (warp-wide call: the key mask word comes from one load per lane and a ballot)
-        auto keep_word = [&](int kc, uint32_t validw) {
-          uint32_t w = validw;
-          if (args.causal) w &= prefix_bits(qi - kc + 1);
-          if (kmask) w &= __ballot_sync(0xffffffffu, kc + lane < L && __ldg(kmask + kc + lane) >= 0.5f);
-          return w;
-        };
+        // 2^k for an integer-valued k <= 0 (k = -inf or below the normal range gives 0)
+        auto pow2_int = [](float k) { return k < -126.f ? 0.f : __int_as_float((static_cast<int>(k) + 127) << 23); };
+        if (tile_mask) {
+          // ---- sweep 1: row maximum
+          float m_tile = -INFINITY;
+          // bit i of validw: key kc + i exists; of the returned word: it also passes the key mask and the causal rule
+          // (warp-wide call: the key mask word comes from one load per lane and a ballot)
+          auto keep_word = [&](int kc, uint32_t validw) {
+            uint32_t w = validw;
+            if (args.causal) w &= prefix_bits(qi - kc + 1);
+            if (kmask) w &= __ballot_sync(0xffffffffu, kc + lane < L && __ldg(kmask + kc + lane) >= 0.5f);
+            return w;
+          };
 #pragma unroll 1
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          if (tile_mask) {
+          for (int c = 0; c < nchunks; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+            tmem_ld_wait();
             // masked keys score -1e9 (what the reference adds), absent ones -inf
             const int kc = k0 + c * 32;
             const uint32_t validw = prefix_bits(L - kc);
             const uint32_t keepw = keep_word(kc, validw);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const float s = __uint_as_float(r[i]) * args.scale;
-              r[i] = __float_as_uint(((keepw >> i) & 1u) ? s : (((validw >> i) & 1u) ? -1e9f : -INFINITY));
+              const float sc = __uint_as_float(r[i]) * args.scale;
+              r[i] = __float_as_uint(((keepw >> i) & 1u) ? sc : (((validw >> i) & 1u) ? -1e9f : -INFINITY));
             }
             m_tile = fmaxf(m_tile, row_max32(r));
-          } else {
-            m_tile = fmaxf(m_tile, row_max32(r) * args.scale);
           }
-        }
-        const float m_new = fmaxf(m_run, m_tile);
-        alpha = fast_exp2((m_run - m_new) * kLog2e);  // 0 on the first step (m_run = -inf)
-        const float m_l2 = m_new * kLog2e;
-        m_run = m_new;
-
-        // ---- pass 2: p = exp(s - m) in the MMA operand precision, row sum, P written over S in TMEM
+          const float m_tile_l2 = m_tile * kLog2e;
+          const float new_ref = m_tile_l2 > m_ref ? ceilf(m_tile_l2) : m_ref;
+          alpha = pow2_int(m_ref - new_ref);          // 0 on the first step (m_ref = -inf)
+          m_ref = new_ref;
+          const float m_l2 = m_ref;
+          const float x_masked = -1e9f * kLog2e - m_l2;
+          // ---- sweep 2: p = exp(s - m) in the MMA operand precision, row sum, P written over S in TMEM
 #pragma unroll 1
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
-          tmem_ld_wait();
-          float p[32];
-          if (tile_mask) {
+          for (int c = 0; c < nchunks; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+            tmem_ld_wait();
+            float p[32];
             const uint32_t validw = prefix_bits(L - (k0 + c * 32));
             const uint32_t keepw = keep_word(k0 + c * 32, validw);
-            const float x_masked = -1e9f * kLog2e - m_l2;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float x = fmaf(__uint_as_float(r[i]), sl2, -m_l2);
               p[i] = fast_exp2(((keepw >> i) & 1u) ? x : (((validw >> i) & 1u) ? x_masked : -INFINITY));
             }
-          } else {
-            const float neg_m = -m_l2;
+            if constexpr (kBf16) {
+              // two bf16 per 32-bit column (even key in the low half): chunk c -> columns [16c, 16c+16).
+              // In-place is safe in increasing c: those columns hold scores of chunk c/2, already consumed.
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+              l_tile += row_sum32(p);   // the unrounded sum: bf16 rounding of P averages out over the row
+              tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
+            } else {
+              uint32_t pk[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                p[i] = round_to_tf32(p[i]);
+                pk[i] = __float_as_uint(p[i]);
+              }
+              l_tile += row_sum32(p);
+              tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
+            }
+          }
+        } else {
+          // ---- one sweep (all 32-key chunks of an interior tile are full)
+#pragma unroll 1
+          for (int c = 0; c < nchunks; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+            tmem_ld_wait();
+            const float cmax = row_max32(r) * sl2;              // scale > 0 here: the maximum commutes with it
+            const bool move = cmax > m_ref + 8.0f || m_ref == -INFINITY;
+            if (__any_sync(0xffffffffu, move)) {
+              // this lane's factor (1 for the rows that stay): exact power of two
+              float a = 1.f;
+              if (move) {
+                const float new_ref = ceilf(cmax);
+                a = pow2_int(m_ref - new_ref);
+                m_ref = new_ref;
+              }
+              tmem_st_wait();                                    // the P chunks written so far have landed
+              for (int cc = 0; cc < c; ++cc) {
+                if constexpr (kBf16) {
+                  uint32_t q[16];
+                  tmem_ld_32x16(tmem_s + lane_addr + cc * 16, q);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int i = 0; i < 16; ++i)
+                    q[i] = pack_bf16x2(__uint_as_float(q[i] << 16) * a, __uint_as_float(q[i] & 0xffff0000u) * a);
+                  tmem_st_32x16(tmem_s + lane_addr + cc * 16, q);
+                } else {
+                  uint32_t q[32];
+                  tmem_ld_32x32(tmem_s + lane_addr + cc * 32, q);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) q[i] = __float_as_uint(__uint_as_float(q[i]) * a);
+                  tmem_st_32x32(tmem_s + lane_addr + cc * 32, q);
+                }
+              }
+              l_tile *= a;
+              l_run *= a;
+#pragma unroll
+              for (int d = 0; d < D; d += 2) mul_f32x2(o_acc[d], o_acc[d + 1], o_acc[d], o_acc[d + 1], a, a);
+            }
+            float p[32];
+            const float neg_m = -m_ref;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               float x0, x1;
@@ -425,25 +488,24 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               p[i] = fast_exp2(x0);
               p[i + 1] = fast_exp2(x1);
             }
-          }
-          if constexpr (kBf16) {
-            // two bf16 per 32-bit column (even key in the low half): chunk c -> columns [16c, 16c+16).
-            // In-place is safe in increasing c: those columns hold scores of chunk c/2, already consumed.
-            uint32_t pk[16];
+            if constexpr (kBf16) {
+              uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
-            l_tile += row_sum32(p);   // the unrounded sum: bf16 rounding of P averages out over the row
-            tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
-          } else {
-            uint32_t pk[32];
+              for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+              l_tile += row_sum32(p);
+              tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
+            } else {
+              uint32_t pk[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              p[i] = round_to_tf32(p[i]);
-              pk[i] = __float_as_uint(p[i]);
+              for (int i = 0; i < 32; ++i) {
+                p[i] = round_to_tf32(p[i]);
+                pk[i] = __float_as_uint(p[i]);
+              }
+              l_tile += row_sum32(p);
+              tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
             }
-            l_tile += row_sum32(p);
-            tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
           }
+          // alpha stays 1: the accumulated sums were scaled where the reference point moved
         }
         tmem_st_wait();
       }
