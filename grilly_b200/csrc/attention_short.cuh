@@ -232,7 +232,9 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
         if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
         tc_fence_after();
         float l_sum = 0.f;
-        if (warp_active) {
+        // bf16 without a key mask takes one sweep over the scores; tf32 (twice the registers per P chunk: measured slower
+        // with one sweep) and masked launches take two
+        if (warp_active && (!kBf16 || kmask)) {
           // pass 1: row maximum (scale > 0 is folded in afterwards). Per 32-key chunk two bit words say which columns
           // exist (validw: key < L) and which also pass the key mask (keepw); a full, unmasked chunk takes the plain path.
           float m_raw = -INFINITY;
@@ -276,6 +278,81 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) p[j] = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_l2));
+            }
+            if constexpr (kBf16) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(p[2 * j], p[2 * j + 1]);
+              l_sum += row_sum32(p);
+              tmem_st_32x16(tmem_s + lane_addr + c * 16, pk);
+            } else {
+              uint32_t pk[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                p[j] = round_to_tf32(p[j]);
+                pk[j] = __float_as_uint(p[j]);
+              }
+              l_sum += row_sum32(p);
+              tmem_st_32x32(tmem_s + lane_addr + c * 32, pk);
+            }
+          }
+          tmem_st_wait();
+        } else if (warp_active) {
+          // No key mask: ONE sweep over the scores. The exponentials refer to an integer-valued reference point (log2
+          // units, scale folded in) that the first chunk sets and a later chunk moves only if its maximum has outgrown
+          // it by more than 2^8; the P chunks and the row sum accumulated so far are then scaled by the exact power of
+          // two (rare). The reference point cancels in O / l.
+          float m_ref = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < nchunks; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_s + lane_addr + c * 32, r);
+            tmem_ld_wait();
+            const uint32_t validw = prefix_bits(L - c * 32);
+            if (validw != 0xffffffffu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (!((validw >> j) & 1u)) r[j] = 0xff800000u;   // -inf: absent keys neither set the maximum nor add to the sum
+            }
+            const float cmax = row_max32(r) * sl2;               // scale > 0 in this kernel
+            const bool move = cmax > m_ref + 8.0f || m_ref == -INFINITY;
+            if (__any_sync(0xffffffffu, move)) {
+              float a = 1.f;
+              if (move) {
+                const float new_ref = ceilf(cmax);
+                const float k = m_ref - new_ref;                 // integer-valued, <= 0 (or -inf)
+                a = k < -126.f ? 0.f : __int_as_float((static_cast<int>(k) + 127) << 23);
+                m_ref = new_ref;
+              }
+              tmem_st_wait();
+              for (int cc = 0; cc < c; ++cc) {
+                if constexpr (kBf16) {
+                  uint32_t q[16];
+                  tmem_ld_32x16(tmem_s + lane_addr + cc * 16, q);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int j = 0; j < 16; ++j)
+                    q[j] = pack_bf16x2(__uint_as_float(q[j] << 16) * a, __uint_as_float(q[j] & 0xffff0000u) * a);
+                  tmem_st_32x16(tmem_s + lane_addr + cc * 16, q);
+                } else {
+                  uint32_t q[32];
+                  tmem_ld_32x32(tmem_s + lane_addr + cc * 32, q);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) q[j] = __float_as_uint(__uint_as_float(q[j]) * a);
+                  tmem_st_32x32(tmem_s + lane_addr + cc * 32, q);
+                }
+              }
+              l_sum *= a;
+            }
+            float p[32];
+            const float neg_m = -m_ref;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float x0, x1;
+              fma_f32x2(x0, x1, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), sl2, sl2, neg_m, neg_m);
+              p[j] = fast_exp2(x0);
+              p[j + 1] = fast_exp2(x1);
             }
             if constexpr (kBf16) {
               uint32_t pk[16];
