@@ -143,7 +143,8 @@ def fused_swiglu(x, w_gate, w_up, b_gate=None, b_up=None):
 
 def fused_geglu(x, w_gate, w_up, b_gate=None, b_up=None):
     """(x Wg^T + bg) * gelu_tanh(x Wu^T + bu): backend/_glu_append.py:224-262 (CPU branch :256-267). Parity unpinned:
-    that file is a fragment no class of the reference includes, so it cannot be run to generate outputs."""
+    that file is a fragment no class of the reference includes, so it cannot be run to generate outputs. The same gated
+    product inside the ModernBERT layer (utils/vulkan_sentence_transformer.py:939-947) is pinned by the layer golden."""
     g = linear(x, w_gate, b_gate).astype(np.float64)
     u = linear(x, w_up, b_up).astype(np.float64)
     return (g * (0.5 * u * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (u + 0.044715 * u ** 3))))).astype(F32)
