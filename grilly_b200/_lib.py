@@ -93,6 +93,7 @@ SIGNATURES = {
     "grilly_encoder_set_weight": [_vp, C.c_char_p, _i, _vp, _sz],
     "grilly_encoder_forward": [_vp, _vp, _vp, _i, _i, _vp],
     "grilly_encoder_forward_device": [_vp, _vp, _vp, _i, _i, _vp],
+    "grilly_encoder_io_buffers": [_vp, _i, _i, _vp, _vp],
     "grilly_encoder_keep_hidden": [_vp, _i],
     "grilly_encoder_last_hidden": [_vp, _vp, _ll, C.POINTER(_ll)],
     "grilly_encoder_destroy": [_vp],

@@ -461,7 +461,7 @@ int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* 
   if (rc) return rc;
   // the ids go on their way first: the copy runs while the host reads the mask
   const size_t n_ids = static_cast<size_t>(B) * S;
-  std::memcpy(e->ids_pin, ids_host, n_ids * sizeof(int));
+  if (ids_host != e->ids_pin) std::memcpy(e->ids_pin, ids_host, n_ids * sizeof(int));   // already staged by the caller otherwise
   GB_CUDA_CHECK(ctx, cudaMemcpyAsync(e->ids_dev, e->ids_pin, n_ids * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
   // valid lengths from the mask; the packed path needs every mask row to be a prefix of ones
   std::vector<int> lengths(B);
@@ -497,7 +497,19 @@ int grilly_encoder_forward(grilly_encoder* e, const int* ids_host, const float* 
     cudaMemsetAsync(ctx->err_dev, 0, sizeof(int), ctx->stream);
     return set_error(ctx, GRILLY_ERR_TIMEOUT, "a device-side wait gave up (kernel status " + std::to_string(code) + ")");
   }
-  std::memcpy(out_host, e->out_pin, out_bytes);
+  if (out_host != e->out_pin) std::memcpy(out_host, e->out_pin, out_bytes);
+  return GRILLY_OK;
+}
+
+int grilly_encoder_io_buffers(grilly_encoder* e, int B, int S, int** ids_pinned, float** out_pinned) {
+  if (!e || B <= 0 || S <= 0) return GRILLY_ERR_INVALID_ARG;
+  grilly_ctx* ctx = e->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  cudaSetDevice(ctx->device);
+  const int rc = ensure_io(e, B, S);
+  if (rc) return rc;
+  if (ids_pinned) *ids_pinned = e->ids_pin;
+  if (out_pinned) *out_pinned = e->out_pin;
   return GRILLY_OK;
 }
 

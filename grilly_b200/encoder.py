@@ -173,6 +173,17 @@ class SentenceEncoder:
                                                        mask.ctypes.data if mask is not None else None, B, S, out.ctypes.data))
         return out
 
+    def io_buffers(self, B: int, S: int):
+        """(ids, out): int32 (B, S) and float32 (B, hidden) NumPy views of the encoder's page-locked staging buffers.
+        Ids written there and passed to ``encode_ids(ids, mask, out=out)`` are copied to the device straight from
+        page-locked memory, and the embeddings arrive in ``out`` without a second host copy. The views stay valid until
+        a larger batch or sequence length is encoded, or the encoder is closed."""
+        ip, op = C.c_void_p(), C.c_void_p()
+        self.dev.check(self.lib.grilly_encoder_io_buffers(self.handle, int(B), int(S), C.byref(ip), C.byref(op)))
+        ids = np.ctypeslib.as_array(C.cast(ip, C.POINTER(C.c_int32)), shape=(int(B), int(S)))
+        out = np.ctypeslib.as_array(C.cast(op, C.POINTER(C.c_float)), shape=(int(B), self.hidden))
+        return ids, out
+
     def forward_device(self, ids_dev_ptr: int, lengths, B: int, S: int, out_dev_ptr: int) -> None:
         """Device buffers in and out, no copies, asynchronous (for timing the kernels alone)."""
         ln = np.ascontiguousarray(lengths, dtype=np.int32)

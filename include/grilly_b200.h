@@ -308,6 +308,12 @@ int grilly_encoder_set_weight(grilly_encoder* enc, const char* name, int layer, 
  * layout with the mask as attention key mask and pooling mask. */
 int grilly_encoder_forward(grilly_encoder* enc, const int* ids_host, const float* mask_host, int B, int S,
                            float* out_host);
+/* The encoder's own page-locked staging buffers, sized for at least B x S ids and B x hidden outputs: a caller that
+ * writes its ids there and passes these same pointers to grilly_encoder_forward has its copies to and from the device
+ * start from / end in page-locked memory without the staging memcpy on either side. The pointers stay valid until a
+ * forward or a call of this function with a larger B or S, or grilly_encoder_destroy. No counterpart in the reference
+ * (its staging is Vulkan-mapped memory inside every op, backend/fnn.py:1437-1489). */
+int grilly_encoder_io_buffers(grilly_encoder* enc, int B, int S, int** ids_pinned, float** out_pinned);
 /* same with device buffers and no copies: ids_dev int32 [B][S], lengths_host int32 [B] valid prefix lengths,
  * out_dev fp32 [B][hidden].  Asynchronous. */
 int grilly_encoder_forward_device(grilly_encoder* enc, const int* ids_dev, const int* lengths_host, int B, int S,

@@ -110,6 +110,21 @@ def test_chunking_padding_and_batch_invariance(small_model):
     assert O.rel_l2(enc.encode_ids(ids[:4]), O.encoder_forward(ids[:4], None, w.as_dict(), 12)) < TOL_TF32
 
 
+def test_page_locked_io_buffers_give_the_same_embeddings(small_model):
+    """Ids written into the encoder's own staging buffer and embeddings read from it: same bits as the pageable path."""
+    w, enc = small_model
+    rng = np.random.default_rng(33)
+    ids, lens, mask = make_batch(rng, 24, 48)
+    want = enc.encode_ids(ids, mask)
+    pin_ids, pin_out = enc.io_buffers(24, 48)
+    assert pin_ids.shape == (24, 48) and pin_ids.dtype == np.int32 and pin_out.shape == (24, 384)
+    pin_ids[...] = ids
+    got = enc.encode_ids(pin_ids, mask, out=pin_out)
+    assert got is pin_out and np.array_equal(got, want)
+    # a smaller batch afterwards reuses the same buffers; a plain call in between does not disturb them
+    assert np.array_equal(enc.encode_ids(ids[:5], mask[:5]), want[:5])
+
+
 def test_masks_with_holes_run_on_the_padded_layout(small_model):
     """A mask that is not a prefix of ones cannot be packed; the encoder then runs padded with the mask as key mask
     and pooling mask, like the reference (positions keep their own position embeddings)."""
