@@ -129,7 +129,6 @@ int grilly_init(int device, grilly_ctx** out) {
   ctx->tune.attn_hpc = env_int("GRILLY_ATTN_HPC", 0);
   ctx->tune.attn_general = getenv("GRILLY_ATTN_GENERAL") != nullptr ? 1 : 0;
   ctx->tune.fused_ln = env_int("GRILLY_FUSED_LN", 1);
-  ctx->tune.ln_deep = env_int("GRILLY_LN_DEEP", -1);
   *out = ctx;
   return GRILLY_OK;
 }
@@ -168,7 +167,6 @@ int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value) {
   else if (n == "attn_hpc") ctx->tune.attn_hpc = value;
   else if (n == "attn_general") ctx->tune.attn_general = value;
   else if (n == "fused_ln") ctx->tune.fused_ln = value;
-  else if (n == "ln_deep") ctx->tune.ln_deep = value;
   else return set_error(ctx, GRILLY_ERR_INVALID_ARG, "set_tuning: unknown knob '" + n + "'");
   return GRILLY_OK;
 }

@@ -272,13 +272,12 @@ static int launch_ln_pair_cfg(grilly_ctx* ctx, const void* x, const void* w, Gem
 
 template <bool kBf16>
 static int launch_ln_pair(grilly_ctx* ctx, const void* x, const void* w, GemmLnArgs& args) {
-  // 384 features: a long K loop is bound by the operand bytes in flight from L2 and takes a fourth stage for one
-  // staging buffer per epilogue warp; a short one is bound by the epilogue and takes three warps per TMEM lane quadrant
-  const bool deep = ctx->tune.ln_deep >= 0 ? ctx->tune.ln_deep != 0 : static_cast<long long>(args.K) * (kBf16 ? 2 : 4) >= 3072;
+  // 384 features: three epilogue warps per TMEM lane quadrant with one staging buffer each leave room for a fourth
+  // operand stage (measured best for K = 384 and K = 1536 alike)
   switch (args.N) {
     case 128: return launch_ln_pair_cfg<128, 2, 2, kBf16>(ctx, x, w, args);
     case 256: return launch_ln_pair_cfg<256, 2, 2, kBf16>(ctx, x, w, args);
-    case 384: return deep ? launch_ln_pair_cfg<384, 2, 1, kBf16>(ctx, x, w, args) : launch_ln_pair_cfg<384, 3, 2, kBf16>(ctx, x, w, args);
+    case 384: return launch_ln_pair_cfg<384, 3, 1, kBf16>(ctx, x, w, args);
     default: return launch_ln_pair_cfg<512, 2, 2, kBf16>(ctx, x, w, args);
   }
 }

@@ -71,7 +71,6 @@ struct grilly_ctx {
     int attn_hpc = 0;        // heads per work unit of the short attention kernel
     int attn_general = 0;    // 1: always the general attention kernel
     int fused_ln = 1;        // 0: linear + LayerNorm as two launches even where the one-kernel form exists
-    int ln_deep = -1;        // 0/1: never/always the four-stage variant of the one-kernel form at 384 features
   } tune;
   // RoPE tables, keyed by (S, D, base, scaling)
   struct RopeTable { int S, D; float base, scaling; float* cos_t; float* sin_t; };

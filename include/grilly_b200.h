@@ -67,8 +67,8 @@ int grilly_set_stream(grilly_ctx* ctx, void* cuda_stream);
 int grilly_sync(grilly_ctx* ctx);
 /* Tuning / debug knobs of the kernel selection, normally left alone. They are read from the environment once in
  * grilly_init (GRILLY_GEMM_GROUP, GRILLY_GEMM_BN, GRILLY_GEMM_PAIR, GRILLY_GEMM_SWAP, GRILLY_ATTN_HPC,
- * GRILLY_ATTN_GENERAL, GRILLY_FUSED_LN, GRILLY_LN_DEEP) and can be changed here per context: name in {gemm_group, gemm_bn, gemm_pair, gemm_swap,
- * attn_hpc, attn_general, fused_ln, ln_deep}; value 0 (gemm_pair, gemm_swap: -1) restores the default choice. The reference has no
+ * GRILLY_ATTN_GENERAL, GRILLY_FUSED_LN) and can be changed here per context: name in {gemm_group, gemm_bn, gemm_pair, gemm_swap,
+ * attn_hpc, attn_general, fused_ln}; value 0 (gemm_pair, gemm_swap: -1) restores the default choice. The reference has no
  * counterpart (its shaders have fixed workgroup sizes, backend/fnn.py:1465-1470). */
 int grilly_set_tuning(grilly_ctx* ctx, const char* name, int value);
 /* number of kernels this context has launched (monotonic) */
