@@ -21,10 +21,14 @@ def make_weights(rng):
                 wg=n(FFN, HID), wu=n(FFN, HID), wd=n(HID, FFN))
 
 
-def block_gpu(b, x, w):
+def block_gpu(b, x, w, fold_norm=False):
     B, S, _ = x.shape
-    h = b.fnn.rmsnorm(x, w["g1"], 1e-5)
-    qkv = b.fnn.fused_qkv_projection(h, w["wqkv"], None, HEADS, D).reshape(B, S, 3, HEADS, D)
+    if fold_norm:
+        # RMSNorm folded into the QKV product (one statistics kernel + one GEMM, the normalised rows never stored)
+        qkv = b.fnn.fused_layernorm_linear(x, w["g1"], None, w["wqkv"], None, 1e-5, mode="rms").reshape(B, S, 3, HEADS, D)
+    else:
+        h = b.fnn.rmsnorm(x, w["g1"], 1e-5)
+        qkv = b.fnn.fused_qkv_projection(h, w["wqkv"], None, HEADS, D).reshape(B, S, 3, HEADS, D)
     a = b.attention.flash_attention2_rope(np.ascontiguousarray(qkv[:, :, 0]), np.ascontiguousarray(qkv[:, :, 1]),
                                           np.ascontiguousarray(qkv[:, :, 2]), causal=True, rope_base=10000.0)
     x = x + b.fnn.linear(a.reshape(B, S, HID), w["wo"])
@@ -53,6 +57,9 @@ def test_decoder_block_parity_bf16(backend_bf16):
     assert O.rel_l2(y, ref) < TOL_BF16
     # the block's own contribution (without the residual stream that dominates the norm)
     assert O.rel_l2(y - x, ref - x) < 3 * TOL_BF16
+    # the same block with the first RMSNorm folded into the QKV projection
+    yf = block_gpu(backend_bf16, x, w, fold_norm=True)
+    assert O.rel_l2(yf, ref) < TOL_BF16 and O.rel_l2(yf - x, ref - x) < 3 * TOL_BF16
 
 
 def test_attention_at_the_configurations_own_shape(backend_bf16):
