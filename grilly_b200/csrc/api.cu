@@ -58,7 +58,8 @@ int get_tmap_2d(grilly_ctx* ctx, int dtype, const void* ptr, uint64_t inner, uin
   CUtensorMap m;
   CUresult r = g_encode(&m, dtype == TM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                         const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle == TM_SW128_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : swizzle == TM_SWNONE ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                        swizzle == TM_SW128_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : swizzle == TM_SWNONE ? CU_TENSOR_MAP_SWIZZLE_NONE
+                        : swizzle == TM_SW64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(ctx, GRILLY_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
   ctx->tmap_misses++;

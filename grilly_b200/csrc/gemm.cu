@@ -228,8 +228,10 @@ static int launch_ln_pair_cfg(grilly_ctx* ctx, const void* x, const void* w, Gem
   if (!args.residual) tr = ta;
   else if ((rc = get_tmap_2d(ctx, dtype, args.residual, args.N, args.M, static_cast<uint64_t>(args.ld_res) * ELT, 32, 32, &tr,
                              kBf16 ? TM_SWNONE : TM_SW128))) return rc;
-  if (args.out_bf16) to = ta;   // bf16 results leave through vector stores; the kernel does not touch this map
-  else if ((rc = get_tmap_2d(ctx, TM_F32, args.out, args.N, args.M, static_cast<uint64_t>(args.ld_out) * 4, 32, 32, &to))) return rc;
+  // output boxes of 32 rows x 32 columns: fp32 rows are 128 bytes (128-byte swizzle), bf16 rows 64 bytes (64-byte swizzle)
+  if (args.out_bf16) {
+    if ((rc = get_tmap_2d(ctx, TM_BF16, args.out, args.N, args.M, static_cast<uint64_t>(args.ld_out) * 2, 32, 32, &to, TM_SW64))) return rc;
+  } else if ((rc = get_tmap_2d(ctx, TM_F32, args.out, args.N, args.M, static_cast<uint64_t>(args.ld_out) * 4, 32, 32, &to))) return rc;
   args.num_tiles = (args.M + 255) / 256;
   args.num_k_blocks = (args.K + BK - 1) / BK;
   args.err = ctx->err_dev;

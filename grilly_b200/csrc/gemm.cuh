@@ -296,6 +296,25 @@ __device__ __forceinline__ void epilogue_swapped_fast(const GemmArgs& args, cons
     }
   }
 }
+// bf16 output without a residual: neighbouring lanes hold neighbouring features; they swap one value per pair of tokens,
+// so that the even lane has both features of token j and the odd lane both of token j + 1, and every lane stores 4 bytes
+// (a bf16 pair) instead of 2. `live` = the lanes of the warp that are here (whole feature pairs: N is even).
+template <int ACT>
+__device__ __forceinline__ void epilogue_swapped_fast_bf16(const GemmArgs& args, const uint32_t (&r)[32], int f, int t0, float b,
+                                                           unsigned live) {
+  const int odd = f & 1;
+  uint32_t* op = reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(t0 + odd) * args.ld_out + (f & ~1));
+  const long long pitch = args.ld_out >> 1;
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float v0 = __uint_as_float(r[j]) + b, v1 = __uint_as_float(r[j + 1]) + b;
+    if constexpr (ACT == ACT_GELU_TANH) { v0 = act_gelu_tanh(v0); v1 = act_gelu_tanh(v1); }
+    else if constexpr (ACT == ACT_SILU) { v0 = act_silu(v0); v1 = act_silu(v1); }
+    else if constexpr (ACT == ACT_RELU) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+    const float got = __shfl_xor_sync(live, odd ? v0 : v1, 1);
+    op[static_cast<long long>(j) * pitch] = odd ? pack_bf16x2(got, v1) : pack_bf16x2(v0, got);
+  }
+}
 
 // Swapped orientation (the 128-row operand is the weight matrix, so TMEM lanes are output features and the
 // accumulator columns are tokens): r[] holds 32 consecutive tokens t0.. for feature f. For a fixed register the
@@ -303,6 +322,19 @@ __device__ __forceinline__ void epilogue_swapped_fast(const GemmArgs& args, cons
 __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, const uint32_t (&r)[32], int f, int t0) {
   const bool f_ok = f < args.N;
   const bool full = t0 + 32 <= args.M;
+  // taken here, where the whole warp is still together (lanes beyond N leave below, lanes on the fast path right away):
+  // the lanes that reach the bf16 pair exchange at the end (whole feature pairs when N is even)
+  const unsigned live = __ballot_sync(0xffffffffu, f_ok);
+  const bool pairs_ok = !(args.N & 1) && !(args.ld_out & 1) && !(reinterpret_cast<uintptr_t>(args.out) & 3);   // warp-uniform
+  if (full && f_ok && args.out_bf16 && pairs_ok && !args.residual && !args.row_rstd && !args.swiglu_pairs) {
+    const float b = args.bias ? __ldg(args.bias + f) : 0.f;
+    switch (args.act) {
+      case ACT_GELU_TANH: return epilogue_swapped_fast_bf16<ACT_GELU_TANH>(args, r, f, t0, b, live);
+      case ACT_SILU: return epilogue_swapped_fast_bf16<ACT_SILU>(args, r, f, t0, b, live);
+      case ACT_RELU: return epilogue_swapped_fast_bf16<ACT_RELU>(args, r, f, t0, b, live);
+      default: return epilogue_swapped_fast_bf16<ACT_NONE>(args, r, f, t0, b, live);
+    }
+  }
   if (full && f_ok && !args.out_bf16 && !args.row_rstd && !args.swiglu_pairs && !(args.residual && args.residual_bf16)) {
     const float b = args.bias ? __ldg(args.bias + f) : 0.f;
     if (args.residual) {
@@ -387,10 +419,24 @@ __device__ __forceinline__ void epilogue_chunk_swapped(const GemmArgs& args, con
     for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
   }
   if (args.out_bf16) {
-    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
+    // Neighbouring lanes hold neighbouring features. They swap one value per pair of tokens, so that the even lane
+    // has both features of token j and the odd lane both of token j + 1, and every lane stores 4 bytes (a bf16 pair)
+    // instead of 2: half the store instructions for the same lines.
+    if (pairs_ok) {
+      const int odd = f & 1;
+      uint32_t* op = reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(t0 + odd) * args.ld_out + (f & ~1));
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (full || t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = __float2bfloat16(v[j]);
+      for (int j = 0; j < 32; j += 2) {
+        const float got = __shfl_xor_sync(live, odd ? v[j] : v[j + 1], 1);
+        const uint32_t pk = odd ? pack_bf16x2(got, v[j + 1]) : pack_bf16x2(v[j], got);
+        if (full || t0 + j + odd < args.M) op[static_cast<long long>(j) * (args.ld_out >> 1)] = pk;
+      }
+    } else {
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || t0 + j < args.M) op[static_cast<long long>(j) * args.ld_out] = __float2bfloat16(v[j]);
+    }
   } else {
     float* op = reinterpret_cast<float*>(args.out) + static_cast<long long>(t0) * args.ld_out + f;
     if (full) {

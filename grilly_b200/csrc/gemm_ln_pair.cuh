@@ -15,7 +15,7 @@
 //   merge:  the SUB partial results of a row meet in shared memory (an mbarrier per quadrant) and every thread
 //           merges them in the same order (M2 = sum M2_i + n_i sum (mean_i - mean)^2), so all agree bit for bit
 //   pass 2: (v - mean) * rstd * gamma + beta, optional tf32 rounding, staged in swizzled shared memory and stored with
-//           cp.async.bulk.tensor (fp32 output) or 8-byte vector stores (bf16 output).
+//           cp.async.bulk.tensor (fp32 boxes under the 128-byte swizzle, bf16 boxes under the 64-byte swizzle).
 // The residual comes in through TMA: every epilogue warp fetches [32 rows x 32 columns] boxes of its own rows and
 // columns into the buffers it later stages its output in, the first ones of a tile while the tile's MMAs still run.
 //
@@ -237,8 +237,6 @@ gemm_rowln_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       const int acc = it % ACCS;
       const uint32_t acc_phase = (it / ACCS) & 1u;
       const int row0 = tile * 256 + static_cast<int>(rank) * 128 + quad * 32;   // first row of this warp's 32
-      const int row = row0 + lane;
-      const bool row_ok = row < args.M;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) { fail(ERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * N + chunk0 * 32;
@@ -343,12 +341,9 @@ gemm_rowln_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         tmem_ld_wait();
         if (cc + 1 < CPW) tmem_ld_32x32(taddr_row + (cc + 1) * 32, nxt);
         uint8_t* stg = my_bufs + (cc % Cfg::BUFS) * Cfg::BUF_BYTES;
-        if (!bf16_out) {
-          // this buffer is free once the bulk store committed BUFS groups ago has READ it
-          if (lane == 0) tma_store_wait_read<Cfg::BUFS - 1>();
-          __syncwarp();
-        }
-        uint8_t* rowp = stg + lane * 128;
+        // this buffer is free once the bulk store committed BUFS groups ago has READ it
+        if (lane == 0) tma_store_wait_read<Cfg::BUFS - 1>();
+        __syncwarp();
         const int col = (chunk0 + cc) * 32;
         // four columns at a time, finished and put away, so that few values are live at once
 #pragma unroll
@@ -362,23 +357,20 @@ gemm_rowln_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           o.w = fmaf((__uint_as_float(cur[4 * q + 3]) - mean) * rstd, g4.w, b4.w);
           if (args.round_tf32) { o.x = round_to_tf32(o.x); o.y = round_to_tf32(o.y); o.z = round_to_tf32(o.z); o.w = round_to_tf32(o.w); }
           if (bf16_out) {
-            if (row_ok) {
-              uint2 pk;
-              pk.x = pack_bf16x2(o.x, o.y);
-              pk.y = pack_bf16x2(o.z, o.w);
-              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(row) * args.ld_out + col + 4 * q) = pk;
-            }
+            // 64-byte rows under the tensor map's 64-byte swizzle: 16-byte piece p of row r lives at piece p ^ ((r >> 1) & 3)
+            uint2 pk;
+            pk.x = pack_bf16x2(o.x, o.y);
+            pk.y = pack_bf16x2(o.z, o.w);
+            *reinterpret_cast<uint2*>(stg + lane * 64 + ((((q >> 1) ^ ((lane >> 1) & 3)) << 4) | ((q & 1) << 3))) = pk;
           } else {
-            *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) = o;    // the tensor map's 128-byte swizzle
+            *reinterpret_cast<float4*>(stg + lane * 128 + ((q ^ (lane & 7)) << 4)) = o;    // the tensor map's 128-byte swizzle
           }
         }
-        if (!bf16_out) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (row0 < args.M) tma_store_2d(&tmap_out, stg, col, row0);   // rows beyond M are clipped
-            tma_store_commit();    // an empty group when nothing was stored: the group count stays in step
-          }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < args.M) tma_store_2d(&tmap_out, stg, col, row0);   // rows beyond M are clipped
+          tma_store_commit();    // an empty group when nothing was stored: the group count stays in step
         }
       }
       // this warp has finished reading the accumulator
@@ -389,7 +381,7 @@ gemm_rowln_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       const int next = tile + num_pairs;
       if (has_res && next < args.num_tiles) {
         if (lane == 0) {
-          if (!bf16_out) tma_store_wait_read<0>();
+          tma_store_wait_read<0>();
 #pragma unroll
           for (int cc = 0; cc < (CPW < Cfg::BUFS ? CPW : Cfg::BUFS); ++cc) fetch_res(next, cc);
         }

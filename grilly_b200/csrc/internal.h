@@ -94,7 +94,7 @@ int prof_begin(grilly_ctx* ctx, int cls, double flops, double bytes);
 void prof_end(grilly_ctx* ctx, int idx);
 
 enum { TM_F32 = 0, TM_BF16 = 1 };
-enum { TM_SW128 = 0, TM_SW128_ATOM32 = 1, TM_SWNONE = 2 };  // 128-byte swizzle of 16-byte chunks, or of 32-byte chunks (tf32 MN-major), or none
+enum { TM_SW128 = 0, TM_SW128_ATOM32 = 1, TM_SWNONE = 2, TM_SW64 = 3 };  // 128-byte swizzle of 16-byte chunks, or of 32-byte chunks (tf32 MN-major), none, or the 64-byte swizzle
 // 2-D row-major tensor [outer][inner] with a row pitch, 128-byte swizzle, zero fill out of bounds.
 int get_tmap_2d(grilly_ctx* ctx, int dtype, const void* ptr, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
                 uint32_t box_inner, uint32_t box_outer, CUtensorMap* out, int swizzle = TM_SW128);

@@ -110,6 +110,7 @@ def main(argv=None):
     ap.add_argument("--k", "--dim-k", dest="k", type=int, default=384)
     ap.add_argument("--act", default="none", choices=["none", "gelu", "silu", "relu"])
     ap.add_argument("--residual", action="store_true")
+    ap.add_argument("--out-bf16", action="store_true", help="linear in bf16 mode: bf16 output (as between the layers of the bf16 encoder)")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--b", type=int, default=256)
     ap.add_argument("--s", type=int, default=128)
@@ -143,12 +144,14 @@ def main(argv=None):
             w = dev.upload((rng.standard_normal((a.n, a.k)) * 0.05).astype(np.float32), dt, round_tf32=True)
             b = dev.upload(np.zeros(a.n, np.float32))
             r = dev.upload(np.zeros((a.m, a.n), np.float32)) if a.residual else None
-            y = dev.empty((a.m, a.n))
+            out16 = bf16 and a.out_bf16
+            y = dev.empty((a.m, a.n), "bf16" if out16 else "f32")
             act = {"none": L.ACT_NONE, "gelu": L.ACT_GELU, "silu": L.ACT_SILU, "relu": L.ACT_RELU}[a.act]
+            flags = L.FLAG_OUT_BF16 if out16 else L.FLAG_ROUND_TF32
             fn = lambda: dev.check(lib.grilly_linear(ctx, x.ptr, w.ptr, b.ptr, r.ptr if r else None, y.ptr, a.m, a.n, a.k, act,  # noqa: E731
-                                                     prec, L.FLAG_ROUND_TF32))
+                                                     prec, flags))
             flops = 2.0 * a.m * a.n * a.k
-            nbytes = elt * (a.m * a.k + a.n * a.k) + 4.0 * a.m * a.n * (2 if a.residual else 1)
+            nbytes = elt * (a.m * a.k + a.n * a.k) + (2.0 if out16 else 4.0) * a.m * a.n + (4.0 * a.m * a.n if a.residual else 0.0)
         elif a.op == "linear_ln":
             x = dev.upload(rng.standard_normal((a.m, a.k)).astype(np.float32), dt, round_tf32=True)
             w = dev.upload((rng.standard_normal((a.n, a.k)) * 0.05).astype(np.float32), dt, round_tf32=True)
