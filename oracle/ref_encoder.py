@@ -9,7 +9,10 @@ What is the reference's and what is restated here:
     pointed at it and the same code drives that backend instead.
   * embedding sum + embedding LayerNorm, masked mean pooling and L2 normalisation are the few NumPy lines of
     ``encode`` (:620-705, :726-744, :1185-1201), which need torch modules only as weight containers; they are
-    restated below in float32, as the reference computes them.
+    restated below in float32, as the reference computes them (``encoder_forward``).
+  * ``encode_texts`` runs the reference's whole ``encode`` (:1109-1219) unmodified instead: the torch modules it reads
+    weights from are replaced by plain containers of tensors, and the HuggingFace tokenizer (not available offline) by
+    a whitespace tokenizer with the same call signature.
 """
 from __future__ import annotations
 
@@ -111,3 +114,56 @@ def encoder_forward(ids, mask, w, num_heads, backend=None, return_hidden=False):
         logging.disable(logging.NOTSET)
     out = np.asarray(pool_normalize(np.asarray(x), mask), dtype=np.float32)
     return (out, np.asarray(x)) if return_hidden else out
+
+
+class WhitespaceTokenizer:
+    """Stands in for the HuggingFace tokenizer ``encode`` calls (:550-556): ids from a checksum of each whitespace-
+    separated word, [CLS] = 1 in front, [SEP] = 2 behind, padding 0; returns NumPy arrays like ``return_tensors='np'``."""
+
+    def __init__(self, vocab: int):
+        self.vocab = int(vocab)
+
+    def __call__(self, texts, padding=True, truncation=True, max_length=128, return_tensors="np"):
+        import zlib
+
+        rows = []
+        for t in texts:
+            ids = [1] + [3 + zlib.crc32(wd.encode()) % (self.vocab - 3) for wd in t.split()][: max_length - 2] + [2]
+            rows.append(ids)
+        width = max(len(r) for r in rows)
+        input_ids = np.zeros((len(rows), width), dtype=np.int64)
+        mask = np.zeros((len(rows), width), dtype=np.int64)
+        for i, r in enumerate(rows):
+            input_ids[i, : len(r)] = r
+            mask[i, : len(r)] = 1
+        return {"input_ids": input_ids, "attention_mask": mask}
+
+
+def make_full_transformer(w, num_heads, backend=None, max_seq_length=128, embed_ln_eps=1e-12):
+    """A ``VulkanSentenceTransformer`` on which the reference's own ``encode`` runs: weights of ``EncoderWeights.as_dict()``
+    in the containers the method reads them from (``transformer_model.embeddings.*.weight``, ``self.layers``)."""
+    import torch
+
+    st = make_transformer(int(w["word"].shape[1]), num_heads, backend)
+    t = lambda a: types.SimpleNamespace(weight=torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)))  # noqa: E731
+    emb = types.SimpleNamespace(word_embeddings=t(w["word"]), position_embeddings=t(w["pos"]))
+    if w.get("type") is not None:
+        emb.token_type_embeddings = t(w["type"])
+    emb.LayerNorm = types.SimpleNamespace(weight=torch.from_numpy(np.asarray(w["emb_ln_g"], np.float32)),
+                                          bias=torch.from_numpy(np.asarray(w["emb_ln_b"], np.float32)), eps=embed_ln_eps)
+    st.transformer_model = types.SimpleNamespace(embeddings=emb)
+    st.tokenizer = WhitespaceTokenizer(int(w["word"].shape[0]))
+    st.max_seq_length = max_seq_length
+    st.layers = list(w["layers"])
+    st.final_norm_weight = None
+    return st
+
+
+def encode_texts(texts, w, num_heads, backend=None, batch_size=32):
+    """``VulkanSentenceTransformer.encode(texts)`` of the reference, unchanged (:1109-1219)."""
+    st = make_full_transformer(w, num_heads, backend)
+    logging.disable(logging.CRITICAL)
+    try:
+        return np.asarray(st.encode(list(texts), batch_size=batch_size))
+    finally:
+        logging.disable(logging.NOTSET)

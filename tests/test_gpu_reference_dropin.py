@@ -55,3 +55,31 @@ def test_reference_encoder_over_compute_matches_resident_encoder(backend):
     finally:
         enc.close()
     R.make_transformer(384, 12, backend=None)   # put the reference's stock Compute back
+
+
+def test_reference_encode_unchanged_over_compute(backend):
+    """The reference's whole ``encode`` (utils/vulkan_sentence_transformer.py:1109-1219: tokenize, embedding lookup,
+    position / type embeddings, embedding LayerNorm, the layers, masked mean pooling, normalisation), unmodified, with
+    ``grilly.Compute`` pointed at this library; against the same method on its CPU branches and against the resident
+    encoder on the same token ids. Texts are seeded pseudo-words."""
+    import grilly_b200
+
+    rng = np.random.default_rng(44)
+    w = grilly_b200.EncoderWeights.random(rng, num_layers=2, vocab=5000, max_pos=64)
+    words = ["".join(chr(97 + int(c)) for c in rng.integers(0, 26, size=int(n))) for n in rng.integers(2, 9, size=300)]
+    texts = [" ".join(words[int(i)] for i in rng.integers(0, 300, size=int(n))) for n in rng.integers(1, 40, size=21)]
+    before = backend.device.launch_count()
+    got = R.encode_texts(texts, w.as_dict(), 12, backend=backend, batch_size=8)
+    assert backend.device.launch_count() - before >= 3 * (2 * 13 + 3), "the reference's encode fell back to its CPU branches"
+    want = R.encode_texts(texts, w.as_dict(), 12, backend=None, batch_size=8)
+    assert got.shape == want.shape == (21, 384) and got.dtype == np.float32
+    assert O.rel_l2(got, want) < TOL_TF32
+    # the resident encoder on what the tokenizer produced (whole list at once: padding to the longest text)
+    enc = grilly_b200.SentenceEncoder(w, num_heads=12, device=backend.device)
+    try:
+        tok = R.WhitespaceTokenizer(5000)(texts, max_length=128)
+        res = enc.encode_ids(tok["input_ids"], tok["attention_mask"].astype(np.float32))
+    finally:
+        enc.close()
+    assert O.rel_l2(res, want) < TOL_TF32
+    R.make_transformer(384, 12, backend=None)   # put the reference's stock Compute back
