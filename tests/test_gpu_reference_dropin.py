@@ -83,3 +83,30 @@ def test_reference_encode_unchanged_over_compute(backend):
         enc.close()
     assert O.rel_l2(res, want) < TOL_TF32
     R.make_transformer(384, 12, backend=None)   # put the reference's stock Compute back
+
+
+def test_modernbert_layer_branch_unchanged_over_compute(backend):
+    """The pre-norm branch of the reference's ``_forward_layer`` (utils/vulkan_sentence_transformer.py:799-970),
+    unmodified, over this backend: its linears, LayerNorm and GELU run through ``functional.*`` on the CUDA library, its
+    RoPE through ``backend.attention.apply_rope`` (the branch asks for ``_rope_cpu`` first, which this backend does not
+    have); the attention of that branch is the reference's own ``_attention_cpu`` by its author's choice. Against the
+    golden output of the same branch on the reference's NumPy paths."""
+    import types
+
+    from pathlib import Path
+
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "extras_golden.npz")
+    m = cases.modernbert_layer()
+    st = R.make_transformer(384, m["num_heads"], backend=backend, model_type="modernbert")
+    st.config = types.SimpleNamespace(hidden_size=384, num_attention_heads=m["num_heads"], local_rope_theta=10000.0, rope_scaling=None)
+    before = backend.device.launch_count()
+    import logging
+    logging.disable(logging.CRITICAL)
+    try:
+        y = R.forward_layers(st, m["x"], [m["lw"]], m["mask"])
+    finally:
+        logging.disable(logging.NOTSET)
+    # 7 linears, 1 layernorm, 1 gelu, 2 rope (+ uploads' rounding kernels)
+    assert backend.device.launch_count() - before >= 11
+    assert O.rel_l2(y, gold["mb_y"]) < TOL_TF32
+    R.make_transformer(384, 12, backend=None)   # put the reference's stock Compute back
