@@ -854,6 +854,25 @@ def reference_pool_stats(native: dict) -> dict:
     return stats
 
 
+class _CoreView:
+    """What callers read from ``backend.core`` (backend/core.py:14-439) without touching Vulkan: the table of available
+    shaders, by the reference's shader names (``nn.Linear.forward`` takes its GEMM path when 'gemm_mnk' is listed,
+    nn/modules.py:146-152), and the device name. There are no Vulkan handles behind it."""
+
+    SHADERS = ("fnn-linear", "fused-linear-gelu", "fused-linear-relu", "fused-linear-silu", "fused-linear-gcu",
+               "fused-linear-roswish", "fused-qkv-projection", "fused-layernorm-linear", "fused-swiglu", "fused-geglu",
+               "gemm_mnk", "fnn-layernorm", "snn-rmsnorm", "fnn-residual", "activation-gelu", "activation-silu",
+               "activation-relu", "activation-softmax", "activation-swiglu", "activation-gcu", "activation-roswish",
+               "flash-attention2", "flash-attention2-rope", "rope", "attention-scores", "attention-mask",
+               "attention-output", "attention-output-gpt", "attention-output-t5", "attention-backward",
+               "embedding-lookup", "embedding-pool", "faiss-distance", "faiss-topk", "fnn-linear-backward",
+               "fnn-layernorm-backward", "activation-softmax-backward", "adam-update")
+
+    def __init__(self, device):
+        self.shaders = {name: b"" for name in self.SHADERS}
+        self.device_name = "NVIDIA B200 (sm_100a), device %d" % device.index
+
+
 class Compute:
     """Drop-in for ``grilly.Compute()`` (``VulkanCompute``, backend/compute.py:23-128) on one B200.
 
@@ -875,6 +894,7 @@ class Compute:
         self.pooling = Pooling(self)
         self.learning = Learning(self)
         self.faiss = Faiss(self)
+        self.core = _CoreView(self.device)
         self._alias()
 
     def _alias(self):

@@ -167,3 +167,11 @@ def encode_texts(texts, w, num_heads, backend=None, batch_size=32):
         return np.asarray(st.encode(list(texts), batch_size=batch_size))
     finally:
         logging.disable(logging.NOTSET)
+
+
+def reference_nn():
+    """The reference's ``grilly.nn.modules`` (nn/modules.py), for tests that drive its ``Linear`` / ``LayerNorm`` modules."""
+    _load()
+    import grilly.nn.modules as M
+
+    return M

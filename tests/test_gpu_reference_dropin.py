@@ -110,3 +110,26 @@ def test_modernbert_layer_branch_unchanged_over_compute(backend):
     assert backend.device.launch_count() - before >= 11
     assert O.rel_l2(y, gold["mb_y"]) < TOL_TF32
     R.make_transformer(384, 12, backend=None)   # put the reference's stock Compute back
+
+
+def test_reference_nn_modules_over_compute(backend):
+    """``grilly.nn.Linear`` and ``grilly.nn.LayerNorm`` of the reference (nn/modules.py:123-181, 340-367), unmodified,
+    with this backend behind them: ``Linear.forward`` reads ``backend.core.shaders`` and takes its ``fnn.gemm`` path for
+    large products (on a transposed VIEW of the weight) and ``fnn.linear`` for small ones."""
+    M = R.reference_nn()
+    R.make_transformer(384, 12, backend=backend)     # points grilly.Compute at this backend (the modules build one)
+    rng = np.random.default_rng(46)
+    lin = M.Linear(96, 160)
+    assert lin._get_backend() is backend
+    W, b = M._get_param_array(lin.weight), M._get_param_array(lin.bias)
+    b[...] = rng.standard_normal(160).astype(np.float32)
+    for shape in ((3, 40, 96), (4, 96)):          # 120 x 160 >= 4096 -> gemm path; 4 x 160 -> linear path
+        x = rng.standard_normal(shape).astype(np.float32)
+        before = backend.device.launch_count()
+        y = lin.forward(x)
+        assert backend.device.launch_count() > before, "nn.Linear fell back to NumPy"
+        assert y.shape == shape[:-1] + (160,) and O.rel_l2(y, O.linear(x, W, b)) < TOL_TF32
+    ln = M.LayerNorm(96)
+    x = (rng.standard_normal((5, 7, 96)) * 2 + 1).astype(np.float32)
+    assert O.rel_l2(ln.forward(x), O.layernorm(x, np.ones(96, np.float32), np.zeros(96, np.float32), 1e-5)) < 2e-6
+    R.make_transformer(384, 12, backend=None)   # put the reference's stock Compute back
