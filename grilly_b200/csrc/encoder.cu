@@ -346,7 +346,9 @@ int grilly_encoder_create(grilly_ctx* ctx, const grilly_encoder_config* cfg, gri
     return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: sizes must be positive");
   if (cfg->hidden % cfg->num_heads) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "encoder: hidden must be divisible by num_heads");
   const int D = cfg->hidden / cfg->num_heads;
-  if (D != 32 && D != 64) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: head_dim must be 32 or 64");
+  // head dims the attention kernels are instantiated for (bf16 head_dim 32 only while every sentence fits one key tile)
+  const bool d_ok = cfg->precision == GRILLY_PREC_BF16 ? (D == 32 || D == 64 || D == 128) : (D == 32 || D == 64 || D == 96 || D == 128);
+  if (!d_ok) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: head_dim must be 32, 64, 96 or 128 (tf32) / 32, 64 or 128 (bf16)");
   if (cfg->precision == GRILLY_PREC_BF16 && (cfg->hidden % 8 || cfg->ffn % 8))
     return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: bf16 mode needs hidden and ffn to be multiples of 8");
   if (cfg->hidden % 4 || cfg->ffn % 4 || cfg->hidden > 1024) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "encoder: hidden and ffn must be multiples of 4, hidden at most 1024");

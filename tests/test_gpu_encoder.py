@@ -125,6 +125,21 @@ def test_page_locked_io_buffers_give_the_same_embeddings(small_model):
     assert np.array_equal(enc.encode_ids(ids[:5], mask[:5]), want[:5])
 
 
+@pytest.mark.parametrize("heads", [4, 3])
+def test_encoder_with_wide_heads(heads):
+    """hidden 384 split into 4 heads of 96 or 3 heads of 128: the long-sequence attention kernel's tf32 instances."""
+    import grilly_b200
+
+    rng = np.random.default_rng(50 + heads)
+    w = grilly_b200.EncoderWeights.random(rng, num_layers=2, hidden=384, ffn=768, vocab=3000, max_pos=256)
+    enc = grilly_b200.SentenceEncoder(w, num_heads=heads)
+    try:
+        ids, lens, mask = make_batch(rng, 9, 150)
+        assert O.rel_l2(enc.encode_ids(ids, mask), O.encoder_forward(ids, mask, w.as_dict(), heads)) < TOL_TF32
+    finally:
+        enc.close()
+
+
 def test_masks_with_holes_run_on_the_padded_layout(small_model):
     """A mask that is not a prefix of ones cannot be packed; the encoder then runs padded with the mask as key mask
     and pooling mask, like the reference (positions keep their own position embeddings)."""
