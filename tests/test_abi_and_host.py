@@ -230,3 +230,20 @@ def test_invalidate_drops_folded_layernorm_weights():
     b.invalidate(g)              # shared gamma: the remaining fold goes too
     assert not b._folds
     assert Compute.MAX_FOLDS >= 8
+
+
+def test_clock_sampler_without_nvidia_smi(monkeypatch):
+    """The clock sampler only queries nvidia-smi; where the tool is absent it reports that instead of failing, and a
+    summary over fabricated rows takes the median SM clock of the samples under load and the active throttle reasons."""
+    from grilly_b200.clocks import ClockSampler
+
+    monkeypatch.setenv("PATH", "/nonexistent")
+    got = ClockSampler(0).start(wait_s=0.2).stop()
+    assert got["samples"] == 0 and got["sm_mhz"] is None
+    s = ClockSampler(0)
+    s.proc = type("P", (), {"terminate": lambda self: None, "wait": lambda self, timeout=None: 0, "kill": lambda self: None})()
+    s.rows = [["0", "1965", "1965", "400.0", "Not Active", "Not Active", "Not Active", "Active"],
+              ["0", "1800", "1965", "500.0", "Not Active", "Not Active", "Not Active", "Active"],
+              ["0", "210", "1965", "90.0", "Not Active", "Not Active", "Not Active", "Not Active"]]
+    out = s.stop()
+    assert out["samples"] == 3 and out["sm_mhz"] == 1882.5 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"]
