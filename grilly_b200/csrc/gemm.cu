@@ -97,7 +97,7 @@ static int launch_pair(grilly_ctx* ctx, const void* x, const void* w, GemmArgs& 
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.blockDim = dim3(GEMM_PAIR_THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = ctx->stream;
   cfg.attrs = attr;

@@ -16,6 +16,13 @@
 
 namespace gb {
 
+// Eight epilogue warps (two per TMEM lane quadrant), not the sixteen of the single-CTA kernel: on the K = 384 launches of the
+// encoder the MMAs and the epilogue arithmetic slow each other down, and with fewer warps busy beside the issuing
+// thread the same launches run 5-7 % faster (QKV 134 -> 128 us, FFN1 + GELU 169 -> 157 us; 8192^3 unchanged; four
+// warps are slower again).
+constexpr int GEMM_PAIR_EPI_WARPS = 8;
+constexpr int GEMM_PAIR_THREADS = 64 + 32 * GEMM_PAIR_EPI_WARPS;   // warp 0 TMA, warp 1 MMA, the rest epilogue
+
 struct GemmPairCfg {
   static constexpr int HALF_BYTES = 128 * 128;                 // 128 rows x 128 B (one operand half)
   static constexpr int STAGE_BYTES = 2 * HALF_BYTES;           // per CTA: weight half + token half
@@ -31,7 +38,7 @@ struct GemmPairCfg {
 // an MN-major N operand in 128-byte-wide column chunks; accumulator lanes are rows of C, the plain epilogue writes
 // C[row][col]). num_m_tiles / num_n_tiles count 256-blocks of the MMA's M / N operand in both cases.
 template <bool kBf16, bool kBMn>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_PAIR_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                          const GemmArgs args) {
   using Cfg = GemmPairCfg;
@@ -67,7 +74,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 2 * GEMM_EPI_WARPS);           // used in the leader only
+      mbar_init(&tmem_empty[a], 2 * GEMM_PAIR_EPI_WARPS);      // used in the leader only
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -167,7 +174,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 features)
     constexpr int NCHUNK = Cfg::TILE / 32;
-    constexpr int G = GEMM_EPI_WARPS / 4;
+    constexpr int G = GEMM_PAIR_EPI_WARPS / 4;
     constexpr int MAXIT = (NCHUNK + G - 1) / G;
     const int quad = warp & 3;
     const int group = (warp - 2) >> 2;
