@@ -76,3 +76,53 @@ def test_attention_random_shapes(backend, backend_bf16, seed):
         if D == 64 or (S <= 128 and not causal):
             got16 = backend_bf16.attention.flash_attention2(q, k, v, mask=mask, causal=causal)
             assert O.rel_l2(got16, ref) < TOL_BF16, (B, S, H, D, causal, mask is not None)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_encoder_random_batches(seed):
+    """The resident encoder on random models and batches: 1-3 layers, head dims 32 / 64 / 96 / 128, batches with empty
+    and one-token sentences, with and without chunking; against the oracle."""
+    import grilly_b200
+
+    rng = np.random.default_rng(4000 + seed)
+    heads = _pick(rng, [12, 6, 4, 3])
+    layers = int(rng.integers(1, 4))
+    ffn = _pick(rng, [384, 768, 1536])
+    B, S = int(rng.integers(1, 40)), _pick(rng, [1, 5, 32, 64, 100, 128, 150])
+    w = grilly_b200.EncoderWeights.random(rng, num_layers=layers, hidden=384, ffn=ffn, vocab=2000, max_pos=max(S, 8))
+    ids = rng.integers(0, 2000, size=(B, S))
+    lens = rng.integers(0, S + 1, size=B)
+    lens[int(rng.integers(0, B))] = S
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.float32)
+    ref = O.encoder_forward(ids, mask, w.as_dict(), heads)
+    for chunk in (0, 97):
+        enc = grilly_b200.SentenceEncoder(w, num_heads=heads, chunk_tokens=chunk)
+        try:
+            got = enc.encode_ids(ids, mask)
+        finally:
+            enc.close()
+        assert got.shape == (B, 384) and np.isfinite(got).all()
+        assert O.rel_l2(got, ref) < TOL_TF32, (heads, layers, ffn, B, S, chunk)
+        assert np.array_equal(got[lens == 0], np.zeros((int((lens == 0).sum()), 384), np.float32))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_search_random_sizes(backend, seed):
+    """faiss.search (distances + top-k without the matrix) against top-k of the oracle's distances."""
+    rng = np.random.default_rng(5000 + seed)
+    nq, ndb, dim = int(rng.integers(1, 70)), _pick(rng, [1, 10, 257, 1000, 5000, 70001]), _pick(rng, [1, 3, 32, 100, 384])
+    k = min(ndb, _pick(rng, [1, 5, 10, 100]))
+    kind = ("l2", "cosine", "dot")[int(rng.integers(0, 3))]
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    d = rng.standard_normal((ndb, dim)).astype(np.float32)
+    idx, val = backend.faiss.search(q, d, k, kind)
+    ridx, rval = O.faiss_topk(O.faiss_distances(q, d, kind), k)
+    assert idx.shape == (nq, k) and val.shape == (nq, k)
+    np.testing.assert_allclose(val, rval, rtol=2e-4, atol=3e-5)
+    # indices agree wherever the oracle's neighbouring distances are further apart than fp32 noise
+    dist = O.faiss_distances(q, d, kind)
+    for r in range(nq):
+        srt = np.sort(dist[r])[: k + 1]
+        gaps = np.diff(srt) if srt.size > 1 else np.array([1.0])
+        if gaps.size and gaps.min() > 1e-4 * max(1.0, float(np.abs(srt).max())):
+            assert np.array_equal(idx[r], ridx[r]), (nq, ndb, dim, k, kind, r)
