@@ -126,3 +126,30 @@ def test_search_random_sizes(backend, seed):
         gaps = np.diff(srt) if srt.size > 1 else np.array([1.0])
         if gaps.size and gaps.min() > 1e-4 * max(1.0, float(np.abs(srt).max())):
             assert np.array_equal(idx[r], ridx[r]), (nq, ndb, dim, k, kind, r)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_encoder_bf16_and_modernbert_random_batches(seed):
+    """The bf16 mode of the post-LN encoder and the pre-norm (ModernBERT) architecture on random batches."""
+    import grilly_b200
+
+    rng = np.random.default_rng(6000 + seed)
+    heads = _pick(rng, [12, 6])
+    B, S = int(rng.integers(1, 30)), _pick(rng, [7, 48, 100, 128])
+    ids = rng.integers(0, 2000, size=(B, S))
+    lens = rng.integers(1, S + 1, size=B)
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.float32)
+    w = grilly_b200.EncoderWeights.random(rng, num_layers=2, hidden=384, ffn=768, vocab=2000, max_pos=128)
+    enc = grilly_b200.SentenceEncoder(w, num_heads=heads, precision="bf16")
+    try:
+        got = enc.encode_ids(ids, mask)
+    finally:
+        enc.close()
+    assert O.rel_l2(got, O.encoder_forward(ids, mask, w.as_dict(), heads)) < TOL_BF16, (heads, B, S)
+    wm = grilly_b200.EncoderWeights.random_modernbert(rng, num_layers=2, hidden=384, ffn=576, vocab=2000)
+    encm = grilly_b200.SentenceEncoder(wm, num_heads=heads, arch="modernbert", rope_base=10000.0)
+    try:
+        gotm = encm.encode_ids(ids, mask)
+    finally:
+        encm.close()
+    assert O.rel_l2(gotm, O.modernbert_forward(ids, mask, wm.as_dict(), heads)) < TOL_TF32, (heads, B, S)
