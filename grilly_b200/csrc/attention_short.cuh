@@ -34,7 +34,14 @@ struct AttnShortCfg {
   static constexpr int THREADS = NSLOT * SLOT_THREADS;
   static constexpr int SLOT_SMEM = 3 * TILE_BYTES;                // Q, K, V of one head (or head pair)
   static constexpr int CTRL_BYTES = 96;                           // per slot: 6 barriers, unit, key-mask words
-  static constexpr int SMEM_BYTES = NSLOT * SLOT_SMEM + 1024 + NSLOT * CTRL_BYTES + 64;
+  // fp32 rows of 32 features (128 bytes) leave the SM through a staging tile per softmax warp (32 rows x 128 B), so
+  // that a store instruction writes four whole rows instead of a 16-byte piece of 32 rows; the other shapes have no
+  // shared memory left for it and store from registers
+  static constexpr bool STAGE_OUT = !kBf16 && D == 32;
+  static constexpr int STAGE_BYTES = STAGE_OUT ? ATTN_TILE * 128 : 0;   // per slot
+  static constexpr int STAGE_OFF = NSLOT * SLOT_SMEM;
+  static constexpr int CTRL_OFF = STAGE_OFF + NSLOT * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = CTRL_OFF + 1024 + NSLOT * CTRL_BYTES + 64;
   static constexpr int TMEM_COLS = 512;
 };
 
@@ -71,7 +78,7 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
   const int warp = t >> 5;                                  // 0..3 softmax (one query row per thread), 4 issuer
   const int lane = t & 31;
   uint8_t* tiles = smem + slot * Cfg::SLOT_SMEM;            // Q | K | V
-  uint8_t* ctrl = smem + Cfg::NSLOT * Cfg::SLOT_SMEM + slot * Cfg::CTRL_BYTES;
+  uint8_t* ctrl = smem + Cfg::CTRL_OFF + slot * Cfg::CTRL_BYTES;
   uint64_t* bar_qk = reinterpret_cast<uint64_t*>(ctrl);     // Q and K of a head (pair) landed
   uint64_t* bar_v = bar_qk + 1;                             // V landed
   uint64_t* bar_s = bar_qk + 2;                             // S complete
@@ -80,7 +87,7 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
   uint64_t* bar_or = bar_qk + 5;                            // O read out of TMEM (only when it shares columns with the next S)
   volatile int* slot_unit = reinterpret_cast<volatile int*>(ctrl + 48);
   uint32_t* s_keep = reinterpret_cast<uint32_t*>(ctrl + 64);   // [4] key-mask bit words of the slot's sequence
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + Cfg::NSLOT * (Cfg::SLOT_SMEM + Cfg::CTRL_BYTES));
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + Cfg::CTRL_OFF + Cfg::NSLOT * Cfg::CTRL_BYTES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   if (t == 0) {
@@ -112,98 +119,138 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
   // Barrier phases run on across units: both roles count the heads (and loaded head groups) they have been through.
   uint32_t heads_done = 0, groups_done = 0;
 
+  // The issuing thread knows the slot's units one ahead: while a unit runs it takes the following one from the counter,
+  // looks up its rows and, during the unit's last head, sends for the first Q, K and V of the following unit, so that a
+  // unit does not start with the round trips of an atomic, two loads and three copies in a row.
+  int nx_unit = -1, nx_row0 = 0, nx_L = 0;    // issuing thread only: the unit this slot runs next
+  bool nx_loaded = false;                     // ... and whether its first Q, K, V are on their way already
+  auto unit_rows = [&](int u, int& r0, int& len) {
+    const int bb = u / head_groups;
+    if (args.cu_seqlens) {
+      r0 = __ldg(args.cu_seqlens + bb);
+      len = __ldg(args.cu_seqlens + bb + 1) - r0;
+    } else {
+      r0 = bb * args.S;
+      len = args.S;
+    }
+  };
+  if (t == Cfg::SLOT_THREADS - 32) {
+    nx_unit = atomicAdd(work_counter, 1);
+    if (nx_unit >= total_units) nx_unit = -1;
+    if (nx_unit >= 0) unit_rows(nx_unit, nx_row0, nx_L);
+  }
+
   while (true) {
-    // ---- next unit: fetched by the issuing thread, published to the slot through shared memory
+    // ---- this unit: published by the issuing thread to the slot through shared memory
     if (t == Cfg::SLOT_THREADS - 32) {
-      int u = -1;
-      if (!*abort_flag) {
-        u = atomicAdd(work_counter, 1);
-        if (u >= total_units) u = -1;
-      }
-      *slot_unit = u;
+      if (*abort_flag) nx_unit = -1;
+      slot_unit[0] = nx_unit;
+      slot_unit[1] = nx_row0;
+      slot_unit[2] = nx_L;
     }
     named_barrier(1 + slot, Cfg::SLOT_THREADS);
-    const int unit = *slot_unit;
+    const int unit = slot_unit[0];
     if (unit < 0) break;
+    const int row0 = slot_unit[1], L = slot_unit[2];
     const int b = unit / head_groups;
     const int h_begin = (unit % head_groups) * heads_per_unit;
     const int h_end = min(args.H, h_begin + heads_per_unit);
-    int row0, L;
-    if (args.cu_seqlens) {
-      row0 = __ldg(args.cu_seqlens + b);
-      L = __ldg(args.cu_seqlens + b + 1) - row0;
-    } else {
-      row0 = b * args.S;
-      L = args.S;
-    }
     const bool has_work = L > 0 && h_begin < h_end;          // uniform over the slot
     const int n_s = (L + 31) & ~31;                          // score columns computed (N = 16 mod 32 runs the MMA much slower)
     const int nchunks = (L + 31) >> 5;                       // 32-key chunks with a valid key
     const int ksteps = (L + UMMA_K - 1) / UMMA_K;            // k-steps of P V that cover valid keys
 
     if (warp == 4) {
-      if (lane == 0 && has_work) {
+      if (lane == 0) {
         // -------------------------------------------------------- TMA + MMA issuer
-        const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
-        // Q and K of the next head (pair) may be fetched as soon as S is complete, V once P V is complete
-        // boxes of n_s rows (32, 64, 96 or 128): rows beyond them keep whatever the slot's previous unit left, which
-        // no MMA result that is stored depends on (S columns and P V k-steps stop at n_s, query rows >= L are not stored)
-        const int bi = (n_s >> 5) - 1;
-        const uint32_t box_bytes = static_cast<uint32_t>(n_s) * 128u * NCH;   // one of Q, K, V
-        const CUtensorMap* mq = &maps.q[bi];
-        const CUtensorMap* mk = &maps.k[bi];
-        const CUtensorMap* mv = &maps.v[bi];
-        auto load_qk = [&](int h) {
-          mbar_expect_tx(bar_qk, 2 * box_bytes);
-#pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            tma_load_2d(tiles + c * ATTN_CHUNK_BYTES, mq, bar_qk, h * D + c * CHE, row0);
-            tma_load_2d(tiles + TILE_BYTES + c * ATTN_CHUNK_BYTES, mk, bar_qk, h * D + c * CHE, row0);
-          }
+        const bool loaded = nx_loaded;          // this unit's first Q, K, V were sent for during the previous unit
+        int taken = -1;                         // the following unit: the atomic's round trip hides behind this unit's copies
+        if (!*abort_flag) taken = atomicAdd(work_counter, 1);
+        bool nx_known = false;
+        nx_unit = -1;
+        nx_loaded = false;
+        auto know_next = [&]() {
+          if (nx_known) return;
+          nx_known = true;
+          nx_unit = (taken >= 0 && taken < total_units) ? taken : -1;
+          if (nx_unit >= 0) unit_rows(nx_unit, nx_row0, nx_L);
         };
-        auto load_v = [&](int h) {
-          mbar_expect_tx(bar_v, box_bytes);
+        if (has_work) {
+          const uint32_t idesc_s = (IDESC_S & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_s >> 3) << 17);
+          // Q and K of the next head (pair) may be fetched as soon as S is complete, V once P V is complete
+          // boxes of n_s rows (32, 64, 96 or 128): rows beyond them keep whatever the slot's previous unit left, which
+          // no MMA result that is stored depends on (S columns and P V k-steps stop at n_s, query rows >= L are not stored)
+          auto load_qk = [&](int h, int r0, int ns) {
+            const int bi = (ns >> 5) - 1;
+            mbar_expect_tx(bar_qk, 2u * static_cast<uint32_t>(ns) * 128u * NCH);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c)
-            tma_load_2d(tiles + 2 * TILE_BYTES + c * ATTN_CHUNK_BYTES, mv, bar_v, h * D + c * CHE, row0);
-        };
-        load_qk(h_begin);
-        load_v(h_begin);
-        for (int h = h_begin; h < h_end; ++h) {
-          const uint32_t ph = heads_done & 1u;
-          const int u = (h - h_begin) % HPR;                 // position of this head inside its loaded group
-          const bool group_ends = u == HPR - 1 || h + 1 == h_end;
-          if (u == 0 && !mbar_wait(bar_qk, groups_done & 1u, abort_flag)) { ATTN_FAIL(); break; }
-          if constexpr (Cfg::SHARE_O) {
-            // these scores overwrite the columns that hold O of the slot's previous head: wait until it has been read
-            if (heads_done > 0 && !mbar_wait(bar_or, (heads_done - 1) & 1u, abort_flag)) { ATTN_FAIL(); break; }
-          }
-          tc_fence_after();
-          const uint32_t sQ = smem_u32(tiles) + u * Cfg::ROW_BYTES, sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
+            for (int c = 0; c < NCH; ++c) {
+              tma_load_2d(tiles + c * ATTN_CHUNK_BYTES, &maps.q[bi], bar_qk, h * D + c * CHE, r0);
+              tma_load_2d(tiles + TILE_BYTES + c * ATTN_CHUNK_BYTES, &maps.k[bi], bar_qk, h * D + c * CHE, r0);
+            }
+          };
+          auto load_v = [&](int h, int r0, int ns) {
+            const int bi = (ns >> 5) - 1;
+            mbar_expect_tx(bar_v, static_cast<uint32_t>(ns) * 128u * NCH);
 #pragma unroll
-          for (int ks = 0; ks < D / UMMA_K; ++ks) {
-            const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
-            umma_ss<kBf16>(tmem_s, make_smem_desc_sw128(sQ + chunk * ATTN_CHUNK_BYTES + off, 16, 1024),
-                           make_smem_desc_sw128(sK + chunk * ATTN_CHUNK_BYTES + off, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
+            for (int c = 0; c < NCH; ++c)
+              tma_load_2d(tiles + 2 * TILE_BYTES + c * ATTN_CHUNK_BYTES, &maps.v[bi], bar_v, h * D + c * CHE, r0);
+          };
+          if (!loaded) {
+            load_qk(h_begin, row0, n_s);
+            load_v(h_begin, row0, n_s);
           }
-          umma_commit(bar_s);
-          if (group_ends && h + 1 < h_end) {
-            // S is the last reader of Q and K: fetch the next head's while this head is in its softmax
-            if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
-            load_qk(h + 1);
+          for (int h = h_begin; h < h_end; ++h) {
+            const uint32_t ph = heads_done & 1u;
+            const int u = (h - h_begin) % HPR;                 // position of this head inside its loaded group
+            const bool last = h + 1 == h_end;
+            const bool group_ends = u == HPR - 1 || last;
+            if (u == 0 && !mbar_wait(bar_qk, groups_done & 1u, abort_flag)) { ATTN_FAIL(); break; }
+            if constexpr (Cfg::SHARE_O) {
+              // these scores overwrite the columns that hold O of the slot's previous head: wait until it has been read
+              if (heads_done > 0 && !mbar_wait(bar_or, (heads_done - 1) & 1u, abort_flag)) { ATTN_FAIL(); break; }
+            }
+            tc_fence_after();
+            const uint32_t sQ = smem_u32(tiles) + u * Cfg::ROW_BYTES, sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < D / UMMA_K; ++ks) {
+              const int chunk = (ks * 32) / 128, off = (ks * 32) % 128;
+              umma_ss<kBf16>(tmem_s, make_smem_desc_sw128(sQ + chunk * ATTN_CHUNK_BYTES + off, 16, 1024),
+                             make_smem_desc_sw128(sK + chunk * ATTN_CHUNK_BYTES + off, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
+            }
+            umma_commit(bar_s);
+            if (h == h_begin) know_next();   // two loads that are back long before the unit's last head asks for them
+            // the following unit's first head group, if it has one: fetched under this unit's last head
+            const int nx_h = (nx_unit % head_groups) * heads_per_unit;
+            const int nx_ns = (nx_L + 31) & ~31;
+            const bool fetch_next = last && nx_unit >= 0 && nx_L > 0 && nx_h < args.H;
+            if (group_ends && !last) {
+              // S is the last reader of Q and K: fetch the next head's while this head is in its softmax
+              if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
+              load_qk(h + 1, row0, n_s);
+            } else if (fetch_next) {
+              if (!mbar_wait(bar_s, ph, abort_flag)) { ATTN_FAIL(); break; }
+              load_qk(nx_h, nx_row0, nx_ns);
+            }
+            if (!mbar_wait(bar_p, ph, abort_flag)) { ATTN_FAIL(); break; }
+            if (u == 0 && !mbar_wait(bar_v, groups_done & 1u, abort_flag)) { ATTN_FAIL(); break; }
+            tc_fence_after();
+            for (int ks = 0; ks < ksteps; ++ks)
+              umma_ts<kBf16>(tmem_o, tmem_s + ks * 8, make_smem_desc_mn<kBf16>(sV + ks * (UMMA_K * 128), ATTN_CHUNK_BYTES), IDESC_O,
+                             ks != 0 ? 1u : 0u);
+            umma_commit(bar_o);
+            if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
+            if (group_ends && !last) {
+              load_v(h + 1, row0, n_s);
+            } else if (fetch_next) {
+              load_v(nx_h, nx_row0, nx_ns);
+              nx_loaded = true;
+            }
+            if (group_ends) ++groups_done;
+            ++heads_done;
           }
-          if (!mbar_wait(bar_p, ph, abort_flag)) { ATTN_FAIL(); break; }
-          if (u == 0 && !mbar_wait(bar_v, groups_done & 1u, abort_flag)) { ATTN_FAIL(); break; }
-          tc_fence_after();
-          for (int ks = 0; ks < ksteps; ++ks)
-            umma_ts<kBf16>(tmem_o, tmem_s + ks * 8, make_smem_desc_mn<kBf16>(sV + ks * (UMMA_K * 128), ATTN_CHUNK_BYTES), IDESC_O,
-                           ks != 0 ? 1u : 0u);
-          umma_commit(bar_o);
-          if (!mbar_wait(bar_o, ph, abort_flag)) { ATTN_FAIL(); break; }
-          if (group_ends && h + 1 < h_end) load_v(h + 1);
-          if (group_ends) ++groups_done;
-          ++heads_done;
         }
+        know_next();
       }
     } else if (has_work) {
       // ---------------------------------------------------------- softmax / output threads (one query row each)
@@ -383,11 +430,41 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
           const float inv = 1.f / l_sum;
           const long long orow = static_cast<long long>(row0 + qrow) * args.ld_out + h * D;
           const bool row_ok = qrow < L;
+          const bool stage_ok = Cfg::STAGE_OUT && !args.out_bf16 && (args.ld_out % 4 == 0) &&
+                                ((reinterpret_cast<uintptr_t>(args.out) & 15) == 0);
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t r[32];
             tmem_ld_32x32(tmem_o + lane_addr + c * 32, r);
             tmem_ld_wait();
+            if constexpr (Cfg::STAGE_OUT) {
+              if (stage_ok) {
+                // lane = row: the row's eight 16-byte pieces go to the warp's staging tile, piece j of row l at
+                // position j ^ (l & 7) (no bank conflicts either way); then lane l stores piece l % 8 of rows
+                // 4 k + l / 8, so that eight lanes write one whole 128-byte row
+                uint8_t* stg = smem + Cfg::STAGE_OFF + slot * Cfg::STAGE_BYTES + quad * 4096;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  float4 q = make_float4(__uint_as_float(r[4 * j]) * inv, __uint_as_float(r[4 * j + 1]) * inv,
+                                         __uint_as_float(r[4 * j + 2]) * inv, __uint_as_float(r[4 * j + 3]) * inv);
+                  if (args.round_tf32) {
+                    q.x = round_to_tf32(q.x); q.y = round_to_tf32(q.y); q.z = round_to_tf32(q.z); q.w = round_to_tf32(q.w);
+                  }
+                  *reinterpret_cast<float4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
+                }
+                __syncwarp();
+                const int piece = lane & 7;
+                float* obase = reinterpret_cast<float*>(args.out) + static_cast<long long>(row0 + quad * 32) * args.ld_out + h * D + piece * 4;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  const int rr = 4 * k + (lane >> 3);
+                  const float4 q = *reinterpret_cast<const float4*>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
+                  if (quad * 32 + rr < L) *reinterpret_cast<float4*>(obase + static_cast<long long>(rr) * args.ld_out) = q;
+                }
+                __syncwarp();
+                continue;
+              }
+            }
             if (row_ok) {
               if (args.out_bf16) {
                 __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + orow + c * 32;
