@@ -245,6 +245,7 @@ class Device:
         names = ["acquired", "released", "bytes_in_use", "peak_bytes", "pool_reserved_bytes",
                  "tensor_map_hits", "tensor_map_misses", "pool_hits"]
         d = {n: int(out[i]) for i, n in enumerate(names)}
+        self._prune()   # entries whose host array has died are not cached weights any more (their key may be reused)
         d["cached_weights"] = len(self._weights)
         return d
 
