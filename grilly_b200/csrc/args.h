@@ -99,6 +99,7 @@ struct EmbedArgs {
   float eps;
   int round_tf32;
   int out_bf16;            // write bf16 rows (bf16 encoder mode)
+  long long rows_hint;     // valid tokens of the batch if the caller knows them (for the byte count of the profile), else 0
 };
 
 struct PoolArgs {
@@ -109,6 +110,7 @@ struct PoolArgs {
   int B, S, F;
   int normalize;          // 1: divide the pooled vector by (||v||_2 + 1e-8)
   int cls;                // 1: take the sequence's first token instead of the mean (CLS pooling)
+  long long rows_hint;    // valid tokens of the batch if the caller knows them (for the byte count of the profile), else 0
 };
 
 }  // namespace gb

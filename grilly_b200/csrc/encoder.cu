@@ -171,7 +171,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
   em.pos = prenorm ? nullptr : e->pos;   // pre-norm models carry positions as RoPE inside attention (:1147-1155)
   em.type0 = (c.has_token_type && !prenorm) ? e->type : nullptr; em.gamma = e->emb_g; em.beta = e->emb_b; em.out = reinterpret_cast<float*>(e->x);
   em.B = Bc; em.S = S; em.F = F; em.vocab = c.vocab; em.max_pos = c.max_pos; em.eps = c.embed_ln_eps;
-  em.round_tf32 = e->bf16 ? 0 : 1; em.out_bf16 = e->bf16 ? 1 : 0;
+  em.round_tf32 = e->bf16 ? 0 : 1; em.out_bf16 = e->bf16 ? 1 : 0; em.rows_hint = rows;
   if ((rc = launch_embed(ctx, em))) return rc;
   float* final_hidden = e->bf16 ? e->xf : reinterpret_cast<float*>(e->x);
   if (prenorm) {
@@ -223,7 +223,7 @@ static int run_chunk(grilly_encoder* e, const int* ids_dev, const int* cu_chunk_
                               c.ffn, last && e->bf16))) return rc;
   }
   PoolArgs p{};
-  p.x = final_hidden; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1;
+  p.x = final_hidden; p.cu_seqlens = cu_chunk_dev; p.mask = key_mask_dev; p.out = out_dev + static_cast<long long>(b0) * F; p.B = Bc; p.S = S; p.F = F; p.normalize = 1; p.rows_hint = rows;
   p.cls = prenorm ? 1 : 0;
   if ((rc = launch_pool(ctx, p))) return rc;
   if (e->keep_hidden && e->hidden_all)

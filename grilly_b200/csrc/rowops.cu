@@ -91,7 +91,9 @@ int launch_embed(grilly_ctx* ctx, const EmbedArgs& a) {
   if (a.B <= 0 || a.S <= 0 || a.F <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "embed: sizes must be positive");
   if (a.F % 4 != 0 || a.F > 128 * 8) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "embed: hidden size must be a multiple of 4 and at most 1024");
   const int grid = grid_for(static_cast<long long>(a.B) * a.S, 8, ctx->num_sms);
-  const int pi = prof_begin(ctx, PROF_EMBED, 0.0, static_cast<double>(a.B) * a.S * (4.0 + 8.0 * a.F));
+  // ids of every position, one table row read and one row written per valid token (the position table stays in L2)
+  const double tokens = a.rows_hint > 0 ? static_cast<double>(a.rows_hint) : static_cast<double>(a.B) * a.S;
+  const int pi = prof_begin(ctx, PROF_EMBED, 0.0, static_cast<double>(a.B) * a.S * 4.0 + tokens * 8.0 * a.F);
   if (a.F <= 128 * 3) embed_ln_kernel<3><<<grid, 256, 0, ctx->stream>>>(a);
   else embed_ln_kernel<8><<<grid, 256, 0, ctx->stream>>>(a);
   prof_end(ctx, pi);
@@ -104,8 +106,12 @@ int launch_pool(grilly_ctx* ctx, const PoolArgs& a) {
   if (a.B <= 0 || a.S <= 0 || a.F <= 0) return set_error(ctx, GRILLY_ERR_INVALID_ARG, "mean_pool: sizes must be positive");
   const size_t smem = (static_cast<size_t>(a.F) + 8) * sizeof(float);
   if (smem > 48 * 1024) return set_error(ctx, GRILLY_ERR_UNSUPPORTED, "mean_pool: feature size too large");
-  const int pi = prof_begin(ctx, PROF_POOL, 0.0, static_cast<double>(a.B) * a.S * a.F * 4.0);
-  pool_normalize_kernel<<<a.B, 128, smem, ctx->stream>>>(a);
+  const double tokens = a.rows_hint > 0 ? static_cast<double>(a.rows_hint) : static_cast<double>(a.B) * a.S;
+  const int pi = prof_begin(ctx, PROF_POOL, 0.0, tokens * a.F * 4.0 + static_cast<double>(a.B) * a.F * 4.0);
+  const bool vec = a.F % 4 == 0 && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out)) & 15) == 0;
+  if (vec && a.F <= 128 * 3) pool_normalize_vec_kernel<3><<<a.B, 128, 0, ctx->stream>>>(a);
+  else if (vec && a.F <= 128 * 8) pool_normalize_vec_kernel<8><<<a.B, 128, 0, ctx->stream>>>(a);
+  else pool_normalize_kernel<<<a.B, 128, smem, ctx->stream>>>(a);
   prof_end(ctx, pi);
   ctx->launches++;
   GB_CUDA_CHECK(ctx, cudaGetLastError());

@@ -65,6 +65,12 @@ def test_embedding_lookup_and_pool(backend):
     pn = backend.pooling.mean_pool_normalize(x, mask)
     assert O.rel_l2(pn, O.embedding_normalize(O.mean_pool(x, mask))) < TOL
     assert np.array_equal(pn[2], np.zeros(384, np.float32))
+    # feature counts on the other pooling kernels: eight 16-byte pieces per lane (768) and the scalar form (770)
+    for feat in (768, 770):
+        xf = rng.standard_normal((3, 37, feat)).astype(np.float32)
+        mf = (rng.random((3, 37)) > 0.4).astype(np.float32)
+        assert O.rel_l2(backend.pooling.mean_pool(xf, mf), O.mean_pool(xf, mf)) < TOL
+        assert O.rel_l2(backend.pooling.mean_pool_normalize(xf, mf), O.embedding_normalize(O.mean_pool(xf, mf))) < TOL
 
 
 def test_device_resident_chain(backend):
