@@ -33,7 +33,7 @@ struct AttnShortCfg {
   static constexpr int SLOT_THREADS = 160;
   static constexpr int THREADS = NSLOT * SLOT_THREADS;
   static constexpr int SLOT_SMEM = 3 * TILE_BYTES;                // Q, K, V of one head (or head pair)
-  static constexpr int CTRL_BYTES = 96;                           // per slot: 6 barriers, unit, key-mask words
+  static constexpr int CTRL_BYTES = 96;                           // per slot: 6 barriers, the unit with its first row and length, key-mask words
   // fp32 rows of 32 features (128 bytes) leave the SM through a staging tile per softmax warp (32 rows x 128 B), so
   // that a store instruction writes four whole rows instead of a 16-byte piece of 32 rows; the other shapes have no
   // shared memory left for it and store from registers
@@ -85,7 +85,7 @@ flash_attn_short_kernel(const __grid_constant__ AttnShortMaps maps, const AttnAr
   uint64_t* bar_p = bar_qk + 3;                             // P written (one arrive per softmax warp)
   uint64_t* bar_o = bar_qk + 4;                             // O complete
   uint64_t* bar_or = bar_qk + 5;                            // O read out of TMEM (only when it shares columns with the next S)
-  volatile int* slot_unit = reinterpret_cast<volatile int*>(ctrl + 48);
+  volatile int* slot_unit = reinterpret_cast<volatile int*>(ctrl + 48);   // [0] unit, [1] its first packed row, [2] its length
   uint32_t* s_keep = reinterpret_cast<uint32_t*>(ctrl + 64);   // [4] key-mask bit words of the slot's sequence
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + Cfg::CTRL_OFF + Cfg::NSLOT * Cfg::CTRL_BYTES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
